@@ -1,0 +1,339 @@
+// BF16 GEMM on the sm_100a tensor cores: C[M,N] = A[M,K] @ B, FP32 accumulation in TMEM.
+//
+// Extends the reference operator (naive/naive.cpp:6-22; kernels naive/naive_1.cu:5-15,
+// shared/shared_2.cu:4-57, blocktile_1d/blocktile_1d.cu:5-68 compute the same C = A @ B in
+// FP32 on CUDA cores) to BF16 operands.
+//
+// One persistent, warp-specialised kernel (192 threads):
+//   warp 0     TMA producer: 128B-swizzled tiles of A and B into a STAGES-deep smem ring;
+//   warp 1     owns TMEM; one thread issues tcgen05.mma (UMMA K = 16) and commits to mbarriers;
+//   warps 2-5  epilogue: tcgen05.ld the FP32 accumulator, convert, store (direct 16-byte global
+//              stores, or per-warp swizzled staging + TMA store).
+// The accumulator is double-buffered in TMEM (2 x 256 columns) so the epilogue of tile i
+// overlaps the main loop of tile i+1.  With CG = 2 two CTAs on neighbouring SMs share one
+// 256x256 tile: each loads its own 128 rows of A and its own 128 columns of B, and the leader
+// CTA issues one cta_group::2 MMA that reads both halves.  No load uses cluster multicast.
+// Tiles are assigned statically (tile = cluster id + i * clusters) along a grouped raster that
+// keeps the tiles in flight on a compact patch of C so A/B tiles are re-read from L2.
+//
+// B row-major [K,N] is fed as an "MN-major" UMMA operand (the k rows of a tile are 128-byte
+// rows of 64 consecutive n); B given as Bt[N,K] is the usual K-major operand.
+#pragma once
+#include <cuda_bf16.h>
+#include "common.cuh"
+#include "tc_common.cuh"
+
+namespace gemm_b200 {
+namespace tc {
+
+constexpr int kBlockM = 128;   // rows of C per CTA
+constexpr int kBlockN = 256;   // columns of C per MMA (per CTA for CG = 1, per CTA pair for CG = 2)
+constexpr int kBlockK = 64;    // bf16 elements per 128-byte swizzled row
+constexpr int kUmmaK = 16;
+constexpr int kTmemCols = 512;
+constexpr int kGemmThreads = 192;
+
+// EPI: 0 = direct global stores, 1 = swizzled smem staging + TMA store
+// COMMIT_MASK: CTA-pair commits use the masked form (one instruction for both CTAs) instead of two
+template <int CG_, int STAGES_, int EPI_, bool COMMIT_MASK_>
+struct Bf16Cfg {
+  static constexpr int CG = CG_, STAGES = STAGES_, EPI = EPI_;
+  static constexpr bool COMMIT_MASK = COMMIT_MASK_;
+  static constexpr int BN_CTA = kBlockN / CG;                       // columns of B each CTA loads
+  static constexpr int A_BYTES = kBlockM * kBlockK * 2;             // 16 KB
+  static constexpr int B_BYTES = BN_CTA * kBlockK * 2;              // 32 KB / 16 KB
+  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  static constexpr int EPI_WARP_BUF = 32 * 128;                     // 32 rows x 128 bytes
+  static constexpr int EPI_BYTES = 4 * 2 * EPI_WARP_BUF;            // 4 warps x 2 buffers
+  static constexpr int BAR_BYTES = (2 * STAGES + 4) * 8 + 16;
+  static constexpr int SMEM_BYTES = 1024 + STAGES * STAGE_BYTES + EPI_BYTES + BAR_BYTES;
+  static_assert(SMEM_BYTES <= 232448, "shared memory budget");
+};
+
+struct GemmShape {
+  int M, N, K;
+  int tiles_m, tiles_n;   // tiles of (kBlockM * CG) x kBlockN
+};
+
+__device__ __forceinline__ void tile_coord(int t, int tiles_m, int tiles_n, int& tm, int& tn) {
+  constexpr int GROUP = 8;
+  const int width = GROUP * tiles_n;
+  const int first_m = (t / width) * GROUP;
+  const int gsz = min(tiles_m - first_m, GROUP);
+  tm = first_m + (t % width) % gsz;
+  tn = (t % width) / gsz;
+}
+
+template <class Cfg, bool B_MN, bool OUT_F32>
+__global__ void __launch_bounds__(kGemmThreads, 1)
+gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                 const __grid_constant__ CUtensorMap tmC, void* __restrict__ Cptr, int64_t ldc,
+                 const GemmShape shape) {
+  constexpr int CG = Cfg::CG, STAGES = Cfg::STAGES;
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  const uint32_t sA0 = smem_base;
+  const uint32_t sB0 = smem_base + STAGES * Cfg::A_BYTES;
+  const uint32_t sEpi0 = smem_base + STAGES * Cfg::STAGE_BYTES;
+  const uint32_t bar0 = sEpi0 + Cfg::EPI_BYTES;
+  auto full_bar = [&](int s) { return bar0 + 8u * s; };
+  auto empty_bar = [&](int s) { return bar0 + 8u * (STAGES + s); };
+  auto tfull_bar = [&](int a) { return bar0 + 8u * (2 * STAGES + a); };
+  auto tempty_bar = [&](int a) { return bar0 + 8u * (2 * STAGES + 2 + a); };
+  const uint32_t tmem_slot = bar0 + 8u * (2 * STAGES + 4);
+
+  const int warp = __shfl_sync(0xffffffffu, (int)(threadIdx.x >> 5), 0);
+  const int lane = threadIdx.x & 31;
+  const uint32_t cta_rank = (CG == 2) ? cluster_ctarank() : 0u;
+  const int cluster_id = blockIdx.x / CG;
+  const int num_clusters = gridDim.x / CG;
+  const int num_tiles = shape.tiles_m * shape.tiles_n;
+  const int num_kb = (shape.K + kBlockK - 1) / kBlockK;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(full_bar(s), 1);
+      mbar_init(empty_bar(s), 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(tfull_bar(a), 1);
+      mbar_init(tempty_bar(a), 4 * CG);   // one arrival per epilogue warp of every CTA of the pair
+    }
+    fence_mbar_init();
+  }
+  if (warp == 0 && lane == 0) {
+    prefetch_tensormap(&tmA);
+    prefetch_tensormap(&tmB);
+    if (Cfg::EPI == 1) prefetch_tensormap(&tmC);
+  }
+  if (warp == 1) {
+    tmem_alloc<CG>(tmem_slot, kTmemCols);
+    tmem_relinquish<CG>();
+    tc_fence_before_sync();
+  }
+  __syncthreads();
+  if (CG == 2) {
+    cluster_arrive();
+    cluster_wait();
+  }
+  tc_fence_after_sync();
+  uint32_t tmem_base;
+  asm volatile("ld.shared.u32 %0, [%1];" : "=r"(tmem_base) : "r"(tmem_slot) : "memory");
+
+  bool failed = false;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      uint32_t it = 0;
+      for (int t = cluster_id; t < num_tiles && !failed; t += num_clusters) {
+        int tm, tn;
+        tile_coord(t, shape.tiles_m, shape.tiles_n, tm, tn);
+        const int m0 = (tm * CG + (int)cta_rank) * kBlockM;
+        const int n0 = tn * kBlockN + (int)cta_rank * Cfg::BN_CTA;
+        for (int kb = 0; kb < num_kb; ++kb, ++it) {
+          const int s = it % STAGES;
+          const uint32_t ph = (it / STAGES) & 1u;
+          if (!mbar_wait(empty_bar(s), ph ^ 1u, kRoleProducer, s)) { failed = true; break; }
+          const uint32_t a_dst = sA0 + s * Cfg::A_BYTES, b_dst = sB0 + s * Cfg::B_BYTES;
+          if constexpr (CG == 1) {
+            mbar_arrive_expect_tx(full_bar(s), Cfg::STAGE_BYTES);
+            tma_load_2d(a_dst, &tmA, kb * kBlockK, m0, full_bar(s));
+            if constexpr (B_MN) {
+#pragma unroll
+              for (int j = 0; j < Cfg::BN_CTA / 64; ++j)
+                tma_load_2d(b_dst + j * 8192, &tmB, n0 + j * 64, kb * kBlockK, full_bar(s));
+            } else {
+              tma_load_2d(b_dst, &tmB, kb * kBlockK, n0, full_bar(s));
+            }
+          } else {
+            // Both CTAs of the pair report their bytes to the leader's barrier.
+            const uint32_t lead_full = map_to_cta(full_bar(s), 0);
+            if (cta_rank == 0) mbar_arrive_expect_tx(full_bar(s), 2 * Cfg::STAGE_BYTES);
+            tma_load_2d_pair(a_dst, &tmA, kb * kBlockK, m0, lead_full);
+            if constexpr (B_MN) {
+#pragma unroll
+              for (int j = 0; j < Cfg::BN_CTA / 64; ++j)
+                tma_load_2d_pair(b_dst + j * 8192, &tmB, n0 + j * 64, kb * kBlockK, lead_full);
+            } else {
+              tma_load_2d_pair(b_dst, &tmB, kb * kBlockK, n0, lead_full);
+            }
+          }
+        }
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer (leader CTA)
+    if (lane == 0 && cta_rank == 0) {
+      constexpr uint32_t idesc = make_idesc_bf16(kBlockM * CG, kBlockN, 0, B_MN ? 1 : 0);
+      constexpr uint64_t a_hi = make_smem_desc_hi(16, 1024, kLayoutSw128);
+      constexpr uint64_t b_hi = B_MN ? make_smem_desc_hi(8192, 1024, kLayoutSw128)
+                                     : make_smem_desc_hi(16, 1024, kLayoutSw128);
+      constexpr uint32_t b_kstep = B_MN ? (kUmmaK * 128) : (kUmmaK * 2);
+      auto commit = [&](uint32_t bar) {
+        if constexpr (CG == 1) {
+          mma_commit_local(bar);
+        } else if constexpr (Cfg::COMMIT_MASK) {
+          mma_commit_pair_mask(bar, (uint16_t)3);
+        } else {
+          mma_commit_pair(map_to_cta(bar, 0));
+          mma_commit_pair(map_to_cta(bar, 1));
+        }
+      };
+      uint32_t it = 0, acc_it = 0;
+      for (int t = cluster_id; t < num_tiles && !failed; t += num_clusters, ++acc_it) {
+        const uint32_t acc = acc_it & 1u, aph = (acc_it >> 1) & 1u;
+        if (!mbar_wait(tempty_bar(acc), aph ^ 1u, kRoleMma, 100 + (int)acc)) { failed = true; break; }
+        tc_fence_after_sync();
+        const uint32_t d_tmem = tmem_base + acc * kBlockN;
+        for (int kb = 0; kb < num_kb; ++kb, ++it) {
+          const int s = it % STAGES;
+          const uint32_t ph = (it / STAGES) & 1u;
+          if (!mbar_wait(full_bar(s), ph, kRoleMma, s)) { failed = true; break; }
+          tc_fence_after_sync();
+          const uint32_t a_addr = sA0 + s * Cfg::A_BYTES, b_addr = sB0 + s * Cfg::B_BYTES;
+#pragma unroll
+          for (int k = 0; k < kBlockK / kUmmaK; ++k) {
+            mma_f16<CG>(d_tmem, smem_desc(a_hi, a_addr + k * (kUmmaK * 2)), smem_desc(b_hi, b_addr + k * b_kstep),
+                        idesc, (kb | k) != 0 ? 1u : 0u);
+          }
+          commit(empty_bar(s));   // frees the smem slot in both CTAs once these MMAs have read it
+        }
+        if (failed) break;
+        commit(tfull_bar(acc));   // accumulator complete -> epilogue warps of both CTAs
+      }
+    }
+    __syncwarp();
+  } else {
+    // ------------------------------------------------------------------ epilogue warps 2..5
+    const int quad = warp & 3;   // TMEM lanes [32 quad, 32 quad + 32) are the ones this warp may read
+    const uint32_t lane_base = (uint32_t)(quad * 32) << 16;
+    const uint32_t stage0 = sEpi0 + (uint32_t)(warp - 2) * 2u * Cfg::EPI_WARP_BUF;
+    uint32_t acc_it = 0, store_it = 0;
+    for (int t = cluster_id; t < num_tiles && !failed; t += num_clusters, ++acc_it) {
+      int tm, tn;
+      tile_coord(t, shape.tiles_m, shape.tiles_n, tm, tn);
+      const int m0 = (tm * CG + (int)cta_rank) * kBlockM + quad * 32;   // first row of this warp
+      const int n0 = tn * kBlockN;
+      const uint32_t acc = acc_it & 1u, aph = (acc_it >> 1) & 1u;
+      // every lane waits, and the warp moves on only if every lane saw the phase complete: the
+      // TMEM loads below are warp-collective and must not run with part of the warp missing
+      const bool ready = mbar_wait(tfull_bar(acc), aph, kRoleEpilogue, 200 + (int)acc);
+      if (!__all_sync(0xffffffffu, ready)) { failed = true; break; }
+      tc_fence_after_sync();
+      const uint32_t t_addr = tmem_base + lane_base + acc * kBlockN;
+      const int row = m0 + lane;
+
+      if constexpr (Cfg::EPI == 0) {
+#pragma unroll 1
+        for (int c = 0; c < kBlockN / 32; ++c) {
+          uint32_t v[32];
+          tmem_ld_32x32b_x32(t_addr + c * 32, v);
+          tmem_ld_wait();
+          const int col = n0 + c * 32;
+          if (row < shape.M) {
+            if constexpr (OUT_F32) {
+              float* dst = reinterpret_cast<float*>(Cptr) + (int64_t)row * ldc + col;
+#pragma unroll
+              for (int j = 0; j < 8; ++j)
+                if (col + 4 * j < shape.N)
+                  *reinterpret_cast<uint4*>(dst + 4 * j) = make_uint4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+            } else {
+              __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(Cptr) + (int64_t)row * ldc + col;
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                if (col + 8 * j < shape.N) {
+                  uint32_t p[4];
+#pragma unroll
+                  for (int e = 0; e < 4; ++e) {
+                    __nv_bfloat162 h = __floats2bfloat162_rn(__uint_as_float(v[8 * j + 2 * e]),
+                                                             __uint_as_float(v[8 * j + 2 * e + 1]));
+                    p[e] = *reinterpret_cast<uint32_t*>(&h);
+                  }
+                  *reinterpret_cast<uint4*>(dst + 8 * j) = make_uint4(p[0], p[1], p[2], p[3]);
+                }
+              }
+            }
+          }
+        }
+      } else {
+        // 128-byte-wide column slabs: 64 bf16 or 32 f32 columns per TMA store of 32 rows.
+        constexpr int SLAB_COLS = OUT_F32 ? 32 : 64;
+#pragma unroll 1
+        for (int c = 0; c < kBlockN / SLAB_COLS; ++c, ++store_it) {
+          const uint32_t buf = stage0 + (store_it & 1u) * Cfg::EPI_WARP_BUF;
+          // the store that last read this buffer was committed two slabs ago
+          if (lane == 0) tma_store_wait_read<1>();
+          __syncwarp();
+          const uint32_t row_addr = buf + (uint32_t)lane * 128u;
+          const uint32_t sw = (uint32_t)(lane & 7);
+          if constexpr (OUT_F32) {
+            uint32_t v[32];
+            tmem_ld_32x32b_x32(t_addr + c * 32, v);
+            tmem_ld_wait();
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+              asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(row_addr + (((uint32_t)j ^ sw) << 4)),
+                           "r"(v[4 * j]), "r"(v[4 * j + 1]), "r"(v[4 * j + 2]), "r"(v[4 * j + 3]) : "memory");
+          } else {
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+              uint32_t v[32];
+              tmem_ld_32x32b_x32(t_addr + c * 64 + h * 32, v);
+              tmem_ld_wait();
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                uint32_t p[4];
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                  __nv_bfloat162 hh = __floats2bfloat162_rn(__uint_as_float(v[8 * j + 2 * e]),
+                                                            __uint_as_float(v[8 * j + 2 * e + 1]));
+                  p[e] = *reinterpret_cast<uint32_t*>(&hh);
+                }
+                asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};"
+                             ::"r"(row_addr + (((uint32_t)(h * 4 + j) ^ sw) << 4)), "r"(p[0]), "r"(p[1]), "r"(p[2]), "r"(p[3])
+                             : "memory");
+              }
+            }
+          }
+          fence_proxy_async_smem();
+          __syncwarp();
+          const int x = n0 + c * SLAB_COLS;
+          if (lane == 0) {
+            if (m0 < shape.M && x < shape.N) tma_store_2d(&tmC, x, m0, buf);
+            tma_store_commit();
+          }
+        }
+      }
+      // accumulator fully read: hand the TMEM buffer back to the MMA issuer (leader CTA)
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) {
+        if constexpr (CG == 1) mbar_arrive(tempty_bar(acc));
+        else mbar_arrive_cluster(map_to_cta(tempty_bar(acc), 0));
+      }
+    }
+    if (Cfg::EPI == 1 && lane == 0) tma_store_wait_all<0>();
+  }
+
+  // ------------------------------------------------------------------ teardown
+  if (failed || aborted()) {
+    // give copies and MMAs still in flight time to land before shared memory and TMEM go away
+    const unsigned long long t0 = globaltimer_ns();
+    while (globaltimer_ns() - t0 < 200000ull) __nanosleep(1000);
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  if (CG == 2) {
+    cluster_arrive();
+    cluster_wait();
+  }
+  if (warp == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc<CG>(tmem_base, kTmemCols);
+  }
+}
+
+}  // namespace tc
+}  // namespace gemm_b200

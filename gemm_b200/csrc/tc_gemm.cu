@@ -1,0 +1,267 @@
+// Host side of the tensor-core entry points: argument checks, TMA descriptors, persistent
+// grid sizing and launches.  Compiled for sm_100a only (tcgen05 needs the arch-specific target).
+#include <mutex>
+
+#include "gemm_bf16.cuh"
+
+namespace gemm_b200 {
+namespace tc {
+
+// cuTensorMapEncodeTiled is fetched through the runtime so the library does not link libcuda.
+using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_tiled_fn() {
+  static EncodeTiledFn fn = [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess ||
+        q != cudaDriverEntryPointSuccess)
+      p = nullptr;
+    return reinterpret_cast<EncodeTiledFn>(p);
+  }();
+  return fn;
+}
+
+// 2-D row-major tensor [rows, cols] with `ld` elements between rows; box = box_cols x box_rows.
+static int make_map_2d(CUtensorMap* map, CUtensorMapDataType dt, int elem_bytes, const void* ptr, int64_t rows,
+                       int64_t cols, int64_t ld, int box_cols, int box_rows, CUtensorMapSwizzle swz) {
+  EncodeTiledFn fn = encode_tiled_fn();
+  if (!fn) return fail(GEMM_B200_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
+  cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)ld * (cuuint64_t)elem_bytes};
+  cuuint32_t box[2] = {(cuuint32_t)box_cols, (cuuint32_t)box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(map, dt, 2, const_cast<void*>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, swz,
+                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS)
+    return fail(GEMM_B200_ERR_CUDA, "cuTensorMapEncodeTiled failed with CUresult %d (rows=%lld cols=%lld ld=%lld box=%dx%d)",
+                (int)r, (long long)rows, (long long)cols, (long long)ld, box_cols, box_rows);
+  return GEMM_B200_OK;
+}
+
+struct DeviceInfo {
+  int dev = -1, sms = 0, cc_major = 0;
+};
+static int device_info(DeviceInfo* out) {
+  static thread_local DeviceInfo cached;
+  int dev = 0;
+  GEMM_B200_CUDA_TRY(cudaGetDevice(&dev));
+  if (cached.dev != dev) {
+    GEMM_B200_CUDA_TRY(cudaDeviceGetAttribute(&cached.sms, cudaDevAttrMultiProcessorCount, dev));
+    GEMM_B200_CUDA_TRY(cudaDeviceGetAttribute(&cached.cc_major, cudaDevAttrComputeCapabilityMajor, dev));
+    cached.dev = dev;
+  }
+  *out = cached;
+  return GEMM_B200_OK;
+}
+
+struct Bf16Args {
+  const void *A, *B;
+  void* C;
+  int64_t M, N, K, lda, ldb, ldc;
+  cudaStream_t stream;
+};
+
+// One instantiation per (config, B layout, output type).
+template <class Cfg, bool B_MN, bool OUT_F32>
+static int launch_bf16(const Bf16Args& a) {
+  constexpr int CG = Cfg::CG;
+  DeviceInfo di;
+  if (int rc = device_info(&di)) return rc;
+  CUtensorMap tmA, tmB, tmC;
+  if (int rc = make_map_2d(&tmA, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, a.A, a.M, a.K, a.lda, kBlockK, kBlockM,
+                           CU_TENSOR_MAP_SWIZZLE_128B))
+    return rc;
+  if (B_MN) {
+    if (int rc = make_map_2d(&tmB, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, a.B, a.K, a.N, a.ldb, 64, kBlockK,
+                             CU_TENSOR_MAP_SWIZZLE_128B))
+      return rc;
+  } else {
+    if (int rc = make_map_2d(&tmB, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, a.B, a.N, a.K, a.ldb, kBlockK, Cfg::BN_CTA,
+                             CU_TENSOR_MAP_SWIZZLE_128B))
+      return rc;
+  }
+  if (Cfg::EPI == 1) {
+    if (int rc = make_map_2d(&tmC, OUT_F32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16,
+                             OUT_F32 ? 4 : 2, a.C, a.M, a.N, a.ldc, OUT_F32 ? 32 : 64, 32, CU_TENSOR_MAP_SWIZZLE_128B))
+      return rc;
+  } else {
+    tmC = tmA;   // unused by the kernel
+  }
+
+  auto kern = gemm_bf16_kernel<Cfg, B_MN, OUT_F32>;
+  static std::mutex mu;
+  static int max_clusters_for_dev[64] = {0};
+  int max_clusters = 0;
+  {
+    std::lock_guard<std::mutex> lk(mu);
+    const int slot = di.dev & 63;
+    if (max_clusters_for_dev[slot] == 0) {
+      GEMM_B200_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES));
+      int n = di.sms / CG;
+      if (CG > 1) {
+        cudaLaunchConfig_t qc = {};
+        qc.gridDim = dim3((unsigned)(di.sms / CG * CG));
+        qc.blockDim = dim3(kGemmThreads);
+        qc.dynamicSmemBytes = Cfg::SMEM_BYTES;
+        cudaLaunchAttribute qa[1];
+        qa[0].id = cudaLaunchAttributeClusterDimension;
+        qa[0].val.clusterDim.x = CG;
+        qa[0].val.clusterDim.y = 1;
+        qa[0].val.clusterDim.z = 1;
+        qc.attrs = qa;
+        qc.numAttrs = 1;
+        int active = 0;
+        GEMM_B200_CUDA_TRY(cudaOccupancyMaxActiveClusters(&active, kern, &qc));
+        if (active < 1) return fail(GEMM_B200_ERR_CUDA, "gemm_bf16: no CTA pair fits on this device");
+        if (active < n) n = active;
+      }
+      max_clusters_for_dev[slot] = n;
+    }
+    max_clusters = max_clusters_for_dev[slot];
+  }
+
+  GemmShape shape;
+  shape.M = (int)a.M;
+  shape.N = (int)a.N;
+  shape.K = (int)a.K;
+  shape.tiles_m = (int)ceil_div64(a.M, kBlockM * CG);
+  shape.tiles_n = (int)ceil_div64(a.N, kBlockN);
+  const int64_t num_tiles = (int64_t)shape.tiles_m * shape.tiles_n;
+  if (num_tiles > 0x7fffffff) return fail(GEMM_B200_ERR_TOO_LARGE, "gemm_bf16: too many tiles");
+  const int clusters = (int)(num_tiles < max_clusters ? num_tiles : max_clusters);
+
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)(clusters * CG));
+  cfg.blockDim = dim3(kGemmThreads);
+  cfg.dynamicSmemBytes = Cfg::SMEM_BYTES;
+  cfg.stream = a.stream;
+  cudaLaunchAttribute attrs[1];
+  attrs[0].id = cudaLaunchAttributeClusterDimension;
+  attrs[0].val.clusterDim.x = CG;
+  attrs[0].val.clusterDim.y = 1;
+  attrs[0].val.clusterDim.z = 1;
+  cfg.attrs = attrs;
+  cfg.numAttrs = 1;
+  void* cptr = a.C;
+  int64_t ldc = a.ldc;
+  GEMM_B200_CUDA_TRY(cudaLaunchKernelEx(&cfg, kern, tmA, tmB, tmC, cptr, ldc, shape));
+  launch_counter().fetch_add(1, std::memory_order_relaxed);
+  return GEMM_B200_OK;
+}
+
+struct Bf16ConfigEntry {
+  const char* name;
+  int (*launch[2][2])(const Bf16Args&);   // [b_layout][out_dtype]
+};
+
+#define GEMM_B200_BF16_ENTRY(NAME, CFG)                                                          \
+  {                                                                                              \
+    NAME, {                                                                                      \
+      {launch_bf16<CFG, true, false>, launch_bf16<CFG, true, true>},                             \
+      {launch_bf16<CFG, false, false>, launch_bf16<CFG, false, true>}                            \
+    }                                                                                            \
+  }
+
+//                          CG ST EPI MASK
+using Bf16_1cta_direct = Bf16Cfg<1, 4, 0, false>;
+using Bf16_1cta_tma    = Bf16Cfg<1, 4, 1, false>;
+using Bf16_2cta_direct = Bf16Cfg<2, 6, 0, false>;
+using Bf16_2cta_tma    = Bf16Cfg<2, 6, 1, false>;
+using Bf16_2cta_tma_m  = Bf16Cfg<2, 6, 1, true>;
+
+static const Bf16ConfigEntry kBf16Configs[] = {
+    GEMM_B200_BF16_ENTRY("1cta_128x256x64_s4_direct", Bf16_1cta_direct),
+    GEMM_B200_BF16_ENTRY("1cta_128x256x64_s4_tmastore", Bf16_1cta_tma),
+    GEMM_B200_BF16_ENTRY("2cta_256x256x64_s6_direct", Bf16_2cta_direct),
+    GEMM_B200_BF16_ENTRY("2cta_256x256x64_s6_tmastore", Bf16_2cta_tma),
+    GEMM_B200_BF16_ENTRY("2cta_256x256x64_s6_tmastore_maskcommit", Bf16_2cta_tma_m),
+};
+constexpr int kNumBf16Configs = sizeof(kBf16Configs) / sizeof(kBf16Configs[0]);
+constexpr int kDefaultBf16Config = 3;
+
+}  // namespace tc
+}  // namespace gemm_b200
+
+extern "C" int gemm_b200_gemm_bf16_cfg(const void* A, const void* B, void* C, int64_t M, int64_t N, int64_t K,
+                                       int64_t lda, int64_t ldb, int64_t ldc, int b_layout, int out_dtype,
+                                       int config, void* stream) {
+  using namespace gemm_b200;
+  if (M < 0 || N < 0 || K < 0) return fail(GEMM_B200_ERR_INVALID_ARG, "gemm_bf16: negative size");
+  if (b_layout != GEMM_B200_B_ROW_MAJOR_KN && b_layout != GEMM_B200_B_ROW_MAJOR_NK)
+    return fail(GEMM_B200_ERR_INVALID_ARG, "gemm_bf16: b_layout %d", b_layout);
+  if (out_dtype != GEMM_B200_OUT_BF16 && out_dtype != GEMM_B200_OUT_F32)
+    return fail(GEMM_B200_ERR_INVALID_ARG, "gemm_bf16: out_dtype %d", out_dtype);
+  if (config >= tc::kNumBf16Configs) return fail(GEMM_B200_ERR_INVALID_ARG, "gemm_bf16: config %d out of range", config);
+  if (M == 0 || N == 0) return GEMM_B200_OK;
+  if (!C || (K > 0 && (!A || !B))) return fail(GEMM_B200_ERR_INVALID_ARG, "gemm_bf16: null pointer");
+  const int64_t b_row = (b_layout == GEMM_B200_B_ROW_MAJOR_KN) ? N : K;
+  if (lda < K || ldb < b_row || ldc < N)
+    return fail(GEMM_B200_ERR_INVALID_ARG, "gemm_bf16: leading dimension smaller than the row (lda=%lld ldb=%lld ldc=%lld)",
+                (long long)lda, (long long)ldb, (long long)ldc);
+  if (M > 0x7fffffff || N > 0x7fffffff || K > 0x7fffffff)
+    return fail(GEMM_B200_ERR_TOO_LARGE, "gemm_bf16: a dimension exceeds 2^31-1");
+  const int c_elem = out_dtype == GEMM_B200_OUT_F32 ? 4 : 2;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (K == 0) {
+    GEMM_B200_CUDA_TRY(cudaMemset2DAsync(C, (size_t)ldc * c_elem, 0, (size_t)N * c_elem, (size_t)M, st));
+    return GEMM_B200_OK;
+  }
+  if ((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(B) | reinterpret_cast<uintptr_t>(C)) % 16 != 0)
+    return fail(GEMM_B200_ERR_ALIGNMENT, "gemm_bf16: A, B and C must be 16-byte aligned");
+  if (lda % 8 != 0 || ldb % 8 != 0 || (ldc * c_elem) % 16 != 0 || N % (16 / c_elem) != 0)
+    return fail(GEMM_B200_ERR_ALIGNMENT,
+                "gemm_bf16: lda and ldb must be multiples of 8, ldc*sizeof(C) and N*sizeof(C) multiples of 16 bytes "
+                "(lda=%lld ldb=%lld ldc=%lld N=%lld)", (long long)lda, (long long)ldb, (long long)ldc, (long long)N);
+  tc::DeviceInfo di;
+  if (int rc = tc::device_info(&di)) return rc;
+  if (di.cc_major != 10)
+    return fail(GEMM_B200_ERR_UNSUPPORTED, "gemm_bf16: device has compute capability %d.x, need 10.x (sm_100a)", di.cc_major);
+  if (config < 0) config = tc::kDefaultBf16Config;
+  tc::Bf16Args args{A, B, C, M, N, K, lda, ldb, ldc, st};
+  return tc::kBf16Configs[config].launch[b_layout][out_dtype](args);
+}
+
+extern "C" int gemm_b200_gemm_bf16(const void* A, const void* B, void* C, int64_t M, int64_t N, int64_t K,
+                                   int64_t lda, int64_t ldb, int64_t ldc, int b_layout, int out_dtype, void* stream) {
+  return gemm_b200_gemm_bf16_cfg(A, B, C, M, N, K, lda, ldb, ldc, b_layout, out_dtype, -1, stream);
+}
+extern "C" int gemm_b200_gemm_bf16_num_configs(void) { return gemm_b200::tc::kNumBf16Configs; }
+extern "C" const char* gemm_b200_gemm_bf16_config_name(int config) {
+  if (config < 0 || config >= gemm_b200::tc::kNumBf16Configs) return "";
+  return gemm_b200::tc::kBf16Configs[config].name;
+}
+
+extern "C" int gemm_b200_check_status(void* stream, int32_t detail[4]) {
+  using namespace gemm_b200;
+  GEMM_B200_CUDA_TRY(cudaStreamSynchronize(static_cast<cudaStream_t>(stream)));
+  int32_t h[4] = {0, 0, 0, 0};
+  GEMM_B200_CUDA_TRY(cudaMemcpyFromSymbol(h, tc::g_status, sizeof(h)));
+  if (detail)
+    for (int i = 0; i < 4; ++i) detail[i] = h[i];
+  if (h[0] != 0) {
+    const int32_t z[4] = {0, 0, 0, 0};
+    GEMM_B200_CUDA_TRY(cudaMemcpyToSymbol(tc::g_status, z, sizeof(z)));
+    return fail(GEMM_B200_ERR_TIMEOUT, "a device-side wait gave up: block %d role %d stage %d", h[1], h[2], h[3]);
+  }
+  return GEMM_B200_OK;
+}
+
+// ---- MXFP8 entry points: placeholder until the block-scaled kernels land in this file ----
+extern "C" int gemm_b200_quantize_mxfp8(const void*, int64_t, int64_t, int64_t, int, void*, void*, void*) {
+  return gemm_b200::fail(GEMM_B200_ERR_UNSUPPORTED, "quantize_mxfp8: not built");
+}
+extern "C" size_t gemm_b200_mxfp8_scale_bytes(int64_t, int64_t) { return 0; }
+extern "C" size_t gemm_b200_mxfp8_scale_offset(int64_t, int64_t, int64_t, int64_t) { return 0; }
+extern "C" int gemm_b200_gemm_mxfp8(const void*, const void*, const void*, const void*, void*, int64_t, int64_t, int64_t,
+                                    int64_t, int, void*) {
+  return gemm_b200::fail(GEMM_B200_ERR_UNSUPPORTED, "gemm_mxfp8: not built");
+}
+extern "C" int gemm_b200_gemm_mxfp8_cfg(const void*, const void*, const void*, const void*, void*, int64_t, int64_t,
+                                        int64_t, int64_t, int, int, void*) {
+  return gemm_b200::fail(GEMM_B200_ERR_UNSUPPORTED, "gemm_mxfp8: not built");
+}
+extern "C" int gemm_b200_gemm_mxfp8_num_configs(void) { return 0; }
+extern "C" const char* gemm_b200_gemm_mxfp8_config_name(int) { return ""; }

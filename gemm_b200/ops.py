@@ -1,0 +1,129 @@
+"""Operators of the library on torch CUDA tensors.
+
+torch is used for device memory and streams only; every function here hands raw pointers to
+the C-ABI (``include/gemm_b200.h``).  The calling convention mirrors the reference wrappers
+(naive/naive.cpp:6-22): ``f(A, B, C) -> C`` writes the caller's C in place and returns it;
+``out=None`` allocates."""
+from __future__ import annotations
+
+import ctypes as C
+
+import torch
+
+from . import _lib
+from ._lib import lib, check
+
+__all__ = [
+    "sgemm_f32", "gemm_bf16", "check_status", "sgemm_f32_host", "gemm_bf16_host",
+    "sgemm_f32_configs", "gemm_bf16_configs", "launch_count",
+]
+
+
+def _stream(t: torch.Tensor) -> int:
+    return torch.cuda.current_stream(t.device).cuda_stream
+
+
+def _require(cond: bool, msg: str) -> None:
+    if not cond:
+        raise ValueError(msg)
+
+
+def _row_major_ld(t: torch.Tensor) -> int:
+    _require(t.dim() == 2, "expected a 2-D tensor")
+    _require(t.size(1) <= 1 or t.stride(1) == 1, "tensor must be row-major (unit column stride)")
+    return t.stride(0) if t.size(0) > 1 else max(t.size(1), 1)
+
+
+def sgemm_f32(A: torch.Tensor, B: torch.Tensor, out: torch.Tensor | None = None, config: int = -1) -> torch.Tensor:
+    """FP32 ``C = A @ B`` on CUDA cores, bit-identical to the reference kernels."""
+    _require(A.is_cuda and B.is_cuda, "A and B must be CUDA tensors")
+    _require(A.dtype == torch.float32 and B.dtype == torch.float32, "expected float32")
+    M, K = A.shape
+    _require(B.shape[0] == K, f"A is {tuple(A.shape)} but B is {tuple(B.shape)}")
+    N = B.shape[1]
+    if out is None:
+        out = torch.empty((M, N), device=A.device, dtype=torch.float32)
+    _require(out.is_cuda and out.dtype == torch.float32 and tuple(out.shape) == (M, N), "bad out tensor")
+    with torch.cuda.device(A.device):
+        check(lib.gemm_b200_sgemm_f32_cfg(A.data_ptr(), B.data_ptr(), out.data_ptr(), M, N, K, _row_major_ld(A),
+                                          _row_major_ld(B), _row_major_ld(out), config, _stream(A)))
+    return out
+
+
+def gemm_bf16(A: torch.Tensor, B: torch.Tensor, out: torch.Tensor | None = None, *, b_is_nk: bool = False,
+              out_dtype: torch.dtype = torch.bfloat16, config: int = -1) -> torch.Tensor:
+    """BF16 ``C = A @ B`` on the tensor cores with FP32 accumulation.
+
+    ``B`` is ``[K, N]`` row-major (the reference's layout) or, with ``b_is_nk``, its transpose
+    ``[N, K]`` row-major."""
+    _require(A.is_cuda and B.is_cuda, "A and B must be CUDA tensors")
+    _require(A.dtype == torch.bfloat16 and B.dtype == torch.bfloat16, "expected bfloat16")
+    _require(out_dtype in (torch.bfloat16, torch.float32), "out_dtype must be bfloat16 or float32")
+    M, K = A.shape
+    if b_is_nk:
+        N = B.shape[0]
+        _require(B.shape[1] == K, f"A is {tuple(A.shape)} but Bt is {tuple(B.shape)}")
+    else:
+        N = B.shape[1]
+        _require(B.shape[0] == K, f"A is {tuple(A.shape)} but B is {tuple(B.shape)}")
+    if out is None:
+        out = torch.empty((M, N), device=A.device, dtype=out_dtype)
+    _require(out.is_cuda and out.dtype == out_dtype and tuple(out.shape) == (M, N), "bad out tensor")
+    with torch.cuda.device(A.device):
+        check(lib.gemm_b200_gemm_bf16_cfg(
+            A.data_ptr(), B.data_ptr(), out.data_ptr(), M, N, K, _row_major_ld(A), _row_major_ld(B), _row_major_ld(out),
+            _lib.B_ROW_MAJOR_NK if b_is_nk else _lib.B_ROW_MAJOR_KN,
+            _lib.OUT_F32 if out_dtype == torch.float32 else _lib.OUT_BF16, config, _stream(A)))
+    return out
+
+
+def check_status(device: torch.device | None = None) -> None:
+    """Synchronises the current stream and raises if a bounded device-side wait gave up."""
+    dev = torch.device("cuda", torch.cuda.current_device()) if device is None else device
+    detail = (C.c_int32 * 4)()
+    with torch.cuda.device(dev):
+        check(lib.gemm_b200_check_status(torch.cuda.current_stream(dev).cuda_stream, detail))
+
+
+def sgemm_f32_host(A: torch.Tensor, B: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
+    """Host-buffer form: A, B, out are CPU tensors (pinned memory overlaps copies and compute)."""
+    _require(not A.is_cuda and not B.is_cuda, "host entry point takes CPU tensors")
+    _require(A.dtype == torch.float32 and B.dtype == torch.float32, "expected float32")
+    _require(A.is_contiguous() and B.is_contiguous(), "host operands must be contiguous")
+    M, K = A.shape
+    _require(B.shape[0] == K, "shape mismatch")
+    N = B.shape[1]
+    if out is None:
+        out = torch.empty((M, N), dtype=torch.float32)
+    _require(out.is_contiguous() and tuple(out.shape) == (M, N) and out.dtype == torch.float32, "bad out tensor")
+    check(lib.gemm_b200_sgemm_f32_host(A.data_ptr(), B.data_ptr(), out.data_ptr(), M, N, K))
+    return out
+
+
+def gemm_bf16_host(A: torch.Tensor, B: torch.Tensor, out: torch.Tensor | None = None, *, b_is_nk: bool = False,
+                   out_dtype: torch.dtype = torch.bfloat16) -> torch.Tensor:
+    _require(not A.is_cuda and not B.is_cuda, "host entry point takes CPU tensors")
+    _require(A.dtype == torch.bfloat16 and B.dtype == torch.bfloat16, "expected bfloat16")
+    _require(A.is_contiguous() and B.is_contiguous(), "host operands must be contiguous")
+    M, K = A.shape
+    N = B.shape[0] if b_is_nk else B.shape[1]
+    _require((B.shape[1] if b_is_nk else B.shape[0]) == K, "shape mismatch")
+    if out is None:
+        out = torch.empty((M, N), dtype=out_dtype)
+    _require(out.is_contiguous() and tuple(out.shape) == (M, N) and out.dtype == out_dtype, "bad out tensor")
+    check(lib.gemm_b200_gemm_bf16_host(A.data_ptr(), B.data_ptr(), out.data_ptr(), M, N, K,
+                                       _lib.B_ROW_MAJOR_NK if b_is_nk else _lib.B_ROW_MAJOR_KN,
+                                       _lib.OUT_F32 if out_dtype == torch.float32 else _lib.OUT_BF16))
+    return out
+
+
+def sgemm_f32_configs() -> list[str]:
+    return [lib.gemm_b200_sgemm_f32_config_name(i).decode() for i in range(lib.gemm_b200_sgemm_f32_num_configs())]
+
+
+def gemm_bf16_configs() -> list[str]:
+    return [lib.gemm_b200_gemm_bf16_config_name(i).decode() for i in range(lib.gemm_b200_gemm_bf16_num_configs())]
+
+
+def launch_count() -> int:
+    return int(lib.gemm_b200_launch_count())

@@ -1,0 +1,12 @@
+// PyTorch extension `naive_gemm_cuda`: drop-in for the reference wrapper naive/naive.cpp:6-26.
+// Exports naive_gemm(A, B, C) -> C (in place, same tensor returned) and matmul(A, B) -> C.
+#include "../shim_common.h"
+
+torch::Tensor naive_gemm_cuda(torch::Tensor A, torch::Tensor B, torch::Tensor C) {
+  return gemm_b200_shim::gemm_into(A, B, C);
+}
+
+PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
+  m.def("naive_gemm", &naive_gemm_cuda, "C = A @ B into C (gemm_b200 FP32 kernel)");
+  m.def("matmul", &gemm_b200_shim::matmul, "C = A @ B (allocates C)");
+}

@@ -1,0 +1,156 @@
+/*
+ * gemm_b200 — C-ABI of the B200 (sm_100a) GEMM library.
+ *
+ * Every entry point takes plain pointers and sizes; none takes a torch type.
+ * Unless a comment says otherwise all data pointers are DEVICE pointers on the
+ * current CUDA device, matrices are row-major, leading dimensions are counted
+ * in elements, and `stream` is a `cudaStream_t` passed as `void*` (NULL = the
+ * legacy default stream, which is what the reference launches on).
+ *
+ * Every function returns 0 on success or a negative GEMM_B200_ERR_* code;
+ * `gemm_b200_last_error()` then holds a human-readable reason for the calling
+ * thread.  Launches are asynchronous, like the reference's.
+ *
+ * The reference interface each entry point stands in for is cited by its path
+ * inside the danielvegamyhre/gemm project.
+ */
+#ifndef GEMM_B200_H_
+#define GEMM_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define GEMM_B200_VERSION 100
+
+/* status codes */
+#define GEMM_B200_OK                 0
+#define GEMM_B200_ERR_INVALID_ARG   -1  /* null pointer, negative size, ld too small       */
+#define GEMM_B200_ERR_ALIGNMENT     -2  /* pointer / leading dimension not aligned enough  */
+#define GEMM_B200_ERR_UNSUPPORTED   -3  /* device is not sm_100, or shape class not built  */
+#define GEMM_B200_ERR_CUDA          -4  /* a CUDA runtime / driver call failed             */
+#define GEMM_B200_ERR_TIMEOUT       -5  /* a bounded device-side wait ran out              */
+#define GEMM_B200_ERR_TOO_LARGE     -6  /* size exceeds a documented maximum               */
+
+/* element types of C for the tensor-core paths */
+#define GEMM_B200_OUT_BF16 0
+#define GEMM_B200_OUT_F32  1
+
+/* layout of the B operand for the tensor-core paths */
+#define GEMM_B200_B_ROW_MAJOR_KN 0   /* B[K,N], N contiguous: the reference's layout            */
+#define GEMM_B200_B_ROW_MAJOR_NK 1   /* B given as its transpose Bt[N,K], K contiguous          */
+
+/* -------------------------------------------------------------------------
+ * FP32 CUDA-core GEMM:  C[M,N] = A[M,K] @ B[K,N], beta = 0, C overwritten.
+ *
+ * Replaces, with one kernel family, all three reference launchers:
+ *   launch_naive_gemm(float*,float*,float*,int M,int N,int K)   naive/naive_1.cu:17-24
+ *   launch_gemm(float*,float*,float*,int M,int N,int K)         shared/shared_2.cu:59-66
+ *   launch_gemm(float*,float*,float*,int M,int N,int K)         blocktile_1d/blocktile_1d.cu:70-82
+ * Same semantics as those kernels: one FP32 accumulator per element of C,
+ * k strictly ascending, fused multiply-add, denormals flushed (the reference
+ * is built with --use_fast_math), so the result is bit-identical to theirs.
+ * Any M, N, K >= 0 is accepted (K == 0 writes zeros).  Addressing is 64-bit.
+ * ------------------------------------------------------------------------- */
+int gemm_b200_sgemm_f32(const float* A, const float* B, float* C,
+                        int64_t M, int64_t N, int64_t K,
+                        int64_t lda, int64_t ldb, int64_t ldc, void* stream);
+
+/* Same, with the tile configuration forced (tests and tuning sweeps).
+ * `config` indexes the table printed by gemm_b200_sgemm_f32_config_name();
+ * -1 = the library's heuristic. */
+int gemm_b200_sgemm_f32_cfg(const float* A, const float* B, float* C,
+                            int64_t M, int64_t N, int64_t K,
+                            int64_t lda, int64_t ldb, int64_t ldc,
+                            int config, void* stream);
+int gemm_b200_sgemm_f32_num_configs(void);
+const char* gemm_b200_sgemm_f32_config_name(int config);
+
+/* -------------------------------------------------------------------------
+ * BF16 tensor-core GEMM (tcgen05, FP32 accumulation in TMEM):
+ *   C[M,N] = A[M,K] @ B,  A bf16 row-major, C bf16 or f32 row-major.
+ * The reference has no BF16 path; this extends the same operator
+ * (naive/naive.cpp:6-22: M = A.size(0), K = A.size(1), N = B.size(1), C
+ * overwritten and returned) to BF16 operands.
+ * Requirements: pointers 16-byte aligned; lda, ldb (and ldc for bf16 output)
+ * multiples of 8 elements (ldc multiple of 4 for f32 output).
+ * ------------------------------------------------------------------------- */
+int gemm_b200_gemm_bf16(const void* A, const void* B, void* C,
+                        int64_t M, int64_t N, int64_t K,
+                        int64_t lda, int64_t ldb, int64_t ldc,
+                        int b_layout, int out_dtype, void* stream);
+
+/* Same with the kernel variant forced (-1 = heuristic). */
+int gemm_b200_gemm_bf16_cfg(const void* A, const void* B, void* C,
+                            int64_t M, int64_t N, int64_t K,
+                            int64_t lda, int64_t ldb, int64_t ldc,
+                            int b_layout, int out_dtype, int config, void* stream);
+int gemm_b200_gemm_bf16_num_configs(void);
+const char* gemm_b200_gemm_bf16_config_name(int config);
+
+/* -------------------------------------------------------------------------
+ * MXFP8 (OCP microscaling): e4m3 data with one UE8M0 scale per 32 consecutive
+ * K elements.  No counterpart in the reference; same operator semantics as
+ * above (naive/naive.cpp:6-22) on quantised operands.
+ *
+ * gemm_b200_quantize_mxfp8 quantises X (bf16) along K.
+ *   transposed_in = 0: X is [rows, K] row-major (ldx >= K)          -> used for A[M,K]
+ *   transposed_in = 1: X is [K, rows] row-major (ldx >= rows)       -> used for B[K,N]
+ * Outputs: Xq  e4m3 [rows, K] row-major, K contiguous (ld = K);
+ *          SF  UE8M0 bytes in the packed layout described by
+ *              gemm_b200_mxfp8_scale_offset() — gemm_b200_mxfp8_scale_bytes(rows, K) bytes.
+ * Recipe: per block amax -> e = floor(log2(amax)) - 8 (amax == 0 or a block
+ * of denormals -> e clamped to -127), scale byte = e + 127,
+ * q = saturate_e4m3(x * 2^-e) with round-to-nearest-even.  K % 32 == 0.
+ * ------------------------------------------------------------------------- */
+int gemm_b200_quantize_mxfp8(const void* X_bf16, int64_t rows, int64_t K, int64_t ldx,
+                             int transposed_in, void* Xq_e4m3, void* SF_ue8m0, void* stream);
+size_t gemm_b200_mxfp8_scale_bytes(int64_t rows, int64_t K);
+/* Byte offset of the scale of (row, K-block kb) inside the packed scale buffer. */
+size_t gemm_b200_mxfp8_scale_offset(int64_t rows, int64_t K, int64_t row, int64_t kb);
+
+/* C[M,N] = dequant(Aq,SFA)[M,K] @ dequant(Bq,SFB)[N,K]^T, FP32 accumulation. */
+int gemm_b200_gemm_mxfp8(const void* Aq, const void* SFA, const void* Bq, const void* SFB,
+                         void* C, int64_t M, int64_t N, int64_t K, int64_t ldc,
+                         int out_dtype, void* stream);
+int gemm_b200_gemm_mxfp8_cfg(const void* Aq, const void* SFA, const void* Bq, const void* SFB,
+                             void* C, int64_t M, int64_t N, int64_t K, int64_t ldc,
+                             int out_dtype, int config, void* stream);
+int gemm_b200_gemm_mxfp8_num_configs(void);
+const char* gemm_b200_gemm_mxfp8_config_name(int config);
+
+/* -------------------------------------------------------------------------
+ * Host-buffer entry points: the same operators on HOST pointers.  Each call
+ * copies the operands to a cached device workspace, launches, copies C back
+ * and synchronises before returning — what a caller holding host arrays sees
+ * end to end.  (The reference's wrapper, naive/naive.cpp:6-22, only accepts
+ * device tensors; its tests create them with device='cuda'.)
+ * ------------------------------------------------------------------------- */
+int gemm_b200_sgemm_f32_host(const float* hA, const float* hB, float* hC,
+                             int64_t M, int64_t N, int64_t K);
+int gemm_b200_gemm_bf16_host(const void* hA, const void* hB, void* hC,
+                             int64_t M, int64_t N, int64_t K, int b_layout, int out_dtype);
+/* Frees the cached workspace of the current device. */
+int gemm_b200_release_workspace(void);
+
+/* -------------------------------------------------------------------------
+ * Library state
+ * ------------------------------------------------------------------------- */
+/* Reads (and clears) the device-side status word that bounded waits write when
+ * they give up.  Synchronises `stream`.  0 = clean, GEMM_B200_ERR_TIMEOUT
+ * otherwise; `detail`, if not NULL, receives {code, block, role, stage}. */
+int gemm_b200_check_status(void* stream, int32_t detail[4]);
+const char* gemm_b200_last_error(void);
+int gemm_b200_version(void);
+/* 1 if device `dev` can run the tensor-core paths (compute capability 10.x). */
+int gemm_b200_device_supported(int dev);
+/* Number of kernels this library has launched in this process. */
+int64_t gemm_b200_launch_count(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* GEMM_B200_H_ */

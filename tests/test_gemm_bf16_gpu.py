@@ -1,0 +1,108 @@
+"""BF16 tensor-core parity on the GPU through the C-ABI (gemm_b200_gemm_bf16).
+
+Bar (stated BF16 tolerance): rtol = atol = 2e-2 against an FP32 matmul of the same BF16
+operands.  With FP32 output the kernel is also held to a much tighter bound, because only the
+summation order differs from the oracle."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+RTOL = ATOL = 2e-2
+
+
+def _check(ops, oracle, M, K, N, *, b_is_nk=False, out_dtype=torch.bfloat16, config=-1, seed=0):
+    A, B = oracle.gen_randn_bf16(M, K, N, seed=seed)
+    want = oracle.bf16_matmul_oracle(A, B)
+    Bdev = B.t().contiguous().cuda() if b_is_nk else B.cuda()
+    C = torch.full((M, N), float("nan"), device="cuda", dtype=out_dtype)
+    out = ops.gemm_bf16(A.cuda(), Bdev, C, b_is_nk=b_is_nk, out_dtype=out_dtype, config=config)
+    ops.check_status()
+    assert out.data_ptr() == C.data_ptr()
+    got = C.float().cpu()
+    torch.testing.assert_close(got, want, rtol=RTOL, atol=ATOL)
+    if out_dtype == torch.float32:
+        assert oracle.rel_frobenius(got, want) < 1e-5
+    else:
+        # within one BF16 rounding of the FP32 result
+        assert oracle.rel_frobenius(got, want) < 3e-3
+
+
+@pytest.mark.parametrize("shape", [(256, 256, 256), (512, 1024, 768), (1024, 4096, 1024)])
+@pytest.mark.parametrize("b_is_nk", [False, True])
+def test_square_and_rect(ops, oracle, shape, b_is_nk):
+    M, K, N = shape
+    _check(ops, oracle, M, K, N, b_is_nk=b_is_nk)
+
+
+@pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
+def test_every_config_both_layouts(ops, oracle, out_dtype):
+    for cfg, name in enumerate(ops.gemm_bf16_configs()):
+        for b_is_nk in (False, True):
+            _check(ops, oracle, 768, 640, 1280, b_is_nk=b_is_nk, out_dtype=out_dtype, config=cfg, seed=cfg)
+
+
+# ragged: M, N not multiples of the tile, K not a multiple of 64, single row, skinny
+EDGE = [(1, 64, 8), (16, 8192, 256), (100, 72, 40), (129, 136, 264), (255, 8, 520), (300, 200, 1000), (2000, 1000, 24)]
+
+
+@pytest.mark.parametrize("M,K,N", EDGE)
+@pytest.mark.parametrize("b_is_nk", [False, True])
+def test_edge_shapes(ops, oracle, M, K, N, b_is_nk):
+    for cfg in range(len(ops.gemm_bf16_configs())):
+        _check(ops, oracle, M, K, N, b_is_nk=b_is_nk, out_dtype=torch.float32, config=cfg, seed=M + N)
+
+
+def test_k_zero_and_empty(ops):
+    C = torch.full((8, 16), 3.0, device="cuda", dtype=torch.bfloat16)
+    ops.gemm_bf16(torch.empty(8, 0, device="cuda", dtype=torch.bfloat16),
+                  torch.empty(0, 16, device="cuda", dtype=torch.bfloat16), C)
+    assert torch.count_nonzero(C) == 0
+    ops.gemm_bf16(torch.empty(0, 8, device="cuda", dtype=torch.bfloat16),
+                  torch.empty(8, 16, device="cuda", dtype=torch.bfloat16))
+
+
+def test_canaries_around_c(ops, oracle):
+    M, K, N = 200, 128, 264
+    A, B = oracle.gen_randn_bf16(M, K, N, seed=5)
+    for cfg in range(len(ops.gemm_bf16_configs())):
+        Cbig = torch.full((M + 2, N + 16), -3.0, device="cuda", dtype=torch.bfloat16)
+        ops.gemm_bf16(A.cuda(), B.cuda(), Cbig[1:M + 1, 8:N + 8], config=cfg)
+        ops.check_status()
+        got = Cbig.float().cpu()
+        torch.testing.assert_close(got[1:M + 1, 8:N + 8], oracle.bf16_matmul_oracle(A, B), rtol=RTOL, atol=ATOL)
+        mask = torch.ones_like(got, dtype=torch.bool); mask[1:M + 1, 8:N + 8] = False
+        assert torch.all(got[mask] == -3.0)
+
+
+def test_deterministic(ops, oracle):
+    A, B = oracle.gen_randn_bf16(1024, 2048, 1024, seed=9)
+    a, b = A.cuda(), B.cuda()
+    c1 = ops.gemm_bf16(a, b).clone()
+    for _ in range(3):
+        assert torch.equal(ops.gemm_bf16(a, b), c1)
+
+
+def test_config3_shapes_sampled(ops, oracle):
+    # full benchmark sizes; the oracle is evaluated on a sample of rows (first/last tile rows included)
+    for (M, K, N) in [(8192, 8192, 8192), (8192, 16384, 4096)]:
+        g = torch.Generator(device="cuda").manual_seed(0)
+        A = torch.randn(M, K, device="cuda", generator=g).bfloat16()
+        B = torch.randn(K, N, device="cuda", generator=g).bfloat16()
+        C = ops.gemm_bf16(A, B)
+        ops.check_status()
+        rows = torch.tensor([0, 1, 127, 128, 255, 256, 4095, 4096, M - 129, M - 128, M - 1])
+        want = torch.matmul(A[rows].float().cpu(), B.float().cpu())
+        torch.testing.assert_close(C[rows].float().cpu(), want, rtol=RTOL, atol=ATOL)
+        # linearity in A (exact: scaling by 2 commutes with every rounding step)
+        C2 = ops.gemm_bf16(A * 2, B)
+        assert torch.equal(C2.float(), C.float() * 2)
+
+
+def test_alignment_errors(ops):
+    import gemm_b200._lib as L
+    A = torch.zeros(16, 20, device="cuda", dtype=torch.bfloat16)      # lda = 20, not a multiple of 8
+    B = torch.zeros(20, 16, device="cuda", dtype=torch.bfloat16)
+    with pytest.raises(L.GemmB200Error) as e:
+        ops.gemm_bf16(A, B)
+    assert e.value.code == L.ERR_ALIGNMENT
