@@ -1,0 +1,387 @@
+#!/usr/bin/env python
+"""Benchmark of the GEMM hot path.  `python bench.py --gpus N --steps K --warmup W` prints ONE
+JSON line on rank 0.
+
+Workload (default): the row-sharded BF16 GEMM  C[M,N] = A[M,K] @ B[K,N],  M = 131072,
+K = N = 8192, FP32 accumulation, bf16 output.  A is made of 8 fixed row blocks (seed 1000 + b)
+so it is identical for any rank count; rank r of N owns 8/N consecutive blocks, B (seed 0) is
+broadcast once from rank 0 before the timed region and C stays sharded, so the timed loop holds
+no collective.  A "step" is one pass of the GEMM over every rank's shard.
+
+* value       whole-job TFLOP/s = 2 M N K / (max over ranks of the device time per step), with
+              operands resident in HBM (CUDA events on the launching stream).
+* e2e         the same metric through the host-buffer C-ABI call (gemm_b200_gemm_bf16_host):
+              operands start in pinned host memory and C ends there, copies inside the timing.
+* roofline    achieved 2MNK/t of the GEMM kernel against the measured cuBLAS bf16 peak.
+* cpu_baseline  the reference's oracle (torch.matmul on the host cores) on a bounded slice.
+* per_dtype   (N = 1 only) the other benchmark configurations, each timed alone.
+
+`--impl reference` times the reference's CPU-side computation instead (torch.matmul on all host
+cores; the reference has no CPU kernels of its own, naive/test.py:23 is its check)."""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+WORKLOADS = {
+    # name: (M, K, N) of the whole job
+    "bf16_rowsharded_131072x8192x8192": (131072, 8192, 8192),
+    "bf16_8192": (8192, 8192, 8192),
+}
+DEFAULT_WORKLOAD = "bf16_rowsharded_131072x8192x8192"
+L2_BYTES = 126 * 1024 * 1024
+
+
+def measured_peaks() -> dict:
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        try:
+            return json.loads(p.read_text())
+        except Exception:
+            pass
+    return {}
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+              "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.gpu = gpu_index
+        self.proc = None
+        self.lines: list[str] = []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--id={self.gpu}", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
+                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except Exception:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=2)
+        except Exception:
+            self.proc.kill()
+        sm, smax, reasons, power = [], [], set(), []
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for ln in self.lines:
+            parts = [p.strip() for p in ln.split(",")]
+            if len(parts) < 9:
+                continue
+            try:
+                sm.append(float(parts[1])); smax.append(float(parts[2])); power.append(float(parts[3]))
+            except ValueError:
+                continue
+            for name, val in zip(names, parts[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        sm.sort()
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": max(smax) if smax else None,
+                "power_w_max": max(power) if power else None, "samples": len(sm), "reasons": sorted(reasons)}
+
+
+def dist_setup(n_gpus: int):
+    import torch
+    import torch.distributed as dist
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if world > 1:
+        torch.cuda.set_device(local)
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    else:
+        torch.cuda.set_device(0)
+    if world != n_gpus:
+        raise SystemExit(f"--gpus {n_gpus} but WORLD_SIZE={world}: launch with torch.distributed.run --nproc-per-node {n_gpus}")
+    return rank, world, local
+
+
+def barrier(world):
+    import torch
+    import torch.distributed as dist
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+
+
+def time_steps(fn, steps: int, warmup: int, world: int):
+    """(device time in s of exactly `steps` calls, max over ranks; kernels this rank launched in that region)."""
+    import torch
+    from gemm_b200 import sharded
+    import gemm_b200.ops as ops
+    for _ in range(warmup):
+        fn()
+    barrier(world)
+    n0 = ops.launch_count()
+    e0 = torch.cuda.Event(enable_timing=True)
+    e1 = torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    launches = ops.launch_count() - n0
+    secs = e0.elapsed_time(e1) / 1e3
+    total = sharded.max_over_ranks(secs, device=torch.device("cuda", torch.cuda.current_device()))
+    barrier(world)
+    return total, launches
+
+
+def time_alone(fn, reps: int = 10, warmup: int = 3) -> float:
+    """Median device time (s) of single launches, L2 flushed before each."""
+    import torch
+    flush = torch.empty(2 * L2_BYTES, dtype=torch.uint8, device="cuda")
+    for _ in range(warmup):
+        fn()
+    ts = []
+    for _ in range(reps):
+        flush.zero_()
+        e0 = torch.cuda.Event(enable_timing=True)
+        e1 = torch.cuda.Event(enable_timing=True)
+        e0.record()
+        fn()
+        e1.record()
+        torch.cuda.synchronize()
+        ts.append(e0.elapsed_time(e1) / 1e3)
+    ts.sort()
+    return ts[len(ts) // 2]
+
+
+def per_dtype_table(peaks: dict) -> dict:
+    """The other benchmark configurations at N = 1, each kernel timed alone (median, L2 flushed)."""
+    import torch
+    import gemm_b200.ops as ops
+    out = {}
+    sm_max = float(peaks.get("sm_max_mhz", 1965.0))
+    sms = torch.cuda.get_device_properties(0).multi_processor_count
+    f32_peak = sms * 128 * 2 * sm_max * 1e6 / 1e12
+    g = torch.Generator(device="cuda").manual_seed(0)
+    for n in (1024, 4096):
+        A = torch.rand(n, n, device="cuda", generator=g) * 2 - 1
+        B = torch.rand(n, n, device="cuda", generator=g) * 2 - 1
+        C = torch.empty(n, n, device="cuda")
+        t = time_alone(lambda: ops.sgemm_f32(A, B, C))
+        tf = 2 * n ** 3 / t / 1e12
+        out[f"fp32_{n}"] = {"tflops": round(tf, 2), "frac_of_simt_peak": round(tf / f32_peak, 4),
+                            "simt_peak_tflops": round(f32_peak, 1)}
+    for (M, K, N) in ((8192, 8192, 8192), (8192, 16384, 4096)):
+        A = torch.randn(M, K, device="cuda", generator=g).bfloat16()
+        B = torch.randn(K, N, device="cuda", generator=g).bfloat16()
+        C = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
+        t = time_alone(lambda: ops.gemm_bf16(A, B, C))
+        tf = 2 * M * N * K / t / 1e12
+        out[f"bf16_{M}x{K}x{N}"] = {"tflops": round(tf, 1), "frac_of_nominal_2250": round(tf / 2250.0, 4),
+                                    "frac_of_measured_burst": round(tf / float(peaks.get("bf16_tflops", 1590.0)), 4)}
+    if hasattr(ops, "gemm_mxfp8") and ops.gemm_mxfp8_configs():
+        for (M, K, N) in ((16384, 8192, 28672), (16, 8192, 28672)):
+            A = torch.randn(M, K, device="cuda", generator=g).bfloat16()
+            B = torch.randn(K, N, device="cuda", generator=g).bfloat16()
+            Aq = ops.quantize_mxfp8(A)
+            Bq = ops.quantize_mxfp8(B, transposed_in=True)
+            del A, B
+            C = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
+            t = time_alone(lambda: ops.gemm_mxfp8(Aq, Bq, C))
+            tf = 2 * M * N * K / t / 1e12
+            bytes_ = M * K + N * K + (M + N) * K // 32 + 2 * M * N
+            out[f"mxfp8_{M}x{K}x{N}"] = {"tflops": round(tf, 1), "frac_of_nominal_4500": round(tf / 4500.0, 4),
+                                         "gbps": round(bytes_ / t / 1e9, 1),
+                                         "frac_of_measured_hbm": round(bytes_ / t / 1e9 / float(peaks.get("hbm_gbs", 6650.0)), 4)}
+            del Aq, Bq, C
+    return out
+
+
+def cpu_baseline(M: int, K: int, N: int, budget_s: float = 15.0) -> dict:
+    """torch.matmul on the host cores over a bounded row slice of the same workload (the oracle:
+    FP32 matmul of the same BF16 operands)."""
+    import torch
+    from oracle import oracle as O
+    g = torch.Generator().manual_seed(0)
+    B = torch.randn(K, N, generator=g).bfloat16()
+    rows = 256
+    A = torch.randn(rows, K, generator=g).bfloat16()
+    O.bf16_matmul_oracle(A, B)                       # warm-up
+    t0 = time.perf_counter(); O.bf16_matmul_oracle(A, B); dt = time.perf_counter() - t0
+    rows = int(min(M, max(256, (budget_s / max(dt, 1e-4)) * 256 // 256 * 256)))
+    rows = min(rows, 16384)
+    A = torch.randn(rows, K, generator=g).bfloat16()
+    t0 = time.perf_counter(); O.bf16_matmul_oracle(A, B); dt = time.perf_counter() - t0
+    return {"value": round(2 * rows * N * K / dt / 1e12, 4), "unit": "TFLOP/s", "cores": O.cpu_threads(),
+            "kind": "port", "sample": f"torch.matmul (FP32 of the bf16 operands) on the first {rows} of {M} rows, "
+                                      f"{dt:.2f} s, os.cpu_count()={os.cpu_count()}"}
+
+
+def run_reference_arm(args) -> int:
+    """The reference's computation on the host cores (rank 0 only)."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return 0
+    import torch
+    from oracle import oracle as O
+    M, K, N = WORKLOADS[args.workload]
+    g = torch.Generator().manual_seed(0)
+    B = torch.randn(K, N, generator=g).bfloat16()
+    rows = 256
+    A = torch.randn(rows, K, generator=g).bfloat16()
+    O.bf16_matmul_oracle(A, B)
+    t0 = time.perf_counter(); O.bf16_matmul_oracle(A, B); dt = time.perf_counter() - t0
+    # each step ~ 60 s / (steps + warmup) of CPU work
+    per_step = 60.0 / max(1, args.steps + args.warmup)
+    rows = int(max(256, min(M, (per_step / max(dt, 1e-4)) * 256 // 256 * 256)))
+    A = torch.randn(rows, K, generator=g).bfloat16()
+    for _ in range(args.warmup):
+        O.bf16_matmul_oracle(A, B)
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        O.bf16_matmul_oracle(A, B)
+    dt = (time.perf_counter() - t0) / max(1, args.steps)
+    tf = 2 * rows * N * K / dt / 1e12
+    sample = f"torch.matmul on host cores, {rows} of {M} rows per step"
+    line = {
+        "impl": "reference", "metric": "tflops", "value": round(tf, 4), "unit": "TFLOP/s", "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(dt * 1e3, 3), "higher_is_better": True,
+        "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": args.workload, "M": M, "K": K, "N": N, "rows_per_step": rows},
+        "cpu_baseline": {"value": round(tf, 4), "unit": "TFLOP/s", "cores": O.cpu_threads(), "kind": "port", "sample": sample},
+        "e2e": {"value": round(tf, 4), "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+    return 0
+
+
+def main() -> int:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="gemm_b200", choices=["gemm_b200", "reference"])
+    ap.add_argument("--workload", default=DEFAULT_WORKLOAD, choices=sorted(WORKLOADS))
+    ap.add_argument("--no-extras", action="store_true", help="skip per_dtype, cpu_baseline and e2e (profiling runs)")
+    ap.add_argument("--e2e-steps", type=int, default=3)
+    args = ap.parse_args()
+    if args.impl == "reference":
+        return run_reference_arm(args)
+
+    import torch
+    import gemm_b200.ops as ops        # raises if the CUDA library is missing: there is no fallback
+    from gemm_b200 import sharded
+
+    rank, world, local = dist_setup(args.gpus)
+    dev = torch.device("cuda", local)
+    peaks = measured_peaks()
+    M, K, N = WORKLOADS[args.workload]
+    shard = sharded.shard_rows(M, world, rank)
+    rows_per_block = M // sharded.BLOCKS
+
+    # operands: A shard generated block by block on the device, B on rank 0 then broadcast
+    A = torch.empty(shard.rows, K, device=dev, dtype=torch.bfloat16)
+    for i, b in enumerate(shard.blocks):
+        A[i * rows_per_block:(i + 1) * rows_per_block] = sharded.gen_a_block_cuda(b, rows_per_block, K, dev)
+    B = sharded.gen_b_cuda(K, N, dev) if rank == 0 else torch.empty(K, N, device=dev, dtype=torch.bfloat16)
+    sharded.broadcast_b(B, src=0)
+    C = torch.empty(shard.rows, N, device=dev, dtype=torch.bfloat16)
+
+    def step():
+        ops.gemm_bf16(A, B, C)
+
+    # correctness guard before timing: a few rows against the FP32 product of the same operands
+    step()
+    ops.check_status()
+    probe = torch.tensor([0, shard.rows // 2 + 1, shard.rows - 1], device=dev)
+    want = torch.matmul(A[probe].float(), B.float())
+    torch.testing.assert_close(C[probe].float(), want, rtol=2e-2, atol=2e-2)
+
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    secs, launches = time_steps(step, args.steps, max(args.warmup, 3), world)
+    launches = int(sharded.sum_over_ranks(float(launches), device=dev))
+    clocks = sampler.stop() if rank == 0 else {}
+    ops.check_status()
+    per_step = secs / args.steps
+    flops = 2.0 * M * N * K
+    value = flops / per_step / 1e12
+
+    # roofline of the GEMM kernel: one launch per rank per step, algorithmic flops of the rank's shard
+    kernel_tflops = 2.0 * shard.rows * N * K / per_step / 1e12
+    long_run = secs >= 1.0
+    peak = float(peaks.get("bf16_tflops_sustained" if long_run else "bf16_tflops", 1400.0 if long_run else 1590.0))
+    roofline = {"bound": "tensor", "achieved": round(kernel_tflops, 1), "peak": peak, "unit": "TFLOP/s",
+                "frac": round(kernel_tflops / peak, 4), "traffic": None,
+                "peak_kind": ("measured sustained" if long_run else "measured burst") if peaks else "fallback",
+                "frac_of_nominal_2250": round(kernel_tflops / 2250.0, 4)}
+
+    e2e = None
+    cpu = None
+    extra = None
+    if not args.no_extras:
+        # end to end: pinned host operands -> C in pinned host memory, through the host-buffer C-ABI call
+        hA = torch.empty(shard.rows, K, dtype=torch.bfloat16, pin_memory=True); hA.copy_(A)
+        hB = torch.empty(K, N, dtype=torch.bfloat16, pin_memory=True); hB.copy_(B)
+        hC = torch.empty(shard.rows, N, dtype=torch.bfloat16, pin_memory=True)
+        ops.gemm_bf16_host(hA, hB, hC)
+        barrier(world)
+        t0 = time.perf_counter()
+        for _ in range(args.e2e_steps):
+            ops.gemm_bf16_host(hA, hB, hC)
+        dt = (time.perf_counter() - t0) / args.e2e_steps
+        dt = sharded.max_over_ranks(dt, device=dev)
+        torch.testing.assert_close(hC[:2].float(), torch.matmul(hA[:2].float(), hB.float()), rtol=2e-2, atol=2e-2)
+        e2e = {"value": round(flops / dt / 1e12, 2), "unit": "TFLOP/s",
+               "h2d_bytes_per_step": int(world * (hB.numel() * 2) + M * K * 2), "d2h_bytes_per_step": int(M * N * 2),
+               "ms_per_step": round(dt * 1e3, 2)}
+        del hA, hB, hC
+        if rank == 0 and world == 1:
+            cpu = cpu_baseline(M, K, N)
+            del A, C
+            torch.cuda.empty_cache()
+            extra = per_dtype_table(peaks)
+
+    if rank == 0:
+        line = {
+            "metric": "tflops", "value": round(value, 1), "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": round(per_step * 1e3, 4), "higher_is_better": True,
+            "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": args.workload, "M": M, "K": K, "N": N, "rows_per_rank": shard.rows,
+                       "parallelism": f"rows{world}", "l2": "inputs larger than L2 (A shard %.0f MiB)" % (shard.rows * K * 2 / 2 ** 20),
+                       "out": "bf16", "accumulate": "fp32"},
+            "roofline": roofline, "clocks": clocks, "gpu_launches": int(launches),
+        }
+        if e2e is not None:
+            line["e2e"] = e2e
+        if cpu is not None:
+            line["cpu_baseline"] = cpu
+        if extra is not None:
+            line["per_dtype"] = extra
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        import torch.distributed as dist
+        dist.destroy_process_group()
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -1,0 +1,265 @@
+// MXFP8 block-scaled GEMM on the sm_100a tensor cores:
+//   C[M,N] = (Aq * SFA)[M,K] @ (Bq * SFB)[N,K]^T,  e4m3 data, one UE8M0 scale per 32 k,
+//   FP32 accumulation in TMEM, bf16 or f32 output.
+//
+// Same operator as the reference's C = A @ B (naive/naive.cpp:6-22, kernels
+// naive/naive_1.cu:5-15, shared/shared_2.cu:4-57, blocktile_1d/blocktile_1d.cu:5-68) on
+// microscaled operands, which the reference does not have.
+//
+// Persistent, warp-specialised, 320 threads:
+//   warp 0      TMA producer: A and B tiles (128 rows x 128 bytes, 128B swizzle) and the packed
+//               scale chunks of the same K range (512 bytes per 128 rows) into a smem ring;
+//   warp 1      owns TMEM; one thread copies the scales smem -> TMEM (tcgen05.cp) and issues
+//               tcgen05.mma kind::mxf8f6f4.block_scale (K = 32 per instruction);
+//   warps 2-9   epilogue: each warp pulls 32 rows x 128 columns of the accumulator into
+//               registers, releases the accumulator at once, then converts and stores.
+// The 256-column accumulator plus the scale columns do not fit twice in the 512 TMEM columns,
+// so the accumulator is single-buffered; draining it to registers first keeps the tensor pipe
+// idle only for the TMEM read, not for the global stores.
+// With CG = 2 a CTA pair shares a 256 x 256 tile; every CTA loads the scales of all 256 columns
+// of B because each SM applies them locally.  No load uses cluster multicast.
+#pragma once
+#include <cuda_bf16.h>
+#include "common.cuh"
+#include "tc_common.cuh"
+#include "gemm_bf16.cuh"
+
+namespace gemm_b200 {
+namespace tc {
+
+constexpr int kMxBlockK = 128;     // e4m3 elements per 128-byte swizzled row = 4 scale blocks
+constexpr int kMxUmmaK = 32;
+constexpr int kMxThreads = 320;
+constexpr int kMxSfaCol = 256;     // TMEM columns [256, 260): scales of A
+constexpr int kMxSfbCol = 260;     // TMEM columns [260, 268): scales of B (256 columns of C)
+
+template <int CG_, int STAGES_, bool COMMIT_MASK_>
+struct MxCfg {
+  static constexpr int CG = CG_, STAGES = STAGES_;
+  static constexpr bool COMMIT_MASK = COMMIT_MASK_;
+  static constexpr int BN_CTA = kBlockN / CG;
+  static constexpr int A_BYTES = kBlockM * kMxBlockK;       // 16 KB
+  static constexpr int B_BYTES = BN_CTA * kMxBlockK;        // 32 KB / 16 KB
+  static constexpr int SFA_BYTES = 512;
+  static constexpr int SFB_BYTES = 1024;                    // 256 columns of C
+  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES + SFA_BYTES + SFB_BYTES;
+  static constexpr int BAR_BYTES = (2 * STAGES + 2) * 8 + 16;
+  static constexpr int SMEM_BYTES = 1024 + STAGES * STAGE_BYTES + BAR_BYTES;
+  static_assert(SMEM_BYTES <= 232448, "shared memory budget");
+};
+
+template <class Cfg, bool OUT_F32>
+__global__ void __launch_bounds__(kMxThreads, 1)
+gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                  const __grid_constant__ CUtensorMap tmSFA, const __grid_constant__ CUtensorMap tmSFB,
+                  void* __restrict__ Cptr, int64_t ldc, const GemmShape shape) {
+  constexpr int CG = Cfg::CG, STAGES = Cfg::STAGES;
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  const uint32_t sA0 = smem_base;
+  const uint32_t sB0 = sA0 + STAGES * Cfg::A_BYTES;
+  const uint32_t sSFA0 = sB0 + STAGES * Cfg::B_BYTES;
+  const uint32_t sSFB0 = sSFA0 + STAGES * Cfg::SFA_BYTES;
+  const uint32_t bar0 = sSFB0 + STAGES * Cfg::SFB_BYTES;
+  auto full_bar = [&](int s) { return bar0 + 8u * s; };
+  auto empty_bar = [&](int s) { return bar0 + 8u * (STAGES + s); };
+  const uint32_t tfull_bar = bar0 + 8u * (2 * STAGES);
+  const uint32_t tempty_bar = bar0 + 8u * (2 * STAGES + 1);
+  const uint32_t tmem_slot = bar0 + 8u * (2 * STAGES + 2);
+
+  const int warp = __shfl_sync(0xffffffffu, (int)(threadIdx.x >> 5), 0);
+  const int lane = threadIdx.x & 31;
+  const uint32_t cta_rank = (CG == 2) ? cluster_ctarank() : 0u;
+  const int cluster_id = blockIdx.x / CG;
+  const int num_clusters = gridDim.x / CG;
+  const int num_tiles = shape.tiles_m * shape.tiles_n;
+  const int num_kb = (shape.K + kMxBlockK - 1) / kMxBlockK;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(full_bar(s), 1);
+      mbar_init(empty_bar(s), 1);
+    }
+    mbar_init(tfull_bar, 1);
+    mbar_init(tempty_bar, 8 * CG);   // one arrival per epilogue warp of every CTA of the pair
+    fence_mbar_init();
+  }
+  if (warp == 0 && lane == 0) {
+    prefetch_tensormap(&tmA);
+    prefetch_tensormap(&tmB);
+    prefetch_tensormap(&tmSFA);
+    prefetch_tensormap(&tmSFB);
+  }
+  if (warp == 1) {
+    tmem_alloc<CG>(tmem_slot, kTmemCols);
+    tmem_relinquish<CG>();
+    tc_fence_before_sync();
+  }
+  __syncthreads();
+  if (CG == 2) {
+    cluster_arrive();
+    cluster_wait();
+  }
+  tc_fence_after_sync();
+  uint32_t tmem_base;
+  asm volatile("ld.shared.u32 %0, [%1];" : "=r"(tmem_base) : "r"(tmem_slot) : "memory");
+
+  bool failed = false;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      uint32_t it = 0;
+      for (int t = cluster_id; t < num_tiles && !failed; t += num_clusters) {
+        int tm, tn;
+        tile_coord(t, shape.tiles_m, shape.tiles_n, tm, tn);
+        const int mblk = tm * CG + (int)cta_rank;            // 128-row block of A / C
+        const int m0 = mblk * kBlockM;
+        const int n0 = tn * kBlockN + (int)cta_rank * Cfg::BN_CTA;
+        for (int kb = 0; kb < num_kb; ++kb, ++it) {
+          const int s = it % STAGES;
+          const uint32_t ph = (it / STAGES) & 1u;
+          if (!mbar_wait(empty_bar(s), ph ^ 1u, kRoleProducer, s)) { failed = true; break; }
+          const uint32_t a_dst = sA0 + s * Cfg::A_BYTES, b_dst = sB0 + s * Cfg::B_BYTES;
+          const uint32_t sfa_dst = sSFA0 + s * Cfg::SFA_BYTES, sfb_dst = sSFB0 + s * Cfg::SFB_BYTES;
+          // scale maps: 32-bit elements, row = 128-row block, 128 elements (512 bytes) per K chunk
+          if constexpr (CG == 1) {
+            mbar_arrive_expect_tx(full_bar(s), Cfg::STAGE_BYTES);
+            tma_load_2d(a_dst, &tmA, kb * kMxBlockK, m0, full_bar(s));
+            tma_load_2d(b_dst, &tmB, kb * kMxBlockK, n0, full_bar(s));
+            tma_load_2d(sfa_dst, &tmSFA, kb * 128, mblk, full_bar(s));
+            tma_load_2d(sfb_dst, &tmSFB, kb * 128, tn * 2, full_bar(s));
+          } else {
+            const uint32_t lead_full = map_to_cta(full_bar(s), 0);
+            if (cta_rank == 0) mbar_arrive_expect_tx(full_bar(s), 2 * Cfg::STAGE_BYTES);
+            tma_load_2d_pair(a_dst, &tmA, kb * kMxBlockK, m0, lead_full);
+            tma_load_2d_pair(b_dst, &tmB, kb * kMxBlockK, n0, lead_full);
+            tma_load_2d_pair(sfa_dst, &tmSFA, kb * 128, mblk, lead_full);
+            tma_load_2d_pair(sfb_dst, &tmSFB, kb * 128, tn * 2, lead_full);
+          }
+        }
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer (leader CTA)
+    if (lane == 0 && cta_rank == 0) {
+      constexpr uint64_t ab_hi = make_smem_desc_hi(16, 1024, kLayoutSw128);
+      // scale chunk: 32 rows x 16 bytes, unswizzled, 8-row groups 128 bytes apart
+      constexpr uint64_t sf_hi = make_smem_desc_hi(16, 128, kLayoutNone);
+      auto commit = [&](uint32_t bar) {
+        if constexpr (CG == 1) {
+          mma_commit_local(bar);
+        } else if constexpr (Cfg::COMMIT_MASK) {
+          mma_commit_pair_mask(bar, (uint16_t)3);
+        } else {
+          mma_commit_pair(map_to_cta(bar, 0));
+          mma_commit_pair(map_to_cta(bar, 1));
+        }
+      };
+      const uint32_t d_tmem = tmem_base;
+      const uint32_t sfa_tmem = tmem_base + kMxSfaCol, sfb_tmem = tmem_base + kMxSfbCol;
+      uint32_t it = 0, acc_it = 0;
+      for (int t = cluster_id; t < num_tiles && !failed; t += num_clusters, ++acc_it) {
+        if (!mbar_wait(tempty_bar, (acc_it & 1u) ^ 1u, kRoleMma, 100)) { failed = true; break; }
+        tc_fence_after_sync();
+        for (int kb = 0; kb < num_kb; ++kb, ++it) {
+          const int s = it % STAGES;
+          const uint32_t ph = (it / STAGES) & 1u;
+          if (!mbar_wait(full_bar(s), ph, kRoleMma, s)) { failed = true; break; }
+          tc_fence_after_sync();
+          const uint32_t a_addr = sA0 + s * Cfg::A_BYTES, b_addr = sB0 + s * Cfg::B_BYTES;
+          const uint32_t sfa_addr = sSFA0 + s * Cfg::SFA_BYTES, sfb_addr = sSFB0 + s * Cfg::SFB_BYTES;
+          tmem_cp_32x128b_warpx4<CG>(sfa_tmem, smem_desc(sf_hi, sfa_addr));
+          tmem_cp_32x128b_warpx4<CG>(sfb_tmem, smem_desc(sf_hi, sfb_addr));
+          tmem_cp_32x128b_warpx4<CG>(sfb_tmem + 4, smem_desc(sf_hi, sfb_addr + 512));
+#pragma unroll
+          for (int k = 0; k < kMxBlockK / kMxUmmaK; ++k) {
+            // byte k of every 32-bit scale column belongs to this 32-wide K slice
+            const uint32_t idesc = make_idesc_mxf8(kBlockM * CG, kBlockN, k, k);
+            mma_mxf8<CG>(d_tmem, smem_desc(ab_hi, a_addr + k * kMxUmmaK), smem_desc(ab_hi, b_addr + k * kMxUmmaK), idesc,
+                         sfa_tmem + ((uint32_t)k << 30), sfb_tmem + ((uint32_t)k << 30), (kb | k) != 0 ? 1u : 0u);
+          }
+          commit(empty_bar(s));
+        }
+        if (failed) break;
+        commit(tfull_bar);
+      }
+    }
+    __syncwarp();
+  } else {
+    // ------------------------------------------------------------------ epilogue warps 2..9
+    const int quad = warp & 3;             // TMEM lanes [32 quad, 32 quad + 32)
+    const int half = (warp - 2) >> 2;      // columns [128 half, 128 half + 128)
+    const uint32_t t_addr = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(half * 128);
+    uint32_t acc_it = 0;
+    for (int t = cluster_id; t < num_tiles && !failed; t += num_clusters, ++acc_it) {
+      int tm, tn;
+      tile_coord(t, shape.tiles_m, shape.tiles_n, tm, tn);
+      const int row = (tm * CG + (int)cta_rank) * kBlockM + quad * 32 + lane;
+      const int col0 = tn * kBlockN + half * 128;
+      const bool ready = mbar_wait(tfull_bar, acc_it & 1u, kRoleEpilogue, 200);
+      if (!__all_sync(0xffffffffu, ready)) { failed = true; break; }
+      tc_fence_after_sync();
+      uint32_t v[4][32];
+#pragma unroll
+      for (int c = 0; c < 4; ++c) tmem_ld_32x32b_x32(t_addr + c * 32, v[c]);
+      tmem_ld_wait();
+      // accumulator is in registers: the next tile's MMAs may overwrite it
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) {
+        if constexpr (CG == 1) mbar_arrive(tempty_bar);
+        else mbar_arrive_cluster(map_to_cta(tempty_bar, 0));
+      }
+      if (row < shape.M) {
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          const int col = col0 + c * 32;
+          if constexpr (OUT_F32) {
+            float* dst = reinterpret_cast<float*>(Cptr) + (int64_t)row * ldc + col;
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+              if (col + 4 * j < shape.N)
+                *reinterpret_cast<uint4*>(dst + 4 * j) =
+                    make_uint4(v[c][4 * j], v[c][4 * j + 1], v[c][4 * j + 2], v[c][4 * j + 3]);
+          } else {
+            __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(Cptr) + (int64_t)row * ldc + col;
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              if (col + 8 * j < shape.N) {
+                uint32_t p[4];
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                  __nv_bfloat162 h = __floats2bfloat162_rn(__uint_as_float(v[c][8 * j + 2 * e]),
+                                                           __uint_as_float(v[c][8 * j + 2 * e + 1]));
+                  p[e] = *reinterpret_cast<uint32_t*>(&h);
+                }
+                *reinterpret_cast<uint4*>(dst + 8 * j) = make_uint4(p[0], p[1], p[2], p[3]);
+              }
+            }
+          }
+        }
+      }
+    }
+  }
+
+  // ------------------------------------------------------------------ teardown
+  if (failed || aborted()) {
+    const unsigned long long t0 = globaltimer_ns();
+    while (globaltimer_ns() - t0 < 200000ull) __nanosleep(1000);
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  if (CG == 2) {
+    cluster_arrive();
+    cluster_wait();
+  }
+  if (warp == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc<CG>(tmem_base, kTmemCols);
+  }
+}
+
+}  // namespace tc
+}  // namespace gemm_b200

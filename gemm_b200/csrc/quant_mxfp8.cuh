@@ -1,0 +1,117 @@
+// MXFP8 quantiser: bf16 -> e4m3 data + one UE8M0 scale per 32 consecutive K elements.
+//
+// No counterpart in the reference (its kernels are FP32 only: naive/naive_1.cu:5-15); this is
+// the operand format of the block-scaled tensor-core GEMM in this library.
+//
+// Recipe per block of 32:  amax = max |x|;  scale byte = max(biased_exponent(amax) - 8, 0),
+// i.e. scale = 2^(floor(log2 amax) - 8) clamped at 2^-127;  q = e4m3(x * 2^(127 - byte)) with
+// round-to-nearest-even and saturation at +-448.  A zero block gets byte 0 and zero data.
+//
+// Scales are written in the layout the GEMM copies straight into tensor memory: 512-byte chunks
+// holding 128 rows x 4 K-blocks as 32 x 16 bytes,
+//     offset(r, kb) = ((r / 128) * ceil(KB / 4) + kb / 4) * 512 + (r % 32) * 16 + ((r / 32) % 4) * 4 + kb % 4,
+// chunks ordered [row block][K chunk]; padding bytes (rows >= rows, kb >= KB) are written as 0.
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_fp8.h>
+#include "common.cuh"
+
+namespace gemm_b200 {
+namespace mx {
+
+__host__ __device__ inline size_t scale_offset(int64_t kchunks, int64_t r, int64_t kb) {
+  return (size_t)((r / 128) * kchunks + kb / 4) * 512 + (size_t)((r % 32) * 16 + ((r / 32) % 4) * 4 + (kb % 4));
+}
+
+__device__ __forceinline__ uint32_t pack4_e4m3(float a, float b, float c, float d) {
+  // cvt.rn.satfinite.e4m3x2.f32 d, hi, lo : low byte = lo
+  uint16_t lo, hi;
+  asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(lo) : "f"(b), "f"(a));
+  asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(hi) : "f"(d), "f"(c));
+  return (uint32_t)lo | ((uint32_t)hi << 16);
+}
+
+__device__ __forceinline__ float bf16_bits_to_float(uint32_t b16) { return __uint_as_float(b16 << 16); }
+
+// quantise 32 values held as 16 packed bf16x2 words; returns the scale byte, writes 8 words of e4m3
+__device__ __forceinline__ uint32_t quantise_block(const uint32_t (&w)[16], uint32_t (&q)[8]) {
+  uint32_t amax_bits = 0;
+#pragma unroll
+  for (int i = 0; i < 16; ++i) {
+    // |x| as FP32 bits compares like an unsigned integer
+    const uint32_t lo = (w[i] << 16) & 0x7fffffffu, hi = w[i] & 0x7fff0000u;
+    amax_bits = max(amax_bits, max(lo, hi));
+  }
+  const int eb = (int)(amax_bits >> 23);                 // biased exponent of amax (0 for 0 / denormals)
+  const uint32_t byte = (uint32_t)max(eb - 8, 0);
+  const float inv = __uint_as_float((uint32_t)(254 - (int)byte) << 23);   // 2^(127 - byte)
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const float a = bf16_bits_to_float(w[2 * i] & 0xffffu) * inv, b = bf16_bits_to_float(w[2 * i] >> 16) * inv;
+    const float c = bf16_bits_to_float(w[2 * i + 1] & 0xffffu) * inv, d = bf16_bits_to_float(w[2 * i + 1] >> 16) * inv;
+    q[i] = pack4_e4m3(a, b, c, d);
+  }
+  return byte;
+}
+
+// X [rows, K] row-major (ldx).  One thread per (row, K-block) over the PADDED scale grid
+// (rows up to a multiple of 128, K-blocks up to a multiple of 4) so padding scales become 0.
+__global__ void __launch_bounds__(256)
+quantize_rows_kernel(const __nv_bfloat16* __restrict__ X, int64_t rows, int64_t K, int64_t ldx,
+                     uint8_t* __restrict__ Xq, uint8_t* __restrict__ SF, int64_t kb_pad, int64_t rows_pad) {
+  const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const int64_t kb = idx % kb_pad, r = idx / kb_pad;
+  if (r >= rows_pad) return;
+  const int64_t KB = K / 32, kchunks = kb_pad / 4;
+  uint32_t byte = 0;
+  if (r < rows && kb < KB) {
+    const uint4* src = reinterpret_cast<const uint4*>(X + r * ldx + kb * 32);
+    uint32_t w[16], q[8];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const uint4 v = __ldg(src + i);
+      w[4 * i] = v.x; w[4 * i + 1] = v.y; w[4 * i + 2] = v.z; w[4 * i + 3] = v.w;
+    }
+    byte = quantise_block(w, q);
+    uint4* dst = reinterpret_cast<uint4*>(Xq + r * K + kb * 32);
+    dst[0] = make_uint4(q[0], q[1], q[2], q[3]);
+    dst[1] = make_uint4(q[4], q[5], q[6], q[7]);
+  }
+  SF[scale_offset(kchunks, r, kb)] = (uint8_t)byte;
+}
+
+// X [K, rows] row-major (ldx): quantise every column along K, write Xq [rows, K] K-contiguous.
+// A CTA stages a 32 (k) x 128 (columns) tile in shared memory; thread c then owns column c.
+__global__ void __launch_bounds__(128)
+quantize_cols_kernel(const __nv_bfloat16* __restrict__ X, int64_t rows, int64_t K, int64_t ldx,
+                     uint8_t* __restrict__ Xq, uint8_t* __restrict__ SF, int64_t kb_pad) {
+  __shared__ uint16_t tile[32][128 + 2];
+  const int64_t c0 = (int64_t)blockIdx.x * 128, kb = blockIdx.y;
+  const int64_t KB = K / 32, kchunks = kb_pad / 4;
+  const int t = threadIdx.x;
+  const bool kb_ok = kb < KB;
+  if (kb_ok) {
+    const uint16_t* Xu = reinterpret_cast<const uint16_t*>(X);
+#pragma unroll 4
+    for (int k = 0; k < 32; ++k) {
+      const int64_t c = c0 + t;
+      tile[k][t] = (c < rows) ? Xu[(kb * 32 + k) * ldx + c] : (uint16_t)0;
+    }
+  }
+  __syncthreads();
+  const int64_t c = c0 + t;   // column of X = row of Xq; the grid covers columns up to a multiple of 128
+  uint32_t byte = 0;
+  if (kb_ok && c < rows) {
+    uint32_t w[16], q[8];
+#pragma unroll
+    for (int i = 0; i < 16; ++i) w[i] = (uint32_t)tile[2 * i][t] | ((uint32_t)tile[2 * i + 1][t] << 16);
+    byte = quantise_block(w, q);
+    uint4* dst = reinterpret_cast<uint4*>(Xq + c * K + kb * 32);
+    dst[0] = make_uint4(q[0], q[1], q[2], q[3]);
+    dst[1] = make_uint4(q[4], q[5], q[6], q[7]);
+  }
+  SF[scale_offset(kchunks, c, kb)] = (uint8_t)byte;
+}
+
+}  // namespace mx
+}  // namespace gemm_b200

@@ -3,6 +3,8 @@
 #include <mutex>
 
 #include "gemm_bf16.cuh"
+#include "gemm_mxfp8.cuh"
+#include "quant_mxfp8.cuh"
 
 namespace gemm_b200 {
 namespace tc {
@@ -249,19 +251,207 @@ extern "C" int gemm_b200_check_status(void* stream, int32_t detail[4]) {
   return GEMM_B200_OK;
 }
 
-// ---- MXFP8 entry points: placeholder until the block-scaled kernels land in this file ----
-extern "C" int gemm_b200_quantize_mxfp8(const void*, int64_t, int64_t, int64_t, int, void*, void*, void*) {
-  return gemm_b200::fail(GEMM_B200_ERR_UNSUPPORTED, "quantize_mxfp8: not built");
+
+// =========================================================================================
+// MXFP8
+// =========================================================================================
+namespace gemm_b200 {
+namespace tc {
+
+struct MxArgs {
+  const void *Aq, *SFA, *Bq, *SFB;
+  void* C;
+  int64_t M, N, K, ldc;
+  cudaStream_t stream;
+};
+
+// packed scale buffer of `rows` rows viewed as int32 [row blocks][kchunks * 128]
+static int make_scale_map(CUtensorMap* map, const void* sf, int64_t rows, int64_t K, int box_blocks) {
+  EncodeTiledFn fn = encode_tiled_fn();
+  if (!fn) return fail(GEMM_B200_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
+  const int64_t kchunks = ceil_div64(K / 32, 4), blocks = ceil_div64(rows, 128);
+  cuuint64_t dims[2] = {(cuuint64_t)(kchunks * 128), (cuuint64_t)blocks};
+  cuuint64_t strides[1] = {(cuuint64_t)(kchunks * 512)};
+  cuuint32_t box[2] = {128, (cuuint32_t)box_blocks};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_INT32, 2, const_cast<void*>(sf), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail(GEMM_B200_ERR_CUDA, "cuTensorMapEncodeTiled (scales) failed with CUresult %d", (int)r);
+  return GEMM_B200_OK;
 }
-extern "C" size_t gemm_b200_mxfp8_scale_bytes(int64_t, int64_t) { return 0; }
-extern "C" size_t gemm_b200_mxfp8_scale_offset(int64_t, int64_t, int64_t, int64_t) { return 0; }
-extern "C" int gemm_b200_gemm_mxfp8(const void*, const void*, const void*, const void*, void*, int64_t, int64_t, int64_t,
-                                    int64_t, int, void*) {
-  return gemm_b200::fail(GEMM_B200_ERR_UNSUPPORTED, "gemm_mxfp8: not built");
+
+template <class Cfg, bool OUT_F32>
+static int launch_mxfp8(const MxArgs& a) {
+  constexpr int CG = Cfg::CG;
+  DeviceInfo di;
+  if (int rc = device_info(&di)) return rc;
+  CUtensorMap tmA, tmB, tmSFA, tmSFB;
+  if (int rc = make_map_2d(&tmA, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, a.Aq, a.M, a.K, a.K, kMxBlockK, kBlockM,
+                           CU_TENSOR_MAP_SWIZZLE_128B))
+    return rc;
+  if (int rc = make_map_2d(&tmB, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, a.Bq, a.N, a.K, a.K, kMxBlockK, Cfg::BN_CTA,
+                           CU_TENSOR_MAP_SWIZZLE_128B))
+    return rc;
+  if (int rc = make_scale_map(&tmSFA, a.SFA, a.M, a.K, 1)) return rc;
+  if (int rc = make_scale_map(&tmSFB, a.SFB, a.N, a.K, 2)) return rc;
+
+  auto kern = gemm_mxfp8_kernel<Cfg, OUT_F32>;
+  static std::mutex mu;
+  static int max_clusters_for_dev[64] = {0};
+  int max_clusters = 0;
+  {
+    std::lock_guard<std::mutex> lk(mu);
+    const int slot = di.dev & 63;
+    if (max_clusters_for_dev[slot] == 0) {
+      GEMM_B200_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES));
+      int n = di.sms / CG;
+      if (CG > 1) {
+        cudaLaunchConfig_t qc = {};
+        qc.gridDim = dim3((unsigned)(di.sms / CG * CG));
+        qc.blockDim = dim3(kMxThreads);
+        qc.dynamicSmemBytes = Cfg::SMEM_BYTES;
+        cudaLaunchAttribute qa[1];
+        qa[0].id = cudaLaunchAttributeClusterDimension;
+        qa[0].val.clusterDim.x = CG;
+        qa[0].val.clusterDim.y = 1;
+        qa[0].val.clusterDim.z = 1;
+        qc.attrs = qa;
+        qc.numAttrs = 1;
+        int active = 0;
+        GEMM_B200_CUDA_TRY(cudaOccupancyMaxActiveClusters(&active, kern, &qc));
+        if (active < 1) return fail(GEMM_B200_ERR_CUDA, "gemm_mxfp8: no CTA pair fits on this device");
+        if (active < n) n = active;
+      }
+      max_clusters_for_dev[slot] = n;
+    }
+    max_clusters = max_clusters_for_dev[slot];
+  }
+  GemmShape shape;
+  shape.M = (int)a.M;
+  shape.N = (int)a.N;
+  shape.K = (int)a.K;
+  shape.tiles_m = (int)ceil_div64(a.M, kBlockM * CG);
+  shape.tiles_n = (int)ceil_div64(a.N, kBlockN);
+  const int64_t num_tiles = (int64_t)shape.tiles_m * shape.tiles_n;
+  if (num_tiles > 0x7fffffff) return fail(GEMM_B200_ERR_TOO_LARGE, "gemm_mxfp8: too many tiles");
+  const int clusters = (int)(num_tiles < max_clusters ? num_tiles : max_clusters);
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)(clusters * CG));
+  cfg.blockDim = dim3(kMxThreads);
+  cfg.dynamicSmemBytes = Cfg::SMEM_BYTES;
+  cfg.stream = a.stream;
+  cudaLaunchAttribute attrs[1];
+  attrs[0].id = cudaLaunchAttributeClusterDimension;
+  attrs[0].val.clusterDim.x = CG;
+  attrs[0].val.clusterDim.y = 1;
+  attrs[0].val.clusterDim.z = 1;
+  cfg.attrs = attrs;
+  cfg.numAttrs = 1;
+  void* cptr = a.C;
+  int64_t ldc = a.ldc;
+  GEMM_B200_CUDA_TRY(cudaLaunchKernelEx(&cfg, kern, tmA, tmB, tmSFA, tmSFB, cptr, ldc, shape));
+  launch_counter().fetch_add(1, std::memory_order_relaxed);
+  return GEMM_B200_OK;
 }
-extern "C" int gemm_b200_gemm_mxfp8_cfg(const void*, const void*, const void*, const void*, void*, int64_t, int64_t,
-                                        int64_t, int64_t, int, int, void*) {
-  return gemm_b200::fail(GEMM_B200_ERR_UNSUPPORTED, "gemm_mxfp8: not built");
+
+struct MxConfigEntry {
+  const char* name;
+  int (*launch[2])(const MxArgs&);   // [out_dtype]
+};
+using Mx_1cta = MxCfg<1, 4, false>;
+using Mx_2cta = MxCfg<2, 6, false>;
+using Mx_2cta_m = MxCfg<2, 6, true>;
+static const MxConfigEntry kMxConfigs[] = {
+    {"1cta_128x256x128_s4", {launch_mxfp8<Mx_1cta, false>, launch_mxfp8<Mx_1cta, true>}},
+    {"2cta_256x256x128_s6", {launch_mxfp8<Mx_2cta, false>, launch_mxfp8<Mx_2cta, true>}},
+    {"2cta_256x256x128_s6_maskcommit", {launch_mxfp8<Mx_2cta_m, false>, launch_mxfp8<Mx_2cta_m, true>}},
+};
+constexpr int kNumMxConfigs = sizeof(kMxConfigs) / sizeof(kMxConfigs[0]);
+constexpr int kDefaultMxConfig = 1;
+
+}  // namespace tc
+}  // namespace gemm_b200
+
+extern "C" size_t gemm_b200_mxfp8_scale_bytes(int64_t rows, int64_t K) {
+  if (rows <= 0 || K <= 0) return 0;
+  return (size_t)(gemm_b200::ceil_div64(rows, 128) * gemm_b200::ceil_div64(gemm_b200::ceil_div64(K, 32), 4) * 512);
 }
-extern "C" int gemm_b200_gemm_mxfp8_num_configs(void) { return 0; }
-extern "C" const char* gemm_b200_gemm_mxfp8_config_name(int) { return ""; }
+extern "C" size_t gemm_b200_mxfp8_scale_offset(int64_t rows, int64_t K, int64_t row, int64_t kb) {
+  (void)rows;
+  return gemm_b200::mx::scale_offset(gemm_b200::ceil_div64(gemm_b200::ceil_div64(K, 32), 4), row, kb);
+}
+
+extern "C" int gemm_b200_quantize_mxfp8(const void* X, int64_t rows, int64_t K, int64_t ldx, int transposed_in,
+                                        void* Xq, void* SF, void* stream) {
+  using namespace gemm_b200;
+  if (rows < 0 || K < 0) return fail(GEMM_B200_ERR_INVALID_ARG, "quantize_mxfp8: negative size");
+  if (rows == 0 || K == 0) return GEMM_B200_OK;
+  if (!X || !Xq || !SF) return fail(GEMM_B200_ERR_INVALID_ARG, "quantize_mxfp8: null pointer");
+  if (K % 32 != 0) return fail(GEMM_B200_ERR_INVALID_ARG, "quantize_mxfp8: K=%lld is not a multiple of 32", (long long)K);
+  if (ldx < (transposed_in ? rows : K)) return fail(GEMM_B200_ERR_INVALID_ARG, "quantize_mxfp8: ldx too small");
+  if (reinterpret_cast<uintptr_t>(Xq) % 16 != 0) return fail(GEMM_B200_ERR_ALIGNMENT, "quantize_mxfp8: Xq must be 16-byte aligned");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const int64_t kb_pad = ceil_div64(K / 32, 4) * 4, rows_pad = ceil_div64(rows, 128) * 128;
+  if (!transposed_in) {
+    if (reinterpret_cast<uintptr_t>(X) % 16 != 0 || ldx % 8 != 0)
+      return fail(GEMM_B200_ERR_ALIGNMENT, "quantize_mxfp8: X must be 16-byte aligned with ldx a multiple of 8");
+    const int64_t threads = rows_pad * kb_pad;
+    const int64_t blocks = ceil_div64(threads, 256);
+    if (blocks > 0x7fffffff) return fail(GEMM_B200_ERR_TOO_LARGE, "quantize_mxfp8: too large");
+    mx::quantize_rows_kernel<<<(unsigned)blocks, 256, 0, st>>>(static_cast<const __nv_bfloat16*>(X), rows, K, ldx,
+                                                               static_cast<uint8_t*>(Xq), static_cast<uint8_t*>(SF),
+                                                               kb_pad, rows_pad);
+  } else {
+    if (kb_pad > 65535) return fail(GEMM_B200_ERR_TOO_LARGE, "quantize_mxfp8: K too large for the transposed path");
+    dim3 grid((unsigned)(rows_pad / 128), (unsigned)kb_pad);
+    mx::quantize_cols_kernel<<<grid, 128, 0, st>>>(static_cast<const __nv_bfloat16*>(X), rows, K, ldx,
+                                                   static_cast<uint8_t*>(Xq), static_cast<uint8_t*>(SF), kb_pad);
+  }
+  launch_counter().fetch_add(1, std::memory_order_relaxed);
+  GEMM_B200_CUDA_TRY(cudaGetLastError());
+  return GEMM_B200_OK;
+}
+
+extern "C" int gemm_b200_gemm_mxfp8_cfg(const void* Aq, const void* SFA, const void* Bq, const void* SFB, void* C,
+                                        int64_t M, int64_t N, int64_t K, int64_t ldc, int out_dtype, int config,
+                                        void* stream) {
+  using namespace gemm_b200;
+  if (M < 0 || N < 0 || K < 0) return fail(GEMM_B200_ERR_INVALID_ARG, "gemm_mxfp8: negative size");
+  if (out_dtype != GEMM_B200_OUT_BF16 && out_dtype != GEMM_B200_OUT_F32)
+    return fail(GEMM_B200_ERR_INVALID_ARG, "gemm_mxfp8: out_dtype %d", out_dtype);
+  if (config >= tc::kNumMxConfigs) return fail(GEMM_B200_ERR_INVALID_ARG, "gemm_mxfp8: config %d out of range", config);
+  if (M == 0 || N == 0) return GEMM_B200_OK;
+  if (!C || (K > 0 && (!Aq || !Bq || !SFA || !SFB))) return fail(GEMM_B200_ERR_INVALID_ARG, "gemm_mxfp8: null pointer");
+  if (ldc < N) return fail(GEMM_B200_ERR_INVALID_ARG, "gemm_mxfp8: ldc smaller than N");
+  if (K % 32 != 0) return fail(GEMM_B200_ERR_INVALID_ARG, "gemm_mxfp8: K=%lld is not a multiple of 32", (long long)K);
+  if (M > 0x7fffffff || N > 0x7fffffff || K > 0x7fffffff)
+    return fail(GEMM_B200_ERR_TOO_LARGE, "gemm_mxfp8: a dimension exceeds 2^31-1");
+  const int c_elem = out_dtype == GEMM_B200_OUT_F32 ? 4 : 2;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (K == 0) {
+    GEMM_B200_CUDA_TRY(cudaMemset2DAsync(C, (size_t)ldc * c_elem, 0, (size_t)N * c_elem, (size_t)M, st));
+    return GEMM_B200_OK;
+  }
+  if ((reinterpret_cast<uintptr_t>(Aq) | reinterpret_cast<uintptr_t>(Bq) | reinterpret_cast<uintptr_t>(C) |
+       reinterpret_cast<uintptr_t>(SFA) | reinterpret_cast<uintptr_t>(SFB)) % 16 != 0)
+    return fail(GEMM_B200_ERR_ALIGNMENT, "gemm_mxfp8: all pointers must be 16-byte aligned");
+  if ((ldc * c_elem) % 16 != 0 || N % (16 / c_elem) != 0)
+    return fail(GEMM_B200_ERR_ALIGNMENT, "gemm_mxfp8: ldc*sizeof(C) and N*sizeof(C) must be multiples of 16 bytes");
+  tc::DeviceInfo di;
+  if (int rc = tc::device_info(&di)) return rc;
+  if (di.cc_major != 10)
+    return fail(GEMM_B200_ERR_UNSUPPORTED, "gemm_mxfp8: device has compute capability %d.x, need 10.x (sm_100a)", di.cc_major);
+  if (config < 0) config = tc::kDefaultMxConfig;
+  tc::MxArgs args{Aq, SFA, Bq, SFB, C, M, N, K, ldc, st};
+  return tc::kMxConfigs[config].launch[out_dtype](args);
+}
+extern "C" int gemm_b200_gemm_mxfp8(const void* Aq, const void* SFA, const void* Bq, const void* SFB, void* C, int64_t M,
+                                    int64_t N, int64_t K, int64_t ldc, int out_dtype, void* stream) {
+  return gemm_b200_gemm_mxfp8_cfg(Aq, SFA, Bq, SFB, C, M, N, K, ldc, out_dtype, -1, stream);
+}
+extern "C" int gemm_b200_gemm_mxfp8_num_configs(void) { return gemm_b200::tc::kNumMxConfigs; }
+extern "C" const char* gemm_b200_gemm_mxfp8_config_name(int config) {
+  if (config < 0 || config >= gemm_b200::tc::kNumMxConfigs) return "";
+  return gemm_b200::tc::kMxConfigs[config].name;
+}

@@ -16,6 +16,7 @@ from ._lib import lib, check
 __all__ = [
     "sgemm_f32", "gemm_bf16", "check_status", "sgemm_f32_host", "gemm_bf16_host",
     "sgemm_f32_configs", "gemm_bf16_configs", "launch_count",
+    "quantize_mxfp8", "gemm_mxfp8", "gemm_mxfp8_configs", "MxFp8Tensor",
 ]
 
 
@@ -127,3 +128,55 @@ def gemm_bf16_configs() -> list[str]:
 
 def launch_count() -> int:
     return int(lib.gemm_b200_launch_count())
+
+
+class MxFp8Tensor:
+    """An MXFP8 operand: `data` uint8 [rows, K] (e4m3, K contiguous) and `scales`, the packed UE8M0
+    buffer in the layout of gemm_b200_mxfp8_scale_offset()."""
+
+    def __init__(self, data: torch.Tensor, scales: torch.Tensor, rows: int, K: int):
+        self.data, self.scales, self.rows, self.K = data, scales, rows, K
+
+    def scale_matrix(self) -> torch.Tensor:
+        """The scale bytes as a plain [rows, K/32] uint8 tensor on the host (tests, debugging)."""
+        sc = self.scales.cpu()
+        r = torch.arange(self.rows).view(-1, 1)
+        kb = torch.arange(self.K // 32).view(1, -1)
+        kchunks = -(-(self.K // 32) // 4)
+        off = ((r // 128) * kchunks + kb // 4) * 512 + (r % 32) * 16 + ((r // 32) % 4) * 4 + (kb % 4)
+        return sc[off]
+
+
+def quantize_mxfp8(X: torch.Tensor, transposed_in: bool = False) -> MxFp8Tensor:
+    """bf16 -> MXFP8 along K.  `X` is [rows, K], or with `transposed_in` [K, rows] (e.g. B[K, N])."""
+    _require(X.is_cuda and X.dtype == torch.bfloat16 and X.dim() == 2, "expected a 2-D CUDA bfloat16 tensor")
+    ldx = _row_major_ld(X)
+    K, rows = (X.shape if transposed_in else (X.shape[1], X.shape[0]))
+    rows, K = int(rows), int(K)
+    data = torch.empty((rows, K), device=X.device, dtype=torch.uint8)
+    scales = torch.empty((max(int(lib.gemm_b200_mxfp8_scale_bytes(rows, K)), 1),), device=X.device, dtype=torch.uint8)
+    with torch.cuda.device(X.device):
+        check(lib.gemm_b200_quantize_mxfp8(X.data_ptr(), rows, K, ldx, 1 if transposed_in else 0, data.data_ptr(),
+                                           scales.data_ptr(), _stream(X)))
+    return MxFp8Tensor(data, scales, rows, K)
+
+
+def gemm_mxfp8(A: MxFp8Tensor, B: MxFp8Tensor, out: torch.Tensor | None = None, *,
+               out_dtype: torch.dtype = torch.bfloat16, config: int = -1) -> torch.Tensor:
+    """C[M, N] = dequant(A)[M, K] @ dequant(B)[N, K]^T on the block-scaled tensor cores."""
+    _require(A.K == B.K, f"K mismatch: {A.K} vs {B.K}")
+    _require(out_dtype in (torch.bfloat16, torch.float32), "out_dtype must be bfloat16 or float32")
+    M, N, K = A.rows, B.rows, A.K
+    if out is None:
+        out = torch.empty((M, N), device=A.data.device, dtype=out_dtype)
+    _require(out.is_cuda and out.dtype == out_dtype and tuple(out.shape) == (M, N), "bad out tensor")
+    with torch.cuda.device(A.data.device):
+        check(lib.gemm_b200_gemm_mxfp8_cfg(A.data.data_ptr(), A.scales.data_ptr(), B.data.data_ptr(), B.scales.data_ptr(),
+                                           out.data_ptr(), M, N, K, _row_major_ld(out),
+                                           _lib.OUT_F32 if out_dtype == torch.float32 else _lib.OUT_BF16, config,
+                                           _stream(A.data)))
+    return out
+
+
+def gemm_mxfp8_configs() -> list[str]:
+    return [lib.gemm_b200_gemm_mxfp8_config_name(i).decode() for i in range(lib.gemm_b200_gemm_mxfp8_num_configs())]

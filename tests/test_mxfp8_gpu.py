@@ -1,0 +1,115 @@
+"""MXFP8 (e4m3 + UE8M0 per 32 k) on the GPU through the C-ABI.
+
+Quantiser bar: bit-exact (bytes and scales) against the oracle's restatement of the recipe.
+GEMM bar (stated MXFP8 tolerance): relative error <= 1e-3 against an FP32 matmul of the
+dequantised operands, measured on FP32 output (bf16 rounding of the output alone is ~1.7e-3);
+bf16 output is held to the bf16 rounding of that FP32 result."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+REL_TOL = 1e-3
+
+
+@pytest.mark.parametrize("rows,K", [(1, 32), (16, 8192), (128, 128), (130, 96), (257, 416), (1000, 2048)])
+@pytest.mark.parametrize("transposed_in", [False, True])
+def test_quantiser_bit_exact(ops, oracle, rows, K, transposed_in):
+    g = torch.Generator().manual_seed(rows * 7 + K)
+    X = (torch.randn(rows, K, generator=g) * torch.exp(torch.randn(rows, 1, generator=g) * 3)).bfloat16()
+    X[0, :32] = 0                                   # an all-zero block
+    if rows > 1:
+        X[1, :32] = 1e-40                           # a block of denormals
+    q_want, s_want = oracle.mxfp8_quantize(X)
+    Xd = X.t().contiguous().cuda() if transposed_in else X.cuda()
+    got = ops.quantize_mxfp8(Xd, transposed_in=transposed_in)
+    torch.cuda.synchronize()
+    assert torch.equal(got.scale_matrix(), s_want)
+    assert torch.equal(got.data.cpu(), q_want)
+    # the packed buffer matches the oracle's packer byte for byte (padding = 0)
+    assert torch.equal(got.scales.cpu(), oracle.mxfp8_pack_scales(s_want, K))
+
+
+def test_saturation_and_extremes(ops, oracle):
+    # scale 2^(floor(log2 amax) - 8) puts |x / s| in [256, 512): values above 448 must saturate
+    X = torch.zeros(4, 64).bfloat16()
+    X[0, :32] = torch.linspace(1.0, 1.99, 32).bfloat16()
+    X[1, :32] = 3.3895e38                           # near the bf16 maximum
+    X[2, 0] = -1.75
+    X[3, :] = torch.tensor([2.0 ** -120]).bfloat16()
+    q_want, s_want = oracle.mxfp8_quantize(X)
+    got = ops.quantize_mxfp8(X.cuda())
+    assert torch.equal(got.data.cpu(), q_want) and torch.equal(got.scale_matrix(), s_want)
+    assert int(q_want[0].max()) == 0x7E             # 448, the e4m3 maximum
+
+
+def _gemm_check(ops, oracle, M, K, N, config=-1, seed=0):
+    A, B = oracle.gen_randn_bf16(M, K, N, seed=seed)
+    Aq = ops.quantize_mxfp8(A.cuda())
+    Bq = ops.quantize_mxfp8(B.cuda(), transposed_in=True)
+    qa, sa = oracle.mxfp8_quantize(A)
+    qb, sb = oracle.mxfp8_quantize(B.t().contiguous())
+    want = oracle.mxfp8_matmul_oracle(qa, sa, qb, sb)
+    C32 = torch.full((M, N), float("nan"), device="cuda")
+    ops.gemm_mxfp8(Aq, Bq, C32, out_dtype=torch.float32, config=config)
+    ops.check_status()
+    assert oracle.rel_frobenius(C32.cpu(), want) <= REL_TOL
+    torch.testing.assert_close(C32.cpu(), want, rtol=1e-3, atol=1e-3 * float(want.abs().max()))
+    C16 = ops.gemm_mxfp8(Aq, Bq, out_dtype=torch.bfloat16, config=config)
+    ops.check_status()
+    assert torch.equal(C16.cpu(), C32.bfloat16().cpu())      # same accumulator, rounded once
+
+
+@pytest.mark.parametrize("shape", [(128, 128, 256), (256, 512, 256), (512, 1024, 768), (1024, 4096, 1024)])
+def test_gemm_every_config(ops, oracle, shape):
+    M, K, N = shape
+    for cfg in range(len(ops.gemm_mxfp8_configs())):
+        _gemm_check(ops, oracle, M, K, N, config=cfg, seed=cfg)
+
+
+@pytest.mark.parametrize("M,K,N", [(1, 32, 8), (16, 8192, 512), (100, 96, 40), (129, 160, 264), (300, 224, 1000), (2000, 992, 24)])
+def test_gemm_edge_shapes(ops, oracle, M, K, N):
+    for cfg in range(len(ops.gemm_mxfp8_configs())):
+        _gemm_check(ops, oracle, M, K, N, config=cfg, seed=M + N)
+
+
+def test_scales_matter(ops, oracle):
+    # rows of A with very different magnitudes: wrong scale placement would show at once
+    M, K, N = 256, 256, 256
+    g = torch.Generator().manual_seed(3)
+    A = (torch.randn(M, K, generator=g) * (2.0 ** torch.randint(-20, 20, (M, 1), generator=g))).bfloat16()
+    B = (torch.randn(K, N, generator=g) * (2.0 ** torch.randint(-10, 10, (1, N), generator=g))).bfloat16()
+    # and per-K-block variation
+    A[:, 32:64] *= 64
+    B[96:128, :] *= 1 / 128
+    Aq = ops.quantize_mxfp8(A.cuda()); Bq = ops.quantize_mxfp8(B.cuda(), transposed_in=True)
+    qa, sa = oracle.mxfp8_quantize(A); qb, sb = oracle.mxfp8_quantize(B.t().contiguous())
+    want = oracle.mxfp8_matmul_oracle(qa, sa, qb, sb)
+    for cfg in range(len(ops.gemm_mxfp8_configs())):
+        got = ops.gemm_mxfp8(Aq, Bq, out_dtype=torch.float32, config=cfg)
+        ops.check_status()
+        err = ((got.cpu() - want).abs() / (want.abs() + 1e-30))
+        assert oracle.rel_frobenius(got.cpu(), want) <= REL_TOL
+        # row-wise relative error, so small-magnitude rows are checked as strictly as large ones
+        rowerr = torch.linalg.norm((got.cpu() - want).double(), dim=1) / torch.linalg.norm(want.double(), dim=1)
+        assert float(rowerr.max()) <= REL_TOL
+
+
+def test_config4_shapes_sampled(ops, oracle):
+    # the FFN shape and the skinny decode shape at full size; oracle on sampled rows
+    for (M, K, N) in [(16384, 8192, 28672), (16, 8192, 28672)]:
+        g = torch.Generator(device="cuda").manual_seed(0)
+        A = torch.randn(M, K, device="cuda", generator=g).bfloat16()
+        B = torch.randn(K, N, device="cuda", generator=g).bfloat16()
+        Aq = ops.quantize_mxfp8(A); Bq = ops.quantize_mxfp8(B, transposed_in=True)
+        C = ops.gemm_mxfp8(Aq, Bq, out_dtype=torch.float32)
+        ops.check_status()
+        rows = torch.tensor(sorted({0, 1, min(127, M - 1), min(128, M - 1), M // 2, M - 1}))
+        qa, sa = oracle.mxfp8_quantize(A[rows].cpu())
+        assert torch.equal(Aq.data[rows].cpu(), qa)
+        cols = torch.arange(0, N, 7)
+        qb, sb = oracle.mxfp8_quantize(B[:, cols].t().contiguous().cpu())
+        want = oracle.mxfp8_matmul_oracle(qa, sa, qb, sb)
+        assert oracle.rel_frobenius(C[rows][:, cols].cpu(), want) <= REL_TOL
+        del A, B, Aq, Bq, C
+        torch.cuda.empty_cache()
