@@ -170,6 +170,8 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
           tc_fence_after_sync();
           const uint32_t a_addr = sA0 + s * Cfg::A_BYTES, b_addr = sB0 + s * Cfg::B_BYTES;
           const uint32_t sfa_addr = sSFA0 + s * Cfg::SFA_BYTES, sfb_addr = sSFB0 + s * Cfg::SFB_BYTES;
+          // tcgen05.cp and tcgen05.mma of one thread execute in issue order: these copies land
+          // after the previous block's MMAs have read the scale columns and before the next ones do
           tmem_cp_32x128b_warpx4<CG>(sfa_tmem, smem_desc(sf_hi, sfa_addr));
           tmem_cp_32x128b_warpx4<CG>(sfb_tmem, smem_desc(sf_hi, sfb_addr));
           tmem_cp_32x128b_warpx4<CG>(sfb_tmem + 4, smem_desc(sf_hi, sfb_addr + 512));

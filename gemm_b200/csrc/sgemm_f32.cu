@@ -272,45 +272,49 @@ int launch_cfg(const float* A, const float* B, float* Cm, int M, int N, int K, i
   return GEMM_B200_OK;
 }
 
-//                 BM   BN  BK  WMW WNW ST MINB X2
-using C128x128k16   = Cfg<128, 128, 16, 4, 2, 3, 2, false>;
-using C128x128k16p  = Cfg<128, 128, 16, 4, 2, 3, 2, true>;
-using C128x128k32p  = Cfg<128, 128, 32, 4, 2, 3, 2, true>;
-using C128x128k8p   = Cfg<128, 128, 8, 4, 2, 4, 2, true>;
-using C128x256k16p  = Cfg<128, 256, 16, 4, 2, 3, 1, true>;
-using C256x128k16p  = Cfg<256, 128, 16, 8, 1, 3, 1, true>;
-using C128x64k16p   = Cfg<128, 64, 16, 4, 2, 3, 3, true>;
-using C64x64k16p    = Cfg<64, 64, 16, 2, 2, 4, 4, true>;
-using C64x64k16     = Cfg<64, 64, 16, 2, 2, 4, 4, false>;
-using C32x64k16p    = Cfg<32, 64, 16, 2, 2, 4, 6, true>;
-using C128x128k32   = Cfg<128, 128, 32, 4, 2, 3, 2, false>;
-using C128x128k16s4p = Cfg<128, 128, 16, 4, 2, 4, 2, true>;
+//                        BM   BN  BK WMW WNW ST MINB X2  AK
+using C128x128k16      = Cfg<128, 128, 16, 4, 2, 3, 2, false>;
+using C128x128k16p     = Cfg<128, 128, 16, 4, 2, 3, 2, true>;
+using C128x128k32p     = Cfg<128, 128, 32, 4, 2, 3, 2, true>;
+using C128x128k32pa4   = Cfg<128, 128, 32, 4, 2, 3, 2, true, 4>;
+using C128x256k16p     = Cfg<128, 256, 16, 4, 2, 3, 1, true>;
+using C128x256k32p     = Cfg<128, 256, 32, 4, 2, 3, 1, true>;
+using C256x128k32p     = Cfg<256, 128, 32, 8, 1, 3, 1, true>;
+using C128x64k32p      = Cfg<128, 64, 32, 4, 2, 3, 2, true>;
+using C64x64k16p       = Cfg<64, 64, 16, 2, 2, 4, 4, true>;
+using C64x64k32p       = Cfg<64, 64, 32, 2, 2, 4, 4, true>;
+using C64x64k16        = Cfg<64, 64, 16, 2, 2, 4, 4, false>;
+using C32x64k16p       = Cfg<32, 64, 16, 2, 2, 4, 6, true>;
+using C32x64k32p       = Cfg<32, 64, 32, 2, 2, 4, 6, true>;
+using C128x128k32      = Cfg<128, 128, 32, 4, 2, 3, 2, false>;
 
 static const ConfigEntry kConfigs[] = {
     {"128x128x16_s3", 128, 128, launch_cfg<C128x128k16>},
     {"128x128x16_s3_f32x2", 128, 128, launch_cfg<C128x128k16p>},
     {"128x128x32_s3_f32x2", 128, 128, launch_cfg<C128x128k32p>},
-    {"128x128x8_s4_f32x2", 128, 128, launch_cfg<C128x128k8p>},
+    {"128x128x32_s3_f32x2_a4", 128, 128, launch_cfg<C128x128k32pa4>},
     {"128x256x16_s3_f32x2", 128, 256, launch_cfg<C128x256k16p>},
-    {"256x128x16_s3_f32x2", 256, 128, launch_cfg<C256x128k16p>},
-    {"128x64x16_s3_f32x2", 128, 64, launch_cfg<C128x64k16p>},
+    {"128x256x32_s3_f32x2", 128, 256, launch_cfg<C128x256k32p>},
+    {"256x128x32_s3_f32x2", 256, 128, launch_cfg<C256x128k32p>},
+    {"128x64x32_s3_f32x2", 128, 64, launch_cfg<C128x64k32p>},
     {"64x64x16_s4_f32x2", 64, 64, launch_cfg<C64x64k16p>},
+    {"64x64x32_s4_f32x2", 64, 64, launch_cfg<C64x64k32p>},
     {"64x64x16_s4", 64, 64, launch_cfg<C64x64k16>},
     {"32x64x16_s4_f32x2", 32, 64, launch_cfg<C32x64k16p>},
+    {"32x64x32_s4_f32x2", 32, 64, launch_cfg<C32x64k32p>},
     {"128x128x32_s3", 128, 128, launch_cfg<C128x128k32>},
-    {"128x128x16_s4_f32x2", 128, 128, launch_cfg<C128x128k16s4p>},
 };
 constexpr int kNumConfigs = sizeof(kConfigs) / sizeof(kConfigs[0]);
+constexpr int kCfgLarge = 2, kCfgMedium = 8, kCfgSmall = 11;
 
-// Heuristic: the largest tile that still yields at least ~2 CTAs per SM worth of tiles;
-// small problems fall through to smaller tiles so that all 148 SMs get work.
+// Heuristic from a sweep of square problems on a B200: 128x128x32 once it yields about four
+// tiles per SM, 64x64 tiles while those still fill the SMs, 32x64 below that.
 inline int pick_config(int64_t M, int64_t N, int num_sms) {
-  const int order[] = {1, 6, 7, 9};  // 128x128, 128x64, 64x64, 32x64 (all f32x2)
-  for (int idx : order) {
-    const int64_t tiles = ceil_div64(M, kConfigs[idx].bm) * ceil_div64(N, kConfigs[idx].bn);
-    if (tiles >= 2 * (int64_t)num_sms) return idx;
-  }
-  return 9;
+  const int64_t t128 = ceil_div64(M, 128) * ceil_div64(N, 128);
+  if (t128 >= 4 * (int64_t)num_sms) return kCfgLarge;
+  const int64_t t64 = ceil_div64(M, 64) * ceil_div64(N, 64);
+  if (t64 >= (int64_t)num_sms + num_sms / 2) return kCfgMedium;
+  return kCfgSmall;
 }
 
 }  // namespace f32

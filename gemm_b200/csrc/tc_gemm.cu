@@ -182,7 +182,7 @@ static const Bf16ConfigEntry kBf16Configs[] = {
     GEMM_B200_BF16_ENTRY("2cta_256x256x64_s6_tmastore_maskcommit", Bf16_2cta_tma_m),
 };
 constexpr int kNumBf16Configs = sizeof(kBf16Configs) / sizeof(kBf16Configs[0]);
-constexpr int kDefaultBf16Config = 3;
+constexpr int kDefaultBf16Config = 4;    // CTA pair, TMA store, masked commit
 
 }  // namespace tc
 }  // namespace gemm_b200
@@ -368,7 +368,8 @@ static const MxConfigEntry kMxConfigs[] = {
     {"2cta_256x256x128_s6_maskcommit", {launch_mxfp8<Mx_2cta_m, false>, launch_mxfp8<Mx_2cta_m, true>}},
 };
 constexpr int kNumMxConfigs = sizeof(kMxConfigs) / sizeof(kMxConfigs[0]);
-constexpr int kDefaultMxConfig = 1;
+constexpr int kDefaultMxConfig = 2;      // CTA pair, masked commit
+constexpr int kSkinnyMxConfig = 0;       // M <= 128: single-CTA tiles give more independent column tiles
 
 }  // namespace tc
 }  // namespace gemm_b200
@@ -442,7 +443,7 @@ extern "C" int gemm_b200_gemm_mxfp8_cfg(const void* Aq, const void* SFA, const v
   if (int rc = tc::device_info(&di)) return rc;
   if (di.cc_major != 10)
     return fail(GEMM_B200_ERR_UNSUPPORTED, "gemm_mxfp8: device has compute capability %d.x, need 10.x (sm_100a)", di.cc_major);
-  if (config < 0) config = tc::kDefaultMxConfig;
+  if (config < 0) config = (M <= 128) ? tc::kSkinnyMxConfig : tc::kDefaultMxConfig;
   tc::MxArgs args{Aq, SFA, Bq, SFB, C, M, N, K, ldc, st};
   return tc::kMxConfigs[config].launch[out_dtype](args);
 }
