@@ -53,6 +53,11 @@ struct Bf16Cfg {
 struct GemmShape {
   int M, N, K;
   int tiles_m, tiles_n;   // tiles of (kBlockM * CG) x kBlockN
+  // split-K (block-scaled kernel only): every tile is cut into k_splits work units of
+  // kb_per_split K blocks; unit (tile, split) writes FP32 partial sums to slice `split` of a
+  // scratch buffer [k_splits][M][ldc].  k_splits == 1: the tile's result goes straight to C.
+  int k_splits, kb_per_split;
+  int64_t split_stride;   // elements between scratch slices
 };
 
 __device__ __forceinline__ void tile_coord(int t, int tiles_m, int tiles_n, int& tm, int& tn) {

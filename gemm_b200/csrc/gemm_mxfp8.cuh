@@ -72,8 +72,15 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
   const uint32_t cta_rank = (CG == 2) ? cluster_ctarank() : 0u;
   const int cluster_id = blockIdx.x / CG;
   const int num_clusters = gridDim.x / CG;
-  const int num_tiles = shape.tiles_m * shape.tiles_n;
   const int num_kb = (shape.K + kMxBlockK - 1) / kMxBlockK;
+  // work units: (tile, K split), consecutive units share the tile
+  const int num_units = shape.tiles_m * shape.tiles_n * shape.k_splits;
+  auto unit_range = [&](int u, int& tile, int& split, int& kb0, int& kb1) {
+    tile = u / shape.k_splits;
+    split = u - tile * shape.k_splits;
+    kb0 = split * shape.kb_per_split;
+    kb1 = min(num_kb, kb0 + shape.kb_per_split);
+  };
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
@@ -110,13 +117,14 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
     // ------------------------------------------------------------------ TMA producer
     if (lane == 0) {
       uint32_t it = 0;
-      for (int t = cluster_id; t < num_tiles && !failed; t += num_clusters) {
-        int tm, tn;
+      for (int u = cluster_id; u < num_units && !failed; u += num_clusters) {
+        int t, split, kb0, kb1, tm, tn;
+        unit_range(u, t, split, kb0, kb1);
         tile_coord(t, shape.tiles_m, shape.tiles_n, tm, tn);
         const int mblk = tm * CG + (int)cta_rank;            // 128-row block of A / C
         const int m0 = mblk * kBlockM;
         const int n0 = tn * kBlockN + (int)cta_rank * Cfg::BN_CTA;
-        for (int kb = 0; kb < num_kb; ++kb, ++it) {
+        for (int kb = kb0; kb < kb1; ++kb, ++it) {
           const int s = it % STAGES;
           const uint32_t ph = (it / STAGES) & 1u;
           if (!mbar_wait(empty_bar(s), ph ^ 1u, kRoleProducer, s)) { failed = true; break; }
@@ -160,10 +168,12 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
       const uint32_t d_tmem = tmem_base;
       const uint32_t sfa_tmem = tmem_base + kMxSfaCol, sfb_tmem = tmem_base + kMxSfbCol;
       uint32_t it = 0, acc_it = 0;
-      for (int t = cluster_id; t < num_tiles && !failed; t += num_clusters, ++acc_it) {
+      for (int u = cluster_id; u < num_units && !failed; u += num_clusters, ++acc_it) {
+        int t, split, kb0, kb1;
+        unit_range(u, t, split, kb0, kb1);
         if (!mbar_wait(tempty_bar, (acc_it & 1u) ^ 1u, kRoleMma, 100)) { failed = true; break; }
         tc_fence_after_sync();
-        for (int kb = 0; kb < num_kb; ++kb, ++it) {
+        for (int kb = kb0; kb < kb1; ++kb, ++it) {
           const int s = it % STAGES;
           const uint32_t ph = (it / STAGES) & 1u;
           if (!mbar_wait(full_bar(s), ph, kRoleMma, s)) { failed = true; break; }
@@ -180,7 +190,7 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
             // byte k of every 32-bit scale column belongs to this 32-wide K slice
             const uint32_t idesc = make_idesc_mxf8(kBlockM * CG, kBlockN, k, k);
             mma_mxf8<CG>(d_tmem, smem_desc(ab_hi, a_addr + k * kMxUmmaK), smem_desc(ab_hi, b_addr + k * kMxUmmaK), idesc,
-                         sfa_tmem + ((uint32_t)k << 30), sfb_tmem + ((uint32_t)k << 30), (kb | k) != 0 ? 1u : 0u);
+                         sfa_tmem + ((uint32_t)k << 30), sfb_tmem + ((uint32_t)k << 30), ((kb - kb0) | k) != 0 ? 1u : 0u);
           }
           commit(empty_bar(s));
         }
@@ -195,8 +205,9 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
     const int half = (warp - 2) >> 2;      // columns [128 half, 128 half + 128)
     const uint32_t t_addr = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(half * 128);
     uint32_t acc_it = 0;
-    for (int t = cluster_id; t < num_tiles && !failed; t += num_clusters, ++acc_it) {
-      int tm, tn;
+    for (int u = cluster_id; u < num_units && !failed; u += num_clusters, ++acc_it) {
+      int t, split, kb0, kb1, tm, tn;
+      unit_range(u, t, split, kb0, kb1);
       tile_coord(t, shape.tiles_m, shape.tiles_n, tm, tn);
       const int row = (tm * CG + (int)cta_rank) * kBlockM + quad * 32 + lane;
       const int col0 = tn * kBlockN + half * 128;
@@ -219,14 +230,14 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
         for (int c = 0; c < 4; ++c) {
           const int col = col0 + c * 32;
           if constexpr (OUT_F32) {
-            float* dst = reinterpret_cast<float*>(Cptr) + (int64_t)row * ldc + col;
+            float* dst = reinterpret_cast<float*>(Cptr) + (int64_t)split * shape.split_stride + (int64_t)row * ldc + col;
 #pragma unroll
             for (int j = 0; j < 8; ++j)
               if (col + 4 * j < shape.N)
                 *reinterpret_cast<uint4*>(dst + 4 * j) =
                     make_uint4(v[c][4 * j], v[c][4 * j + 1], v[c][4 * j + 2], v[c][4 * j + 3]);
           } else {
-            __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(Cptr) + (int64_t)row * ldc + col;
+            __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(Cptr) + (int64_t)row * ldc + col;   // k_splits == 1
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
               if (col + 8 * j < shape.N) {
@@ -260,6 +271,31 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
   if (warp == 1) {
     tc_fence_after_sync();
     tmem_dealloc<CG>(tmem_base, kTmemCols);
+  }
+}
+
+// Sums the k_splits FP32 partial results of a split-K run (slice s at W + s * split_stride, row
+// pitch ldw) in ascending s, and writes C as bf16 or f32.  One thread per 4 columns.
+template <bool OUT_F32>
+__global__ void __launch_bounds__(256)
+splitk_reduce_kernel(const float* __restrict__ W, int64_t split_stride, int64_t ldw, int k_splits,
+                     void* __restrict__ Cptr, int64_t ldc, int M, int N) {
+  const int64_t n4 = N / 4;
+  const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= (int64_t)M * n4) return;
+  const int64_t r = idx / n4, c = (idx % n4) * 4;
+  const float* src = W + r * ldw + c;
+  float4 acc = *reinterpret_cast<const float4*>(src);
+  for (int s = 1; s < k_splits; ++s) {
+    const float4 v = *reinterpret_cast<const float4*>(src + (int64_t)s * split_stride);
+    acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+  }
+  if constexpr (OUT_F32) {
+    *reinterpret_cast<float4*>(reinterpret_cast<float*>(Cptr) + r * ldc + c) = acc;
+  } else {
+    __nv_bfloat162 lo = __floats2bfloat162_rn(acc.x, acc.y), hi = __floats2bfloat162_rn(acc.z, acc.w);
+    uint2 p = make_uint2(*reinterpret_cast<uint32_t*>(&lo), *reinterpret_cast<uint32_t*>(&hi));
+    *reinterpret_cast<uint2*>(reinterpret_cast<__nv_bfloat16*>(Cptr) + r * ldc + c) = p;
   }
 }
 

@@ -131,6 +131,9 @@ static int launch_bf16(const Bf16Args& a) {
   shape.K = (int)a.K;
   shape.tiles_m = (int)ceil_div64(a.M, kBlockM * CG);
   shape.tiles_n = (int)ceil_div64(a.N, kBlockN);
+  shape.k_splits = 1;
+  shape.kb_per_split = 0;
+  shape.split_stride = 0;
   const int64_t num_tiles = (int64_t)shape.tiles_m * shape.tiles_n;
   if (num_tiles > 0x7fffffff) return fail(GEMM_B200_ERR_TOO_LARGE, "gemm_bf16: too many tiles");
   const int clusters = (int)(num_tiles < max_clusters ? num_tiles : max_clusters);
@@ -263,6 +266,8 @@ struct MxArgs {
   void* C;
   int64_t M, N, K, ldc;
   cudaStream_t stream;
+  int k_splits = 1;        // > 1: FP32 partials go to `scratch` ([k_splits][M][N]), then a reduce pass
+  float* scratch = nullptr;
 };
 
 // packed scale buffer of `rows` rows viewed as int32 [row blocks][kchunks * 128]
@@ -333,7 +338,11 @@ static int launch_mxfp8(const MxArgs& a) {
   shape.K = (int)a.K;
   shape.tiles_m = (int)ceil_div64(a.M, kBlockM * CG);
   shape.tiles_n = (int)ceil_div64(a.N, kBlockN);
-  const int64_t num_tiles = (int64_t)shape.tiles_m * shape.tiles_n;
+  const int num_kb = (int)ceil_div64(a.K, kMxBlockK);
+  shape.kb_per_split = (int)ceil_div64(num_kb, a.k_splits);
+  shape.k_splits = (int)ceil_div64(num_kb, shape.kb_per_split);   // no empty split
+  shape.split_stride = a.M * a.N;
+  const int64_t num_tiles = (int64_t)shape.tiles_m * shape.tiles_n * shape.k_splits;
   if (num_tiles > 0x7fffffff) return fail(GEMM_B200_ERR_TOO_LARGE, "gemm_mxfp8: too many tiles");
   const int clusters = (int)(num_tiles < max_clusters ? num_tiles : max_clusters);
   cudaLaunchConfig_t cfg = {};
@@ -352,6 +361,64 @@ static int launch_mxfp8(const MxArgs& a) {
   int64_t ldc = a.ldc;
   GEMM_B200_CUDA_TRY(cudaLaunchKernelEx(&cfg, kern, tmA, tmB, tmSFA, tmSFB, cptr, ldc, shape));
   launch_counter().fetch_add(1, std::memory_order_relaxed);
+  return GEMM_B200_OK;
+}
+
+// Split-K: FP32 partial sums of every (tile, K split) into scratch, then one reduce pass into C.
+template <class Cfg>
+static int launch_mxfp8_splitk(const MxArgs& a, int out_dtype) {
+  MxArgs part = a;
+  part.C = a.scratch;
+  part.ldc = a.N;
+  if (int rc = launch_mxfp8<Cfg, true>(part)) return rc;
+  const int num_kb = (int)ceil_div64(a.K, kMxBlockK);
+  const int kb_per = (int)ceil_div64(num_kb, a.k_splits);
+  const int splits = (int)ceil_div64(num_kb, kb_per);
+  const int64_t threads = a.M * (a.N / 4);
+  const unsigned blocks = (unsigned)ceil_div64(threads, 256);
+  if (out_dtype == GEMM_B200_OUT_F32)
+    splitk_reduce_kernel<true><<<blocks, 256, 0, a.stream>>>(a.scratch, a.M * a.N, a.N, splits, a.C, a.ldc, (int)a.M, (int)a.N);
+  else
+    splitk_reduce_kernel<false><<<blocks, 256, 0, a.stream>>>(a.scratch, a.M * a.N, a.N, splits, a.C, a.ldc, (int)a.M, (int)a.N);
+  launch_counter().fetch_add(1, std::memory_order_relaxed);
+  GEMM_B200_CUDA_TRY(cudaGetLastError());
+  return GEMM_B200_OK;
+}
+
+// Number of K splits for a problem whose tiles alone do not fill the GPU: the split count that
+// wastes the fewest CTA slots in the last round, mildly preferring fewer splits (each split
+// writes and re-reads an M x N FP32 slice).  1 = do not split.
+static int auto_splits(int64_t M, int64_t N, int64_t K, int sms) {
+  const int64_t tiles = ceil_div64(M, kBlockM) * ceil_div64(N, kBlockN);
+  const int64_t num_kb = ceil_div64(K, kMxBlockK);
+  if (tiles >= sms || num_kb < 8) return 1;
+  int best = 1;
+  double best_score = (double)tiles / (double)(ceil_div64(tiles, sms) * sms);
+  for (int s = 2; s <= 16 && num_kb / s >= 4; ++s) {
+    const int64_t kb_per = ceil_div64(num_kb, s);
+    if (ceil_div64(num_kb, kb_per) != s) continue;
+    const int64_t units = tiles * s;
+    const double score = (double)units / (double)(ceil_div64(units, sms) * sms) - 0.01 * s;
+    if (score > best_score + 1e-9) { best_score = score; best = s; }
+  }
+  return best;
+}
+
+// library-owned scratch for the automatic split-K path, one buffer per device, grown on demand
+static std::mutex g_scratch_mu;
+static void* g_scratch[64] = {nullptr};
+static size_t g_scratch_bytes[64] = {0};
+static int cached_scratch(int dev, size_t bytes, float** out) {
+  std::lock_guard<std::mutex> lk(g_scratch_mu);
+  const int slot = dev & 63;
+  if (g_scratch_bytes[slot] < bytes) {
+    if (g_scratch[slot]) GEMM_B200_CUDA_TRY(cudaFree(g_scratch[slot]));
+    g_scratch[slot] = nullptr;
+    g_scratch_bytes[slot] = 0;
+    GEMM_B200_CUDA_TRY(cudaMalloc(&g_scratch[slot], bytes));
+    g_scratch_bytes[slot] = bytes;
+  }
+  *out = static_cast<float*>(g_scratch[slot]);
   return GEMM_B200_OK;
 }
 
@@ -443,9 +510,68 @@ extern "C" int gemm_b200_gemm_mxfp8_cfg(const void* Aq, const void* SFA, const v
   if (int rc = tc::device_info(&di)) return rc;
   if (di.cc_major != 10)
     return fail(GEMM_B200_ERR_UNSUPPORTED, "gemm_mxfp8: device has compute capability %d.x, need 10.x (sm_100a)", di.cc_major);
-  if (config < 0) config = (M <= 128) ? tc::kSkinnyMxConfig : tc::kDefaultMxConfig;
   tc::MxArgs args{Aq, SFA, Bq, SFB, C, M, N, K, ldc, st};
+  if (config < 0) {
+    if (M <= 128) {
+      // skinny: single-CTA tiles, and K splits when the column tiles alone leave SMs idle
+      const int splits = tc::auto_splits(M, N, K, di.sms);
+      if (splits > 1) {
+        if (int rc = tc::cached_scratch(di.dev, (size_t)splits * M * N * sizeof(float), &args.scratch)) return rc;
+        args.k_splits = splits;
+        return tc::launch_mxfp8_splitk<tc::Mx_1cta>(args, out_dtype);
+      }
+      config = tc::kSkinnyMxConfig;
+    } else {
+      config = tc::kDefaultMxConfig;
+    }
+  }
   return tc::kMxConfigs[config].launch[out_dtype](args);
+}
+
+extern "C" int gemm_b200_gemm_mxfp8_auto_splits(int64_t M, int64_t N, int64_t K) {
+  gemm_b200::tc::DeviceInfo di;
+  if (gemm_b200::tc::device_info(&di)) return 1;
+  return gemm_b200::tc::auto_splits(M, N, K, di.sms);
+}
+
+extern "C" size_t gemm_b200_gemm_mxfp8_splitk_scratch_bytes(int64_t M, int64_t N, int k_splits) {
+  if (M <= 0 || N <= 0 || k_splits <= 1) return 0;
+  return (size_t)k_splits * (size_t)M * (size_t)N * sizeof(float);
+}
+
+extern "C" int gemm_b200_gemm_mxfp8_splitk(const void* Aq, const void* SFA, const void* Bq, const void* SFB, void* C,
+                                           int64_t M, int64_t N, int64_t K, int64_t ldc, int out_dtype, int k_splits,
+                                           void* scratch, size_t scratch_bytes, void* stream) {
+  using namespace gemm_b200;
+  if (k_splits < 1 || k_splits > 64) return fail(GEMM_B200_ERR_INVALID_ARG, "gemm_mxfp8_splitk: k_splits %d not in [1, 64]", k_splits);
+  if (k_splits == 1 || M == 0 || N == 0 || K == 0)
+    return gemm_b200_gemm_mxfp8_cfg(Aq, SFA, Bq, SFB, C, M, N, K, ldc, out_dtype, tc::kSkinnyMxConfig, stream);
+  // same argument checks as the unsplit entry point
+  if (M < 0 || N < 0 || K < 0) return fail(GEMM_B200_ERR_INVALID_ARG, "gemm_mxfp8_splitk: negative size");
+  if (out_dtype != GEMM_B200_OUT_BF16 && out_dtype != GEMM_B200_OUT_F32)
+    return fail(GEMM_B200_ERR_INVALID_ARG, "gemm_mxfp8_splitk: out_dtype %d", out_dtype);
+  if (!C || !Aq || !Bq || !SFA || !SFB || !scratch) return fail(GEMM_B200_ERR_INVALID_ARG, "gemm_mxfp8_splitk: null pointer");
+  if (ldc < N) return fail(GEMM_B200_ERR_INVALID_ARG, "gemm_mxfp8_splitk: ldc smaller than N");
+  if (K % 32 != 0) return fail(GEMM_B200_ERR_INVALID_ARG, "gemm_mxfp8_splitk: K=%lld is not a multiple of 32", (long long)K);
+  if (M > 0x7fffffff || N > 0x7fffffff || K > 0x7fffffff)
+    return fail(GEMM_B200_ERR_TOO_LARGE, "gemm_mxfp8_splitk: a dimension exceeds 2^31-1");
+  const int c_elem = out_dtype == GEMM_B200_OUT_F32 ? 4 : 2;
+  if ((reinterpret_cast<uintptr_t>(Aq) | reinterpret_cast<uintptr_t>(Bq) | reinterpret_cast<uintptr_t>(C) |
+       reinterpret_cast<uintptr_t>(SFA) | reinterpret_cast<uintptr_t>(SFB) | reinterpret_cast<uintptr_t>(scratch)) % 16 != 0)
+    return fail(GEMM_B200_ERR_ALIGNMENT, "gemm_mxfp8_splitk: all pointers must be 16-byte aligned");
+  if ((ldc * c_elem) % 16 != 0 || N % 8 != 0)
+    return fail(GEMM_B200_ERR_ALIGNMENT, "gemm_mxfp8_splitk: ldc*sizeof(C) must be a multiple of 16 bytes and N of 8");
+  const size_t need = gemm_b200_gemm_mxfp8_splitk_scratch_bytes(M, N, k_splits);
+  if (scratch_bytes < need)
+    return fail(GEMM_B200_ERR_INVALID_ARG, "gemm_mxfp8_splitk: scratch holds %zu bytes, %zu needed", scratch_bytes, need);
+  tc::DeviceInfo di;
+  if (int rc = tc::device_info(&di)) return rc;
+  if (di.cc_major != 10)
+    return fail(GEMM_B200_ERR_UNSUPPORTED, "gemm_mxfp8_splitk: device has compute capability %d.x, need 10.x (sm_100a)", di.cc_major);
+  tc::MxArgs args{Aq, SFA, Bq, SFB, C, M, N, K, ldc, static_cast<cudaStream_t>(stream)};
+  args.k_splits = k_splits;
+  args.scratch = static_cast<float*>(scratch);
+  return tc::launch_mxfp8_splitk<tc::Mx_1cta>(args, out_dtype);
 }
 extern "C" int gemm_b200_gemm_mxfp8(const void* Aq, const void* SFA, const void* Bq, const void* SFB, void* C, int64_t M,
                                     int64_t N, int64_t K, int64_t ldc, int out_dtype, void* stream) {

@@ -16,7 +16,7 @@ from ._lib import lib, check
 __all__ = [
     "sgemm_f32", "gemm_bf16", "check_status", "sgemm_f32_host", "gemm_bf16_host",
     "sgemm_f32_configs", "gemm_bf16_configs", "launch_count",
-    "quantize_mxfp8", "gemm_mxfp8", "gemm_mxfp8_configs", "MxFp8Tensor",
+    "quantize_mxfp8", "gemm_mxfp8", "gemm_mxfp8_configs", "MxFp8Tensor", "gemm_mxfp8_splitk", "gemm_mxfp8_auto_splits",
 ]
 
 
@@ -176,6 +176,28 @@ def gemm_mxfp8(A: MxFp8Tensor, B: MxFp8Tensor, out: torch.Tensor | None = None, 
                                            _lib.OUT_F32 if out_dtype == torch.float32 else _lib.OUT_BF16, config,
                                            _stream(A.data)))
     return out
+
+
+def gemm_mxfp8_splitk(A: MxFp8Tensor, B: MxFp8Tensor, k_splits: int, out: torch.Tensor | None = None, *,
+                      out_dtype: torch.dtype = torch.bfloat16, scratch: torch.Tensor | None = None) -> torch.Tensor:
+    """Split-K form with a caller-owned scratch tensor (allocated here when not given)."""
+    _require(A.K == B.K, f"K mismatch: {A.K} vs {B.K}")
+    M, N, K = A.rows, B.rows, A.K
+    if out is None:
+        out = torch.empty((M, N), device=A.data.device, dtype=out_dtype)
+    need = int(lib.gemm_b200_gemm_mxfp8_splitk_scratch_bytes(M, N, k_splits))
+    if scratch is None:
+        scratch = torch.empty((max(need, 16),), device=A.data.device, dtype=torch.uint8)
+    with torch.cuda.device(A.data.device):
+        check(lib.gemm_b200_gemm_mxfp8_splitk(A.data.data_ptr(), A.scales.data_ptr(), B.data.data_ptr(), B.scales.data_ptr(),
+                                              out.data_ptr(), M, N, K, _row_major_ld(out),
+                                              _lib.OUT_F32 if out_dtype == torch.float32 else _lib.OUT_BF16, k_splits,
+                                              scratch.data_ptr(), scratch.numel() * scratch.element_size(), _stream(A.data)))
+    return out
+
+
+def gemm_mxfp8_auto_splits(M: int, N: int, K: int) -> int:
+    return int(lib.gemm_b200_gemm_mxfp8_auto_splits(M, N, K))
 
 
 def gemm_mxfp8_configs() -> list[str]:

@@ -119,6 +119,17 @@ int gemm_b200_gemm_mxfp8(const void* Aq, const void* SFA, const void* Bq, const 
 int gemm_b200_gemm_mxfp8_cfg(const void* Aq, const void* SFA, const void* Bq, const void* SFB,
                              void* C, int64_t M, int64_t N, int64_t K, int64_t ldc,
                              int out_dtype, int config, void* stream);
+/* Split-K form for problems with few output tiles (skinny M): every tile is cut into `k_splits`
+ * ranges of K whose FP32 partial sums go to `scratch` ([k_splits][M][N] floats, device memory,
+ * 16-byte aligned, at least gemm_b200_gemm_mxfp8_splitk_scratch_bytes() bytes) and are then
+ * summed in ascending split order into C by a second kernel.  gemm_b200_gemm_mxfp8() takes this
+ * path by itself for M <= 128, with a library-owned scratch buffer and the split count of
+ * gemm_b200_gemm_mxfp8_auto_splits().  No counterpart in the reference. */
+int gemm_b200_gemm_mxfp8_splitk(const void* Aq, const void* SFA, const void* Bq, const void* SFB,
+                                void* C, int64_t M, int64_t N, int64_t K, int64_t ldc, int out_dtype,
+                                int k_splits, void* scratch, size_t scratch_bytes, void* stream);
+size_t gemm_b200_gemm_mxfp8_splitk_scratch_bytes(int64_t M, int64_t N, int k_splits);
+int gemm_b200_gemm_mxfp8_auto_splits(int64_t M, int64_t N, int64_t K);
 int gemm_b200_gemm_mxfp8_num_configs(void);
 const char* gemm_b200_gemm_mxfp8_config_name(int config);
 

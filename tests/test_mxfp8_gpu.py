@@ -113,3 +113,44 @@ def test_config4_shapes_sampled(ops, oracle):
         assert oracle.rel_frobenius(C[rows][:, cols].cpu(), want) <= REL_TOL
         del A, B, Aq, Bq, C
         torch.cuda.empty_cache()
+
+
+@pytest.mark.parametrize("M,K,N,splits", [(16, 8192, 512, 5), (16, 2048, 264, 2), (100, 1024, 1000, 7), (128, 4096, 256, 16), (1, 1024, 8, 3)])
+def test_splitk_matches_the_oracle(ops, oracle, M, K, N, splits):
+    A, B = oracle.gen_randn_bf16(M, K, N, seed=splits)
+    Aq = ops.quantize_mxfp8(A.cuda()); Bq = ops.quantize_mxfp8(B.cuda(), transposed_in=True)
+    qa, sa = oracle.mxfp8_quantize(A); qb, sb = oracle.mxfp8_quantize(B.t().contiguous())
+    want = oracle.mxfp8_matmul_oracle(qa, sa, qb, sb)
+    got32 = ops.gemm_mxfp8_splitk(Aq, Bq, splits, out_dtype=torch.float32)
+    ops.check_status()
+    assert oracle.rel_frobenius(got32.cpu(), want) <= REL_TOL
+    got16 = ops.gemm_mxfp8_splitk(Aq, Bq, splits, out_dtype=torch.bfloat16)
+    assert torch.equal(got16.cpu(), got32.bfloat16().cpu())
+    # same bits on a second run (partials are summed in a fixed order)
+    assert torch.equal(ops.gemm_mxfp8_splitk(Aq, Bq, splits, out_dtype=torch.float32), got32)
+
+
+def test_skinny_default_takes_the_splitk_path(ops, oracle):
+    M, K, N = 16, 8192, 28672
+    splits = ops.gemm_mxfp8_auto_splits(M, N, K)
+    assert splits > 1
+    g = torch.Generator(device="cuda").manual_seed(0)
+    A = torch.randn(M, K, device="cuda", generator=g).bfloat16()
+    B = torch.randn(K, N, device="cuda", generator=g).bfloat16()
+    Aq = ops.quantize_mxfp8(A); Bq = ops.quantize_mxfp8(B, transposed_in=True)
+    auto = ops.gemm_mxfp8(Aq, Bq, out_dtype=torch.float32)
+    explicit = ops.gemm_mxfp8_splitk(Aq, Bq, splits, out_dtype=torch.float32)
+    ops.check_status()
+    assert torch.equal(auto, explicit)
+    unsplit = ops.gemm_mxfp8(Aq, Bq, out_dtype=torch.float32, config=0)
+    assert oracle.rel_frobenius(auto.cpu(), unsplit.cpu()) <= 1e-5      # only the summation order differs
+
+
+def test_splitk_rejects_a_small_scratch(ops):
+    import gemm_b200._lib as L
+    A = torch.zeros(16, 1024, device="cuda", dtype=torch.bfloat16)
+    B = torch.zeros(1024, 256, device="cuda", dtype=torch.bfloat16)
+    Aq = ops.quantize_mxfp8(A); Bq = ops.quantize_mxfp8(B, transposed_in=True)
+    with pytest.raises(L.GemmB200Error) as e:
+        ops.gemm_mxfp8_splitk(Aq, Bq, 4, scratch=torch.empty(1024, device="cuda", dtype=torch.uint8))
+    assert e.value.code == L.ERR_INVALID_ARG
