@@ -582,3 +582,60 @@ extern "C" const char* gemm_b200_gemm_mxfp8_config_name(int config) {
   if (config < 0 || config >= gemm_b200::tc::kNumMxConfigs) return "";
   return gemm_b200::tc::kMxConfigs[config].name;
 }
+
+// =========================================================================================
+// Split-K MXFP8 GEMM on a scratch buffer that is part of the library image
+// =========================================================================================
+// The FP32 partial sums of the split-K path normally live in memory somebody allocates: the
+// caller (gemm_b200_gemm_mxfp8_splitk) or the library on first use (gemm_b200_gemm_mxfp8).
+// This entry point is for callers that can do neither on their call path: a serving loop that
+// handed all of HBM to its own pool at start-up (a later cudaMalloc fails, and even when it
+// succeeds it synchronises the whole device), or a plugin host whose execute callback forbids
+// allocation.  The scratch is a fixed array in the library's device image, so every GPU that
+// loads the library carries GEMM_B200_STATIC_SCRATCH_BYTES of it until the process exits.
+namespace gemm_b200 {
+namespace tc {
+
+static __device__ __align__(256) float g_static_scratch[GEMM_B200_STATIC_SCRATCH_BYTES / sizeof(float)];
+
+// In host code `g_static_scratch` is only a handle for the runtime, not a device address; the
+// address kernels can use comes from cudaGetSymbolAddress, looked up once per device with that
+// device current.
+static std::mutex g_static_mu;
+static float* g_static_ptr[64] = {nullptr};
+
+static int static_scratch_for_current_device(float** out) {
+  int dev = 0;
+  GEMM_B200_CUDA_TRY(cudaGetDevice(&dev));
+  std::lock_guard<std::mutex> lk(g_static_mu);
+  const int slot = dev & 63;
+  if (!g_static_ptr[slot]) {
+    void* p = nullptr;
+    GEMM_B200_CUDA_TRY(cudaGetSymbolAddress(&p, g_static_scratch));
+    g_static_ptr[slot] = static_cast<float*>(p);
+  }
+  *out = g_static_ptr[slot];
+  return GEMM_B200_OK;
+}
+
+}  // namespace tc
+}  // namespace gemm_b200
+
+extern "C" int gemm_b200_gemm_mxfp8_splitk_static(const void* Aq, const void* SFA, const void* Bq, const void* SFB,
+                                                  void* C, int64_t M, int64_t N, int64_t K, int64_t ldc, int out_dtype,
+                                                  int k_splits, void* stream) {
+  using namespace gemm_b200;
+  if (M < 0 || N < 0 || K < 0) return fail(GEMM_B200_ERR_INVALID_ARG, "gemm_mxfp8_splitk_static: negative size");
+  if (k_splits > 64) return fail(GEMM_B200_ERR_INVALID_ARG, "gemm_mxfp8_splitk_static: k_splits %d above 64", k_splits);
+  if (k_splits <= 0) k_splits = gemm_b200_gemm_mxfp8_auto_splits(M, N, K);
+  const size_t need = gemm_b200_gemm_mxfp8_splitk_scratch_bytes(M, N, k_splits);
+  if (need > (size_t)GEMM_B200_STATIC_SCRATCH_BYTES)
+    return fail(GEMM_B200_ERR_TOO_LARGE,
+                "gemm_mxfp8_splitk_static: %d splits of a %lld x %lld result need %zu bytes of scratch, the built-in "
+                "buffer holds %zu; use gemm_b200_gemm_mxfp8_splitk with your own scratch",
+                k_splits, (long long)M, (long long)N, need, (size_t)GEMM_B200_STATIC_SCRATCH_BYTES);
+  float* scratch = nullptr;
+  if (int rc = tc::static_scratch_for_current_device(&scratch)) return rc;
+  return gemm_b200_gemm_mxfp8_splitk(Aq, SFA, Bq, SFB, C, M, N, K, ldc, out_dtype, k_splits, scratch,
+                                     (size_t)GEMM_B200_STATIC_SCRATCH_BYTES, stream);
+}

@@ -129,6 +129,26 @@ int gemm_b200_gemm_mxfp8_splitk(const void* Aq, const void* SFA, const void* Bq,
                                 void* C, int64_t M, int64_t N, int64_t K, int64_t ldc, int out_dtype,
                                 int k_splits, void* scratch, size_t scratch_bytes, void* stream);
 size_t gemm_b200_gemm_mxfp8_splitk_scratch_bytes(int64_t M, int64_t N, int k_splits);
+
+/* The same split-K GEMM for callers that cannot allocate device memory where they call it: a
+ * serving loop that gave all of HBM to its own pool at start-up (cudaMalloc would fail there, and
+ * it synchronises the device even when it succeeds), or a plugin host that forbids allocation
+ * inside its execute callback.  It has no counterpart in the reference.
+ *   - The FP32 partial sums go to a GEMM_B200_STATIC_SCRATCH_BYTES array built into the library's
+ *     device image; every GPU that loads the library holds that much until the process exits.
+ *   - Limit: k_splits * M * N * 4 bytes must fit (k_splits <= 0 picks the library's split count);
+ *     larger problems get GEMM_B200_ERR_TOO_LARGE and should use gemm_b200_gemm_mxfp8_splitk.
+ *   - The call performs no cudaMalloc / cudaFree and calls no allocating library routine.
+ *   - The first call on each device looks the array's device address up; make that first call
+ *     before starting any stream capture on that device.
+ *   - All calls on a device share the one array, which keeps whatever the last call left there
+ *     (nothing in it has to start at zero: every value read is written by the same call first).
+ *     Two calls whose kernels can overlap on the GPU (different streams) race on it; keep them on
+ *     one stream or order them with events. */
+#define GEMM_B200_STATIC_SCRATCH_BYTES (16u << 20)
+int gemm_b200_gemm_mxfp8_splitk_static(const void* Aq, const void* SFA, const void* Bq, const void* SFB,
+                                       void* C, int64_t M, int64_t N, int64_t K, int64_t ldc,
+                                       int out_dtype, int k_splits, void* stream);
 int gemm_b200_gemm_mxfp8_auto_splits(int64_t M, int64_t N, int64_t K);
 int gemm_b200_gemm_mxfp8_num_configs(void);
 const char* gemm_b200_gemm_mxfp8_config_name(int config);
