@@ -58,15 +58,28 @@ struct GemmShape {
   // scratch buffer [k_splits][M][ldc].  k_splits == 1: the tile's result goes straight to C.
   int k_splits, kb_per_split;
   int64_t split_stride;   // elements between scratch slices
+  // raster: tiles are walked in bands of `raster_group` row tiles (> 0: a band spans all column
+  // tiles, row index fastest) or of `-raster_group` column tiles (< 0: a band spans all row tiles,
+  // column index fastest); the operand panel of the band stays in L2 while the other streams.
+  int raster_group;
 };
 
-__device__ __forceinline__ void tile_coord(int t, int tiles_m, int tiles_n, int& tm, int& tn) {
-  constexpr int GROUP = 8;
-  const int width = GROUP * tiles_n;
-  const int first_m = (t / width) * GROUP;
-  const int gsz = min(tiles_m - first_m, GROUP);
-  tm = first_m + (t % width) % gsz;
-  tn = (t % width) / gsz;
+__device__ __forceinline__ void tile_coord(int t, const GemmShape& sh, int& tm, int& tn) {
+  if (sh.raster_group > 0) {
+    const int group = sh.raster_group;
+    const int width = group * sh.tiles_n;
+    const int first_m = (t / width) * group;
+    const int gsz = min(sh.tiles_m - first_m, group);
+    tm = first_m + (t % width) % gsz;
+    tn = (t % width) / gsz;
+  } else {
+    const int group = -sh.raster_group;
+    const int width = group * sh.tiles_m;
+    const int first_n = (t / width) * group;
+    const int gsz = min(sh.tiles_n - first_n, group);
+    tn = first_n + (t % width) % gsz;
+    tm = (t % width) / gsz;
+  }
 }
 
 template <class Cfg, bool B_MN, bool OUT_F32>
@@ -130,10 +143,14 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
     if (lane == 0) {
+      auto load = [&](uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
+        if constexpr (CG == 1) tma_load_2d(dst, map, x, y, bar);
+        else tma_load_2d_pair(dst, map, x, y, bar);
+      };
       uint32_t it = 0;
       for (int t = cluster_id; t < num_tiles && !failed; t += num_clusters) {
         int tm, tn;
-        tile_coord(t, shape.tiles_m, shape.tiles_n, tm, tn);
+        tile_coord(t, shape, tm, tn);
         const int m0 = (tm * CG + (int)cta_rank) * kBlockM;
         const int n0 = tn * kBlockN + (int)cta_rank * Cfg::BN_CTA;
         for (int kb = 0; kb < num_kb; ++kb, ++it) {
@@ -141,28 +158,15 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           const uint32_t ph = (it / STAGES) & 1u;
           if (!mbar_wait(empty_bar(s), ph ^ 1u, kRoleProducer, s)) { failed = true; break; }
           const uint32_t a_dst = sA0 + s * Cfg::A_BYTES, b_dst = sB0 + s * Cfg::B_BYTES;
-          if constexpr (CG == 1) {
-            mbar_arrive_expect_tx(full_bar(s), Cfg::STAGE_BYTES);
-            tma_load_2d(a_dst, &tmA, kb * kBlockK, m0, full_bar(s));
-            if constexpr (B_MN) {
+          // Both CTAs of a pair report their bytes to the leader's barrier.
+          const uint32_t bar = (CG == 1) ? full_bar(s) : map_to_cta(full_bar(s), 0);
+          if (cta_rank == 0) mbar_arrive_expect_tx(full_bar(s), CG * Cfg::STAGE_BYTES);
+          load(a_dst, &tmA, kb * kBlockK, m0, bar);
+          if constexpr (B_MN) {
 #pragma unroll
-              for (int j = 0; j < Cfg::BN_CTA / 64; ++j)
-                tma_load_2d(b_dst + j * 8192, &tmB, n0 + j * 64, kb * kBlockK, full_bar(s));
-            } else {
-              tma_load_2d(b_dst, &tmB, kb * kBlockK, n0, full_bar(s));
-            }
+            for (int j = 0; j < Cfg::BN_CTA / 64; ++j) load(b_dst + j * 8192, &tmB, n0 + j * 64, kb * kBlockK, bar);
           } else {
-            // Both CTAs of the pair report their bytes to the leader's barrier.
-            const uint32_t lead_full = map_to_cta(full_bar(s), 0);
-            if (cta_rank == 0) mbar_arrive_expect_tx(full_bar(s), 2 * Cfg::STAGE_BYTES);
-            tma_load_2d_pair(a_dst, &tmA, kb * kBlockK, m0, lead_full);
-            if constexpr (B_MN) {
-#pragma unroll
-              for (int j = 0; j < Cfg::BN_CTA / 64; ++j)
-                tma_load_2d_pair(b_dst + j * 8192, &tmB, n0 + j * 64, kb * kBlockK, lead_full);
-            } else {
-              tma_load_2d_pair(b_dst, &tmB, kb * kBlockK, n0, lead_full);
-            }
+            load(b_dst, &tmB, kb * kBlockK, n0, bar);
           }
         }
       }
@@ -218,7 +222,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     uint32_t acc_it = 0, store_it = 0;
     for (int t = cluster_id; t < num_tiles && !failed; t += num_clusters, ++acc_it) {
       int tm, tn;
-      tile_coord(t, shape.tiles_m, shape.tiles_n, tm, tn);
+      tile_coord(t, shape, tm, tn);
       const int m0 = (tm * CG + (int)cta_rank) * kBlockM + quad * 32;   // first row of this warp
       const int n0 = tn * kBlockN;
       const uint32_t acc = acc_it & 1u, aph = (acc_it >> 1) & 1u;

@@ -120,7 +120,7 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
       for (int u = cluster_id; u < num_units && !failed; u += num_clusters) {
         int t, split, kb0, kb1, tm, tn;
         unit_range(u, t, split, kb0, kb1);
-        tile_coord(t, shape.tiles_m, shape.tiles_n, tm, tn);
+        tile_coord(t, shape, tm, tn);
         const int mblk = tm * CG + (int)cta_rank;            // 128-row block of A / C
         const int m0 = mblk * kBlockM;
         const int n0 = tn * kBlockN + (int)cta_rank * Cfg::BN_CTA;
@@ -208,7 +208,7 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
     for (int u = cluster_id; u < num_units && !failed; u += num_clusters, ++acc_it) {
       int t, split, kb0, kb1, tm, tn;
       unit_range(u, t, split, kb0, kb1);
-      tile_coord(t, shape.tiles_m, shape.tiles_n, tm, tn);
+      tile_coord(t, shape, tm, tn);
       const int row = (tm * CG + (int)cta_rank) * kBlockM + quad * 32 + lane;
       const int col0 = tn * kBlockN + half * 128;
       const bool ready = mbar_wait(tfull_bar, acc_it & 1u, kRoleEpilogue, 200);

@@ -81,25 +81,42 @@ quantize_rows_kernel(const __nv_bfloat16* __restrict__ X, int64_t rows, int64_t 
 }
 
 // X [K, rows] row-major (ldx): quantise every column along K, write Xq [rows, K] K-contiguous.
-// A CTA stages a 32 (k) x 128 (columns) tile in shared memory; thread c then owns column c.
-__global__ void __launch_bounds__(128)
+// A CTA of 256 threads stages a 32 (k) x 256 (columns) tile in shared memory with 16-byte loads
+// (thread t loads 8 columns of k row t / 32 ... in four passes), then thread c owns column c:
+// it reads its 32 values down the tile, quantises and writes 32 contiguous bytes of Xq.
+__global__ void __launch_bounds__(256)
 quantize_cols_kernel(const __nv_bfloat16* __restrict__ X, int64_t rows, int64_t K, int64_t ldx,
-                     uint8_t* __restrict__ Xq, uint8_t* __restrict__ SF, int64_t kb_pad) {
-  __shared__ uint16_t tile[32][128 + 2];
-  const int64_t c0 = (int64_t)blockIdx.x * 128, kb = blockIdx.y;
+                     uint8_t* __restrict__ Xq, uint8_t* __restrict__ SF, int64_t kb_pad, int vec_ok) {
+  __shared__ __align__(16) uint16_t tile[32][256 + 8];
+  const int64_t c0 = (int64_t)blockIdx.x * 256, kb = blockIdx.y;
   const int64_t KB = K / 32, kchunks = kb_pad / 4;
   const int t = threadIdx.x;
   const bool kb_ok = kb < KB;
   if (kb_ok) {
     const uint16_t* Xu = reinterpret_cast<const uint16_t*>(X);
+    if (vec_ok) {
+      // 32 threads x 8 columns cover the 256 columns of one k row; 8 k rows per pass
+      const int cg = (t & 31) * 8, kr = t >> 5;
+#pragma unroll
+      for (int p = 0; p < 4; ++p) {
+        const int k = kr + 8 * p;
+        const int64_t c = c0 + cg;
+        uint4 v = make_uint4(0, 0, 0, 0);
+        if (c < rows) v = __ldg(reinterpret_cast<const uint4*>(Xu + (kb * 32 + k) * ldx + c));   // rows % 8 == 0 here
+        *reinterpret_cast<uint4*>(&tile[k][cg]) = v;
+      }
+    } else {
 #pragma unroll 4
-    for (int k = 0; k < 32; ++k) {
-      const int64_t c = c0 + t;
-      tile[k][t] = (c < rows) ? Xu[(kb * 32 + k) * ldx + c] : (uint16_t)0;
+      for (int k = 0; k < 32; ++k) {
+        const int64_t c = c0 + t;
+        tile[k][t] = (c < rows) ? Xu[(kb * 32 + k) * ldx + c] : (uint16_t)0;
+      }
     }
   }
   __syncthreads();
-  const int64_t c = c0 + t;   // column of X = row of Xq; the grid covers columns up to a multiple of 128
+  const int64_t c = c0 + t;   // column of X = row of Xq
+  const int64_t rows_pad = ((rows + 127) / 128) * 128;
+  if (c >= rows_pad) return;
   uint32_t byte = 0;
   if (kb_ok && c < rows) {
     uint32_t w[16], q[8];

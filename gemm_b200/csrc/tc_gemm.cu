@@ -1,6 +1,7 @@
 // Host side of the tensor-core entry points: argument checks, TMA descriptors, persistent
 // grid sizing and launches.  Compiled for sm_100a only (tcgen05 needs the arch-specific target).
 #include <mutex>
+#include <stdlib.h>
 
 #include "gemm_bf16.cuh"
 #include "gemm_mxfp8.cuh"
@@ -41,6 +42,19 @@ static int make_map_2d(CUtensorMap* map, CUtensorMapDataType dt, int elem_bytes,
     return fail(GEMM_B200_ERR_CUDA, "cuTensorMapEncodeTiled failed with CUresult %d (rows=%lld cols=%lld ld=%lld box=%dx%d)",
                 (int)r, (long long)rows, (long long)cols, (long long)ld, box_cols, box_rows);
   return GEMM_B200_OK;
+}
+
+// Band width of the tile raster.  GEMM_B200_RASTER_GROUP overrides it (tuning knob): n > 0 =
+// bands of n row tiles, n < 0 = bands of -n column tiles.
+static int raster_group_for(int tiles_m, int tiles_n) {
+  static const int forced = [] {
+    const char* e = getenv("GEMM_B200_RASTER_GROUP");
+    return e ? atoi(e) : 0;
+  }();
+  if (forced != 0) return forced;
+  (void)tiles_m;
+  (void)tiles_n;
+  return 8;
 }
 
 struct DeviceInfo {
@@ -134,6 +148,7 @@ static int launch_bf16(const Bf16Args& a) {
   shape.k_splits = 1;
   shape.kb_per_split = 0;
   shape.split_stride = 0;
+  shape.raster_group = raster_group_for(shape.tiles_m, shape.tiles_n);
   const int64_t num_tiles = (int64_t)shape.tiles_m * shape.tiles_n;
   if (num_tiles > 0x7fffffff) return fail(GEMM_B200_ERR_TOO_LARGE, "gemm_bf16: too many tiles");
   const int clusters = (int)(num_tiles < max_clusters ? num_tiles : max_clusters);
@@ -342,6 +357,7 @@ static int launch_mxfp8(const MxArgs& a) {
   shape.kb_per_split = (int)ceil_div64(num_kb, a.k_splits);
   shape.k_splits = (int)ceil_div64(num_kb, shape.kb_per_split);   // no empty split
   shape.split_stride = a.M * a.N;
+  shape.raster_group = raster_group_for(shape.tiles_m, shape.tiles_n);
   const int64_t num_tiles = (int64_t)shape.tiles_m * shape.tiles_n * shape.k_splits;
   if (num_tiles > 0x7fffffff) return fail(GEMM_B200_ERR_TOO_LARGE, "gemm_mxfp8: too many tiles");
   const int clusters = (int)(num_tiles < max_clusters ? num_tiles : max_clusters);
@@ -472,9 +488,10 @@ extern "C" int gemm_b200_quantize_mxfp8(const void* X, int64_t rows, int64_t K, 
                                                                kb_pad, rows_pad);
   } else {
     if (kb_pad > 65535) return fail(GEMM_B200_ERR_TOO_LARGE, "quantize_mxfp8: K too large for the transposed path");
-    dim3 grid((unsigned)(rows_pad / 128), (unsigned)kb_pad);
-    mx::quantize_cols_kernel<<<grid, 128, 0, st>>>(static_cast<const __nv_bfloat16*>(X), rows, K, ldx,
-                                                   static_cast<uint8_t*>(Xq), static_cast<uint8_t*>(SF), kb_pad);
+    dim3 grid((unsigned)ceil_div64(rows_pad, 256), (unsigned)kb_pad);
+    const int vec_ok = (reinterpret_cast<uintptr_t>(X) % 16 == 0 && ldx % 8 == 0 && rows % 8 == 0) ? 1 : 0;
+    mx::quantize_cols_kernel<<<grid, 256, 0, st>>>(static_cast<const __nv_bfloat16*>(X), rows, K, ldx,
+                                                   static_cast<uint8_t*>(Xq), static_cast<uint8_t*>(SF), kb_pad, vec_ok);
   }
   launch_counter().fetch_add(1, std::memory_order_relaxed);
   GEMM_B200_CUDA_TRY(cudaGetLastError());

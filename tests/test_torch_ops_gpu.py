@@ -1,0 +1,29 @@
+"""torch.library registration: the custom ops give the same result as the direct calls and can be
+traced with fake tensors."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def test_custom_ops_match_direct_calls(ops, oracle):
+    import gemm_b200.torch_ops  # noqa: F401
+    A, B = oracle.gen_uniform_f32(200, 96, 136, seed=1)
+    got = torch.ops.gemm_b200.sgemm_f32(A.cuda(), B.cuda())
+    assert torch.equal(got.cpu(), oracle.sgemm_seq(A, B))
+    Ab, Bb = oracle.gen_randn_bf16(256, 128, 264, seed=2)
+    c1 = torch.ops.gemm_b200.gemm_bf16(Ab.cuda(), Bb.cuda())
+    assert torch.equal(c1, ops.gemm_bf16(Ab.cuda(), Bb.cuda()))
+    c2 = torch.ops.gemm_b200.gemm_bf16(Ab.cuda(), Bb.t().contiguous().cuda(), True, True)
+    torch.testing.assert_close(c2.cpu(), oracle.bf16_matmul_oracle(Ab, Bb), rtol=2e-2, atol=2e-2)
+
+
+def test_fake_tensor_shapes():
+    import gemm_b200.torch_ops  # noqa: F401
+    from torch._subclasses.fake_tensor import FakeTensorMode
+    with FakeTensorMode():
+        A = torch.empty(64, 32, device="cuda"); B = torch.empty(32, 48, device="cuda")
+        assert torch.ops.gemm_b200.sgemm_f32(A, B).shape == (64, 48)
+        Ab = torch.empty(64, 32, device="cuda", dtype=torch.bfloat16); Bt = torch.empty(48, 32, device="cuda", dtype=torch.bfloat16)
+        out = torch.ops.gemm_b200.gemm_bf16(Ab, Bt, True, True)
+        assert out.shape == (64, 48) and out.dtype == torch.float32
