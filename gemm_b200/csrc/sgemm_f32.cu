@@ -305,10 +305,12 @@ static const ConfigEntry kConfigs[] = {
     {"128x128x32_s3", 128, 128, launch_cfg<C128x128k32>},
 };
 constexpr int kNumConfigs = sizeof(kConfigs) / sizeof(kConfigs[0]);
-constexpr int kCfgLarge = 2, kCfgMedium = 8, kCfgSmall = 11;
+constexpr int kCfgLarge = 2, kCfgMedium = 9, kCfgSmall = 12;
 
-// Heuristic from a sweep of square problems on a B200: 128x128x32 once it yields about four
-// tiles per SM, 64x64 tiles while those still fill the SMs, 32x64 below that.
+// Heuristic from a sweep of square problems on a B200 (TFLOP/s at n = 512 / 1024 / 2048 / 4096 /
+// 8192): 128x128x32: 5 / 22 / 47 / 56 / 56;  64x64x32: 14 / 39 / 53 / 55 / 56;  32x64x32:
+// 16 / 34 / 43 / 44 / 45.  So: 128x128x32 once it yields about four tiles per SM, 64x64x32 while
+// those tiles still fill the SMs, 32x64x32 below that.
 inline int pick_config(int64_t M, int64_t N, int num_sms) {
   const int64_t t128 = ceil_div64(M, 128) * ceil_div64(N, 128);
   if (t128 >= 4 * (int64_t)num_sms) return kCfgLarge;
