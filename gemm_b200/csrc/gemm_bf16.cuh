@@ -35,24 +35,37 @@ constexpr int kGemmThreads = 192;
 
 // EPI: 0 = direct global stores, 1 = swizzled smem staging + TMA store
 // COMMIT_MASK: CTA-pair commits use the masked form (one instruction for both CTAs) instead of two
-template <int CG_, int STAGES_, int EPI_, bool COMMIT_MASK_>
+// NT: column tiles of kBlockN per work unit.
+//   NT = 1: one 256-column accumulator per tile, double-buffered in TMEM (the epilogue of a tile
+//           overlaps the main loop of the next), 4 epilogue warps.
+//   NT = 2: two 256-column accumulators (all 512 TMEM columns) that share the A tile: every A
+//           tile fetched from L2 feeds twice the math, i.e. 25 % fewer operand bytes per flop
+//           (less L2 / fabric power on a power-capped board) at the price of an epilogue that
+//           is not overlapped; 8 epilogue warps keep that short.
+template <int CG_, int STAGES_, int EPI_, bool COMMIT_MASK_, int NT_ = 1, int EPI_BUFS_ = (NT_ == 1 ? 2 : 1)>
 struct Bf16Cfg {
-  static constexpr int CG = CG_, STAGES = STAGES_, EPI = EPI_;
+  static constexpr int CG = CG_, STAGES = STAGES_, EPI = EPI_, NT = NT_;
   static constexpr bool COMMIT_MASK = COMMIT_MASK_;
-  static constexpr int BN_CTA = kBlockN / CG;                       // columns of B each CTA loads
+  static constexpr int ACC_STAGES = (NT == 1) ? 2 : 1;
+  static constexpr int EPI_WARPS = 4 * NT;
+  static constexpr int THREADS = 64 + 32 * EPI_WARPS;
+  static constexpr int EPI_BUFS = EPI_BUFS_;                       // staging buffers per epilogue warp
+  static constexpr int TILE_N = kBlockN * NT;                       // columns of C per work unit
+  static constexpr int BN_CTA = kBlockN / CG;                       // columns of B each CTA loads per column tile
   static constexpr int A_BYTES = kBlockM * kBlockK * 2;             // 16 KB
-  static constexpr int B_BYTES = BN_CTA * kBlockK * 2;              // 32 KB / 16 KB
-  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  static constexpr int B_BYTES = BN_CTA * kBlockK * 2;              // 32 KB / 16 KB, per column tile
+  static constexpr int STAGE_BYTES = A_BYTES + NT * B_BYTES;
   static constexpr int EPI_WARP_BUF = 32 * 128;                     // 32 rows x 128 bytes
-  static constexpr int EPI_BYTES = 4 * 2 * EPI_WARP_BUF;            // 4 warps x 2 buffers
+  static constexpr int EPI_BYTES = EPI_WARPS * EPI_BUFS * EPI_WARP_BUF;
   static constexpr int BAR_BYTES = (2 * STAGES + 4) * 8 + 16;
   static constexpr int SMEM_BYTES = 1024 + STAGES * STAGE_BYTES + EPI_BYTES + BAR_BYTES;
+  static_assert(NT == 1 || NT == 2, "column tiles per unit");
   static_assert(SMEM_BYTES <= 232448, "shared memory budget");
 };
 
 struct GemmShape {
   int M, N, K;
-  int tiles_m, tiles_n;   // tiles of (kBlockM * CG) x kBlockN
+  int tiles_m, tiles_n;   // work units of (kBlockM * CG) rows x (kBlockN * NT) columns
   // split-K (block-scaled kernel only): every tile is cut into k_splits work units of
   // kb_per_split K blocks; unit (tile, split) writes FP32 partial sums to slice `split` of a
   // scratch buffer [k_splits][M][ldc].  k_splits == 1: the tile's result goes straight to C.
@@ -83,15 +96,15 @@ __device__ __forceinline__ void tile_coord(int t, const GemmShape& sh, int& tm, 
 }
 
 template <class Cfg, bool B_MN, bool OUT_F32>
-__global__ void __launch_bounds__(kGemmThreads, 1)
+__global__ void __launch_bounds__(Cfg::THREADS, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                  const __grid_constant__ CUtensorMap tmC, void* __restrict__ Cptr, int64_t ldc,
                  const GemmShape shape) {
-  constexpr int CG = Cfg::CG, STAGES = Cfg::STAGES;
+  constexpr int CG = Cfg::CG, STAGES = Cfg::STAGES, NT = Cfg::NT, ACC_STAGES = Cfg::ACC_STAGES;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   const uint32_t sA0 = smem_base;
-  const uint32_t sB0 = smem_base + STAGES * Cfg::A_BYTES;
+  const uint32_t sB0 = smem_base + STAGES * Cfg::A_BYTES;     // [stage][column tile][B_BYTES]
   const uint32_t sEpi0 = smem_base + STAGES * Cfg::STAGE_BYTES;
   const uint32_t bar0 = sEpi0 + Cfg::EPI_BYTES;
   auto full_bar = [&](int s) { return bar0 + 8u * s; };
@@ -115,7 +128,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(tfull_bar(a), 1);
-      mbar_init(tempty_bar(a), 4 * CG);   // one arrival per epilogue warp of every CTA of the pair
+      mbar_init(tempty_bar(a), Cfg::EPI_WARPS * CG);   // one arrival per epilogue warp of every CTA of the pair
     }
     fence_mbar_init();
   }
@@ -152,21 +165,25 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         int tm, tn;
         tile_coord(t, shape, tm, tn);
         const int m0 = (tm * CG + (int)cta_rank) * kBlockM;
-        const int n0 = tn * kBlockN + (int)cta_rank * Cfg::BN_CTA;
         for (int kb = 0; kb < num_kb; ++kb, ++it) {
           const int s = it % STAGES;
           const uint32_t ph = (it / STAGES) & 1u;
           if (!mbar_wait(empty_bar(s), ph ^ 1u, kRoleProducer, s)) { failed = true; break; }
-          const uint32_t a_dst = sA0 + s * Cfg::A_BYTES, b_dst = sB0 + s * Cfg::B_BYTES;
+          const uint32_t a_dst = sA0 + s * Cfg::A_BYTES;
           // Both CTAs of a pair report their bytes to the leader's barrier.
           const uint32_t bar = (CG == 1) ? full_bar(s) : map_to_cta(full_bar(s), 0);
           if (cta_rank == 0) mbar_arrive_expect_tx(full_bar(s), CG * Cfg::STAGE_BYTES);
           load(a_dst, &tmA, kb * kBlockK, m0, bar);
-          if constexpr (B_MN) {
 #pragma unroll
-            for (int j = 0; j < Cfg::BN_CTA / 64; ++j) load(b_dst + j * 8192, &tmB, n0 + j * 64, kb * kBlockK, bar);
-          } else {
-            load(b_dst, &tmB, kb * kBlockK, n0, bar);
+          for (int nt = 0; nt < NT; ++nt) {
+            const uint32_t b_dst = sB0 + (s * NT + nt) * Cfg::B_BYTES;
+            const int n0 = (tn * NT + nt) * kBlockN + (int)cta_rank * Cfg::BN_CTA;
+            if constexpr (B_MN) {
+#pragma unroll
+              for (int j = 0; j < Cfg::BN_CTA / 64; ++j) load(b_dst + j * 8192, &tmB, n0 + j * 64, kb * kBlockK, bar);
+            } else {
+              load(b_dst, &tmB, kb * kBlockK, n0, bar);
+            }
           }
         }
       }
@@ -192,20 +209,24 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       };
       uint32_t it = 0, acc_it = 0;
       for (int t = cluster_id; t < num_tiles && !failed; t += num_clusters, ++acc_it) {
-        const uint32_t acc = acc_it & 1u, aph = (acc_it >> 1) & 1u;
+        const uint32_t acc = acc_it % ACC_STAGES, aph = (acc_it / ACC_STAGES) & 1u;
         if (!mbar_wait(tempty_bar(acc), aph ^ 1u, kRoleMma, 100 + (int)acc)) { failed = true; break; }
         tc_fence_after_sync();
-        const uint32_t d_tmem = tmem_base + acc * kBlockN;
+        const uint32_t d_tmem = tmem_base + acc * NT * kBlockN;   // NT accumulators of 256 columns
         for (int kb = 0; kb < num_kb; ++kb, ++it) {
           const int s = it % STAGES;
           const uint32_t ph = (it / STAGES) & 1u;
           if (!mbar_wait(full_bar(s), ph, kRoleMma, s)) { failed = true; break; }
           tc_fence_after_sync();
-          const uint32_t a_addr = sA0 + s * Cfg::A_BYTES, b_addr = sB0 + s * Cfg::B_BYTES;
+          const uint32_t a_addr = sA0 + s * Cfg::A_BYTES;
 #pragma unroll
           for (int k = 0; k < kBlockK / kUmmaK; ++k) {
-            mma_f16<CG>(d_tmem, smem_desc(a_hi, a_addr + k * (kUmmaK * 2)), smem_desc(b_hi, b_addr + k * b_kstep),
-                        idesc, (kb | k) != 0 ? 1u : 0u);
+#pragma unroll
+            for (int nt = 0; nt < NT; ++nt) {
+              const uint32_t b_addr = sB0 + (s * NT + nt) * Cfg::B_BYTES;
+              mma_f16<CG>(d_tmem + nt * kBlockN, smem_desc(a_hi, a_addr + k * (kUmmaK * 2)),
+                          smem_desc(b_hi, b_addr + k * b_kstep), idesc, (kb | k) != 0 ? 1u : 0u);
+            }
           }
           commit(empty_bar(s));   // frees the smem slot in both CTAs once these MMAs have read it
         }
@@ -215,23 +236,24 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     }
     __syncwarp();
   } else {
-    // ------------------------------------------------------------------ epilogue warps 2..5
+    // ------------------------------------------------------------------ epilogue warps 2..
     const int quad = warp & 3;   // TMEM lanes [32 quad, 32 quad + 32) are the ones this warp may read
+    const int nt_w = (warp - 2) >> 2;   // which 256-column accumulator this warp drains (0 when NT = 1)
     const uint32_t lane_base = (uint32_t)(quad * 32) << 16;
-    const uint32_t stage0 = sEpi0 + (uint32_t)(warp - 2) * 2u * Cfg::EPI_WARP_BUF;
+    const uint32_t stage0 = sEpi0 + (uint32_t)(warp - 2) * (uint32_t)Cfg::EPI_BUFS * Cfg::EPI_WARP_BUF;
     uint32_t acc_it = 0, store_it = 0;
     for (int t = cluster_id; t < num_tiles && !failed; t += num_clusters, ++acc_it) {
       int tm, tn;
       tile_coord(t, shape, tm, tn);
       const int m0 = (tm * CG + (int)cta_rank) * kBlockM + quad * 32;   // first row of this warp
-      const int n0 = tn * kBlockN;
-      const uint32_t acc = acc_it & 1u, aph = (acc_it >> 1) & 1u;
+      const int n0 = (tn * NT + nt_w) * kBlockN;
+      const uint32_t acc = acc_it % ACC_STAGES, aph = (acc_it / ACC_STAGES) & 1u;
       // every lane waits, and the warp moves on only if every lane saw the phase complete: the
       // TMEM loads below are warp-collective and must not run with part of the warp missing
       const bool ready = mbar_wait(tfull_bar(acc), aph, kRoleEpilogue, 200 + (int)acc);
       if (!__all_sync(0xffffffffu, ready)) { failed = true; break; }
       tc_fence_after_sync();
-      const uint32_t t_addr = tmem_base + lane_base + acc * kBlockN;
+      const uint32_t t_addr = tmem_base + lane_base + (acc * NT + nt_w) * kBlockN;
       const int row = m0 + lane;
 
       if constexpr (Cfg::EPI == 0) {
@@ -271,9 +293,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         constexpr int SLAB_COLS = OUT_F32 ? 32 : 64;
 #pragma unroll 1
         for (int c = 0; c < kBlockN / SLAB_COLS; ++c, ++store_it) {
-          const uint32_t buf = stage0 + (store_it & 1u) * Cfg::EPI_WARP_BUF;
-          // the store that last read this buffer was committed two slabs ago
-          if (lane == 0) tma_store_wait_read<1>();
+          const uint32_t buf = stage0 + (store_it % Cfg::EPI_BUFS) * Cfg::EPI_WARP_BUF;
+          // the store that last read this buffer was committed EPI_BUFS slabs ago
+          if (lane == 0) tma_store_wait_read<Cfg::EPI_BUFS - 1>();
           __syncwarp();
           const uint32_t row_addr = buf + (uint32_t)lane * 128u;
           const uint32_t sw = (uint32_t)(lane & 7);

@@ -248,9 +248,12 @@ struct ConfigEntry {
                 cudaStream_t);
 };
 
+// Internal linkage on purpose: this source is compiled into several modules of one process (the
+// shared library and the three extension modules), each with its own copy of the kernels; the
+// "attribute already set" cache below must not be merged across them by the dynamic linker.
 template <class C>
-int launch_cfg(const float* A, const float* B, float* Cm, int M, int N, int K, int64_t lda,
-               int64_t ldb, int64_t ldc, bool vec, cudaStream_t stream) {
+static int launch_cfg(const float* A, const float* B, float* Cm, int M, int N, int K, int64_t lda,
+                      int64_t ldb, int64_t ldc, bool vec, cudaStream_t stream) {
   const int tiles_m = (M + C::BM - 1) / C::BM, tiles_n = (N + C::BN - 1) / C::BN;
   const int64_t tiles = (int64_t)tiles_m * tiles_n;
   if (tiles == 0) return GEMM_B200_OK;
@@ -258,13 +261,18 @@ int launch_cfg(const float* A, const float* B, float* Cm, int M, int N, int K, i
   auto kv = sgemm_kernel<C, 4>;
   auto ks = sgemm_kernel<C, 1>;
   auto kern = vec ? kv : ks;
-  static thread_local int attr_dev_v = -1, attr_dev_s = -1;
-  int dev = 0;
-  GEMM_B200_CUDA_TRY(cudaGetDevice(&dev));
-  int& attr_dev = vec ? attr_dev_v : attr_dev_s;
-  if (attr_dev != dev) {
-    GEMM_B200_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES));
-    attr_dev = dev;
+  if (C::SMEM_BYTES > 48 * 1024) {
+    // opt in to more than 48 KB of dynamic shared memory, once per (device, kernel)
+    static thread_local int done_dev[2] = {-1, -1};
+    static thread_local const void* done_fn[2] = {nullptr, nullptr};
+    int dev = 0;
+    GEMM_B200_CUDA_TRY(cudaGetDevice(&dev));
+    const int slot = vec ? 0 : 1;
+    if (done_dev[slot] != dev || done_fn[slot] != reinterpret_cast<const void*>(kern)) {
+      GEMM_B200_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES));
+      done_dev[slot] = dev;
+      done_fn[slot] = reinterpret_cast<const void*>(kern);
+    }
   }
   kern<<<(unsigned)tiles, C::THREADS, C::SMEM_BYTES, stream>>>(A, B, Cm, M, N, K, lda, ldb, ldc, tiles_m, tiles_n);
   launch_counter().fetch_add(1, std::memory_order_relaxed);
