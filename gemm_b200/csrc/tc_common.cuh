@@ -101,7 +101,8 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
 }
 // Bounded wait.  Returns false (after recording the place) when the limit ran out or when
 // another wait anywhere on the device has already given up.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int role, int stage) {
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int role, int stage,
+                                          unsigned long long limit_ns = kWaitLimitNs) {
   if (mbar_try_wait(bar, parity)) return true;
   const unsigned long long t0 = globaltimer_ns();
   uint32_t spins = 0;
@@ -109,7 +110,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int rol
     if (mbar_try_wait(bar, parity)) return true;
     if ((++spins & 255u) == 0) {
       if (aborted()) return false;
-      if (globaltimer_ns() - t0 > kWaitLimitNs) {
+      if (globaltimer_ns() - t0 > limit_ns) {
         record_timeout(role, stage);
         return false;
       }

@@ -677,3 +677,40 @@ extern "C" int gemm_b200_gemm_mxfp8_splitk_static(const void* Aq, const void* SF
   return gemm_b200_gemm_mxfp8_splitk(Aq, SFA, Bq, SFB, C, M, N, K, ldc, out_dtype, k_splits, scratch,
                                      (size_t)GEMM_B200_STATIC_SCRATCH_BYTES, stream);
 }
+
+// =========================================================================================
+// Self-test of the bounded-wait / status path
+// =========================================================================================
+namespace gemm_b200 {
+namespace tc {
+
+// One warp waits on an mbarrier that nothing ever arrives on.  The wait gives up after
+// `limit_ns`, records {code, block, role = setup, stage = 777} in the status word and the kernel
+// returns normally — the same path a real kernel takes when a pipeline wait runs out.
+__global__ void __launch_bounds__(32) wait_timeout_selftest_kernel(unsigned long long limit_ns, int* returned_normally) {
+  __shared__ __align__(8) uint64_t bar;
+  const uint32_t b = smem_u32(&bar);
+  if (threadIdx.x == 0) {
+    mbar_init(b, 1);
+    fence_mbar_init();
+  }
+  __syncwarp();
+  bool ok = true;
+  if (threadIdx.x == 0) ok = mbar_wait(b, 0, kRoleSetup, 777, limit_ns);
+  ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+  __syncwarp();
+  if (threadIdx.x == 0) *returned_normally = ok ? 2 : 1;   // 1: the wait ran out and the kernel still got here
+}
+
+}  // namespace tc
+}  // namespace gemm_b200
+
+extern "C" int gemm_b200_selftest_wait_timeout(int64_t limit_us, int* device_flag, void* stream) {
+  using namespace gemm_b200;
+  if (limit_us < 1 || limit_us > 100000) return fail(GEMM_B200_ERR_INVALID_ARG, "selftest_wait_timeout: limit_us must be in [1, 100000]");
+  if (!device_flag) return fail(GEMM_B200_ERR_INVALID_ARG, "selftest_wait_timeout: null flag pointer");
+  tc::wait_timeout_selftest_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>((unsigned long long)limit_us * 1000ull, device_flag);
+  launch_counter().fetch_add(1, std::memory_order_relaxed);
+  GEMM_B200_CUDA_TRY(cudaGetLastError());
+  return GEMM_B200_OK;
+}

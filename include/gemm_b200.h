@@ -174,6 +174,13 @@ int gemm_b200_release_workspace(void);
  * they give up.  Synchronises `stream`.  0 = clean, GEMM_B200_ERR_TIMEOUT
  * otherwise; `detail`, if not NULL, receives {code, block, role, stage}. */
 int gemm_b200_check_status(void* stream, int32_t detail[4]);
+/* Self-test of the bounded-wait machinery: launches one warp that waits `limit_us` microseconds
+ * (1 .. 100000) on a barrier nothing arrives on, then records the give-up in the status word and
+ * returns normally (writing 1 to *device_flag, an int in device memory).  A following
+ * gemm_b200_check_status() must report GEMM_B200_ERR_TIMEOUT with role 4, stage 777, and clears
+ * the status.  Nothing hangs: the kernel ends by itself after `limit_us`.  The reference has no
+ * error path at all (naive/naive_1.cu:23 launches and returns). */
+int gemm_b200_selftest_wait_timeout(int64_t limit_us, int* device_flag, void* stream);
 const char* gemm_b200_last_error(void);
 int gemm_b200_version(void);
 /* 1 if device `dev` can run the tensor-core paths (compute capability 10.x). */
