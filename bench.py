@@ -39,7 +39,7 @@ WORKLOADS = {
 }
 DEFAULT_WORKLOAD = "bf16_rowsharded_131072x8192x8192"
 L2_BYTES = 126 * 1024 * 1024
-TRAFFIC_BYTES_FULL = 26.84e9   # see the roofline block in main()
+TRAFFIC_BYTES_FULL = 19.77e9   # see the roofline block in main()
 
 
 def measured_peaks() -> dict:
@@ -352,7 +352,7 @@ def main() -> int:
     # DRAM bytes of one launch of gemm_bf16_kernel on this workload, from the one-pass capture
     #   ncu --metrics dram__bytes_read.sum,dram__bytes_write.sum --clock-control none \
     #       -k regex:gemm_bf16_kernel -s 3 -c 1 python bench.py --steps 2 --warmup 3 --no-extras
-    # at N = 1 (24.70 GB read + 2.14 GB written); per-rank traffic scales with the rank's rows.
+    # at N = 1 (17.63 GB read + 2.14 GB written); per-rank traffic scales with the rank's rows.
     traffic = (TRAFFIC_BYTES_FULL * shard.rows / M) if args.workload == DEFAULT_WORKLOAD else None
     roofline = {"bound": "tensor", "achieved": round(kernel_tflops, 1), "peak": peak, "unit": "TFLOP/s",
                 "frac": round(kernel_tflops / peak, 4), "traffic": traffic,
