@@ -54,7 +54,9 @@ static int raster_group_for(int tiles_m, int tiles_n) {
   if (forced != 0) return forced;
   (void)tiles_m;
   (void)tiles_n;
-  return 8;
+  // bands of 8 column tiles, walked column-fastest: on B200 this measured 1-5 % faster and
+  // 10-20 % less DRAM traffic than bands of 8 row tiles (8192^3 and 131072 x 8192 x 8192, bf16)
+  return -8;
 }
 
 struct DeviceInfo {
