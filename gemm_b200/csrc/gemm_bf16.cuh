@@ -254,6 +254,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       if (!__all_sync(0xffffffffu, ready)) { failed = true; break; }
       tc_fence_after_sync();
       const uint32_t t_addr = tmem_base + lane_base + (acc * NT + nt_w) * kBlockN;
+      bool released = false;   // TMEM already handed back inside the branch below
       const int row = m0 + lane;
 
       if constexpr (Cfg::EPI == 0) {
@@ -286,6 +287,49 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                 }
               }
             }
+          }
+        }
+      } else if constexpr (ACC_STAGES == 1 && !OUT_F32) {
+        // Single-buffered accumulator: the MMA issuer is waiting for this TMEM.  Pull all 256
+        // columns into registers as packed bf16 first (128 registers), hand TMEM back, and only
+        // then stage and store, so the stores overlap the next tile's main loop.
+        uint32_t packed[kBlockN / 2];
+#pragma unroll
+        for (int c = 0; c < kBlockN / 32; ++c) {
+          uint32_t v[32];
+          tmem_ld_32x32b_x32(t_addr + c * 32, v);
+          tmem_ld_wait();
+#pragma unroll
+          for (int e = 0; e < 16; ++e) {
+            __nv_bfloat162 hh = __floats2bfloat162_rn(__uint_as_float(v[2 * e]), __uint_as_float(v[2 * e + 1]));
+            packed[c * 16 + e] = *reinterpret_cast<uint32_t*>(&hh);
+          }
+        }
+        tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) {
+          if constexpr (CG == 1) mbar_arrive(tempty_bar(acc));
+          else mbar_arrive_cluster(map_to_cta(tempty_bar(acc), 0));
+        }
+        released = true;
+#pragma unroll
+        for (int c = 0; c < kBlockN / 64; ++c, ++store_it) {
+          const uint32_t buf = stage0 + (store_it % Cfg::EPI_BUFS) * Cfg::EPI_WARP_BUF;
+          if (lane == 0) tma_store_wait_read<Cfg::EPI_BUFS - 1>();
+          __syncwarp();
+          const uint32_t row_addr = buf + (uint32_t)lane * 128u;
+          const uint32_t sw = (uint32_t)(lane & 7);
+#pragma unroll
+          for (int j = 0; j < 8; ++j)
+            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(row_addr + (((uint32_t)j ^ sw) << 4)),
+                         "r"(packed[c * 32 + 4 * j]), "r"(packed[c * 32 + 4 * j + 1]), "r"(packed[c * 32 + 4 * j + 2]),
+                         "r"(packed[c * 32 + 4 * j + 3]) : "memory");
+          fence_proxy_async_smem();
+          __syncwarp();
+          const int x = n0 + c * 64;
+          if (lane == 0) {
+            if (m0 < shape.M && x < shape.N) tma_store_2d(&tmC, x, m0, buf);
+            tma_store_commit();
           }
         }
       } else {
@@ -338,11 +382,13 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         }
       }
       // accumulator fully read: hand the TMEM buffer back to the MMA issuer (leader CTA)
-      tc_fence_before_sync();
-      __syncwarp();
-      if (lane == 0) {
-        if constexpr (CG == 1) mbar_arrive(tempty_bar(acc));
-        else mbar_arrive_cluster(map_to_cta(tempty_bar(acc), 0));
+      if (!released) {
+        tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) {
+          if constexpr (CG == 1) mbar_arrive(tempty_bar(acc));
+          else mbar_arrive_cluster(map_to_cta(tempty_bar(acc), 0));
+        }
       }
     }
     if (Cfg::EPI == 1 && lane == 0) tma_store_wait_all<0>();

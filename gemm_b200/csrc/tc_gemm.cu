@@ -214,7 +214,7 @@ constexpr int kBf16Cfg512 = 7;    // CTA pair, 256x512 tiles (A shared by two ac
 // 256x512 tiles move 25 % fewer operand bytes per flop and measure ~4 % faster when both tile
 // shapes fill their rounds equally well; with few tiles the coarser grid wastes more of the last
 // round of the persistent schedule.  Pick by estimated round efficiency.
-static int pick_bf16_config(int64_t M, int64_t N, int sms) {
+static int pick_bf16_config(int64_t M, int64_t N, int64_t K, int sms) {
   const int64_t clusters = sms / 2 > 0 ? sms / 2 : 1;
   auto eff = [&](int64_t tile_n) {
     const int64_t units = ceil_div64(M, 2 * kBlockM) * ceil_div64(N, tile_n);
@@ -222,7 +222,10 @@ static int pick_bf16_config(int64_t M, int64_t N, int sms) {
     const double used = (double)N / (double)(ceil_div64(N, tile_n) * tile_n);   // columns of the last tile in use
     return fill * used;
   };
-  return (1.04 * eff(2 * kBlockN) >= eff(kBlockN)) ? kBf16Cfg512 : kBf16Cfg256;
+  // the 512-wide tile's epilogue is not hidden under a main loop: it pays off from K ~ 4096 up
+  // (8192^2 x K, TFLOP/s 256-wide / 512-wide: K=2048 1607 / 1570, 4096 1627 / 1662, 8192 1591 / 1660)
+  const double gain = K >= 3072 ? 1.04 : 0.97;
+  return (gain * eff(2 * kBlockN) >= eff(kBlockN)) ? kBf16Cfg512 : kBf16Cfg256;
 }
 
 }  // namespace tc
@@ -262,7 +265,7 @@ extern "C" int gemm_b200_gemm_bf16_cfg(const void* A, const void* B, void* C, in
   if (int rc = tc::device_info(&di)) return rc;
   if (di.cc_major != 10)
     return fail(GEMM_B200_ERR_UNSUPPORTED, "gemm_bf16: device has compute capability %d.x, need 10.x (sm_100a)", di.cc_major);
-  if (config < 0) config = tc::pick_bf16_config(M, N, di.sms);
+  if (config < 0) config = tc::pick_bf16_config(M, N, K, di.sms);
   tc::Bf16Args args{A, B, C, M, N, K, lda, ldb, ldc, st};
   return tc::kBf16Configs[config].launch[b_layout][out_dtype](args);
 }
