@@ -31,7 +31,6 @@ constexpr int kBlockN = 256;   // columns of C per MMA (per CTA for CG = 1, per 
 constexpr int kBlockK = 64;    // bf16 elements per 128-byte swizzled row
 constexpr int kUmmaK = 16;
 constexpr int kTmemCols = 512;
-constexpr int kGemmThreads = 192;
 
 // EPI: 0 = direct global stores, 1 = swizzled smem staging + TMA store
 // COMMIT_MASK: CTA-pair commits use the masked form (one instruction for both CTAs) instead of two

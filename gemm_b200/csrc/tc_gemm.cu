@@ -1,7 +1,9 @@
 // Host side of the tensor-core entry points: argument checks, TMA descriptors, persistent
 // grid sizing and launches.  Compiled for sm_100a only (tcgen05 needs the arch-specific target).
+#include <map>
 #include <mutex>
 #include <stdlib.h>
+#include <utility>
 
 #include "gemm_bf16.cuh"
 #include "gemm_mxfp8.cuh"
@@ -75,6 +77,64 @@ static int device_info(DeviceInfo* out) {
   return GEMM_B200_OK;
 }
 
+
+// Number of CTA clusters of `kern` that can be resident at once on the current device (the size
+// of the persistent grid), looked up once per device and kernel.  Also opts the kernel in to its
+// dynamic shared memory size.
+template <class Kern>
+static int persistent_clusters(Kern kern, int cg, int threads, int smem_bytes, const DeviceInfo& di, int* out) {
+  // keyed by (device, kernel): kernels of one signature share this function's instantiation
+  static std::mutex mu;
+  static std::map<std::pair<int, const void*>, int> cache;
+  std::lock_guard<std::mutex> lk(mu);
+  const std::pair<int, const void*> key(di.dev, reinterpret_cast<const void*>(kern));
+  auto hit = cache.find(key);
+  if (hit == cache.end()) {
+    GEMM_B200_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes));
+    int n = di.sms / cg;
+    if (cg > 1) {
+      cudaLaunchConfig_t qc = {};
+      qc.gridDim = dim3((unsigned)(di.sms / cg * cg));
+      qc.blockDim = dim3((unsigned)threads);
+      qc.dynamicSmemBytes = (size_t)smem_bytes;
+      cudaLaunchAttribute qa[1];
+      qa[0].id = cudaLaunchAttributeClusterDimension;
+      qa[0].val.clusterDim.x = (unsigned)cg;
+      qa[0].val.clusterDim.y = 1;
+      qa[0].val.clusterDim.z = 1;
+      qc.attrs = qa;
+      qc.numAttrs = 1;
+      int active = 0;
+      GEMM_B200_CUDA_TRY(cudaOccupancyMaxActiveClusters(&active, kern, &qc));
+      if (active < 1) return fail(GEMM_B200_ERR_CUDA, "no CTA pair of this kernel fits on the device");
+      if (active < n) n = active;
+    }
+    hit = cache.emplace(key, n).first;
+  }
+  *out = hit->second;
+  return GEMM_B200_OK;
+}
+
+// Launches `kern` on `clusters` clusters of `cg` CTAs.
+template <class Kern, class... Args>
+static int launch_clusters(Kern kern, int clusters, int cg, int threads, int smem_bytes, cudaStream_t stream, Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)(clusters * cg));
+  cfg.blockDim = dim3((unsigned)threads);
+  cfg.dynamicSmemBytes = (size_t)smem_bytes;
+  cfg.stream = stream;
+  cudaLaunchAttribute attrs[1];
+  attrs[0].id = cudaLaunchAttributeClusterDimension;
+  attrs[0].val.clusterDim.x = (unsigned)cg;
+  attrs[0].val.clusterDim.y = 1;
+  attrs[0].val.clusterDim.z = 1;
+  cfg.attrs = attrs;
+  cfg.numAttrs = 1;
+  GEMM_B200_CUDA_TRY(cudaLaunchKernelEx(&cfg, kern, args...));
+  launch_counter().fetch_add(1, std::memory_order_relaxed);
+  return GEMM_B200_OK;
+}
+
 struct Bf16Args {
   const void *A, *B;
   void* C;
@@ -110,36 +170,8 @@ static int launch_bf16(const Bf16Args& a) {
   }
 
   auto kern = gemm_bf16_kernel<Cfg, B_MN, OUT_F32>;
-  static std::mutex mu;
-  static int max_clusters_for_dev[64] = {0};
   int max_clusters = 0;
-  {
-    std::lock_guard<std::mutex> lk(mu);
-    const int slot = di.dev & 63;
-    if (max_clusters_for_dev[slot] == 0) {
-      GEMM_B200_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES));
-      int n = di.sms / CG;
-      if (CG > 1) {
-        cudaLaunchConfig_t qc = {};
-        qc.gridDim = dim3((unsigned)(di.sms / CG * CG));
-        qc.blockDim = dim3(Cfg::THREADS);
-        qc.dynamicSmemBytes = Cfg::SMEM_BYTES;
-        cudaLaunchAttribute qa[1];
-        qa[0].id = cudaLaunchAttributeClusterDimension;
-        qa[0].val.clusterDim.x = CG;
-        qa[0].val.clusterDim.y = 1;
-        qa[0].val.clusterDim.z = 1;
-        qc.attrs = qa;
-        qc.numAttrs = 1;
-        int active = 0;
-        GEMM_B200_CUDA_TRY(cudaOccupancyMaxActiveClusters(&active, kern, &qc));
-        if (active < 1) return fail(GEMM_B200_ERR_CUDA, "gemm_bf16: no CTA pair fits on this device");
-        if (active < n) n = active;
-      }
-      max_clusters_for_dev[slot] = n;
-    }
-    max_clusters = max_clusters_for_dev[slot];
-  }
+  if (int rc = persistent_clusters(kern, CG, Cfg::THREADS, Cfg::SMEM_BYTES, di, &max_clusters)) return rc;
 
   GemmShape shape;
   shape.M = (int)a.M;
@@ -155,23 +187,7 @@ static int launch_bf16(const Bf16Args& a) {
   if (num_tiles > 0x7fffffff) return fail(GEMM_B200_ERR_TOO_LARGE, "gemm_bf16: too many tiles");
   const int clusters = (int)(num_tiles < max_clusters ? num_tiles : max_clusters);
 
-  cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3((unsigned)(clusters * CG));
-  cfg.blockDim = dim3(Cfg::THREADS);
-  cfg.dynamicSmemBytes = Cfg::SMEM_BYTES;
-  cfg.stream = a.stream;
-  cudaLaunchAttribute attrs[1];
-  attrs[0].id = cudaLaunchAttributeClusterDimension;
-  attrs[0].val.clusterDim.x = CG;
-  attrs[0].val.clusterDim.y = 1;
-  attrs[0].val.clusterDim.z = 1;
-  cfg.attrs = attrs;
-  cfg.numAttrs = 1;
-  void* cptr = a.C;
-  int64_t ldc = a.ldc;
-  GEMM_B200_CUDA_TRY(cudaLaunchKernelEx(&cfg, kern, tmA, tmB, tmC, cptr, ldc, shape));
-  launch_counter().fetch_add(1, std::memory_order_relaxed);
-  return GEMM_B200_OK;
+  return launch_clusters(kern, clusters, CG, Cfg::THREADS, Cfg::SMEM_BYTES, a.stream, tmA, tmB, tmC, a.C, a.ldc, shape);
 }
 
 struct Bf16ConfigEntry {
@@ -343,36 +359,9 @@ static int launch_mxfp8(const MxArgs& a) {
   if (int rc = make_scale_map(&tmSFB, a.SFB, a.N, a.K, 2)) return rc;
 
   auto kern = gemm_mxfp8_kernel<Cfg, OUT_F32>;
-  static std::mutex mu;
-  static int max_clusters_for_dev[64] = {0};
   int max_clusters = 0;
-  {
-    std::lock_guard<std::mutex> lk(mu);
-    const int slot = di.dev & 63;
-    if (max_clusters_for_dev[slot] == 0) {
-      GEMM_B200_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES));
-      int n = di.sms / CG;
-      if (CG > 1) {
-        cudaLaunchConfig_t qc = {};
-        qc.gridDim = dim3((unsigned)(di.sms / CG * CG));
-        qc.blockDim = dim3(kMxThreads);
-        qc.dynamicSmemBytes = Cfg::SMEM_BYTES;
-        cudaLaunchAttribute qa[1];
-        qa[0].id = cudaLaunchAttributeClusterDimension;
-        qa[0].val.clusterDim.x = CG;
-        qa[0].val.clusterDim.y = 1;
-        qa[0].val.clusterDim.z = 1;
-        qc.attrs = qa;
-        qc.numAttrs = 1;
-        int active = 0;
-        GEMM_B200_CUDA_TRY(cudaOccupancyMaxActiveClusters(&active, kern, &qc));
-        if (active < 1) return fail(GEMM_B200_ERR_CUDA, "gemm_mxfp8: no CTA pair fits on this device");
-        if (active < n) n = active;
-      }
-      max_clusters_for_dev[slot] = n;
-    }
-    max_clusters = max_clusters_for_dev[slot];
-  }
+  if (int rc = persistent_clusters(kern, CG, kMxThreads, Cfg::SMEM_BYTES, di, &max_clusters)) return rc;
+
   GemmShape shape;
   shape.M = (int)a.M;
   shape.N = (int)a.N;
@@ -387,23 +376,7 @@ static int launch_mxfp8(const MxArgs& a) {
   const int64_t num_tiles = (int64_t)shape.tiles_m * shape.tiles_n * shape.k_splits;
   if (num_tiles > 0x7fffffff) return fail(GEMM_B200_ERR_TOO_LARGE, "gemm_mxfp8: too many tiles");
   const int clusters = (int)(num_tiles < max_clusters ? num_tiles : max_clusters);
-  cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3((unsigned)(clusters * CG));
-  cfg.blockDim = dim3(kMxThreads);
-  cfg.dynamicSmemBytes = Cfg::SMEM_BYTES;
-  cfg.stream = a.stream;
-  cudaLaunchAttribute attrs[1];
-  attrs[0].id = cudaLaunchAttributeClusterDimension;
-  attrs[0].val.clusterDim.x = CG;
-  attrs[0].val.clusterDim.y = 1;
-  attrs[0].val.clusterDim.z = 1;
-  cfg.attrs = attrs;
-  cfg.numAttrs = 1;
-  void* cptr = a.C;
-  int64_t ldc = a.ldc;
-  GEMM_B200_CUDA_TRY(cudaLaunchKernelEx(&cfg, kern, tmA, tmB, tmSFA, tmSFB, cptr, ldc, shape));
-  launch_counter().fetch_add(1, std::memory_order_relaxed);
-  return GEMM_B200_OK;
+  return launch_clusters(kern, clusters, CG, kMxThreads, Cfg::SMEM_BYTES, a.stream, tmA, tmB, tmSFA, tmSFB, a.C, a.ldc, shape);
 }
 
 // Split-K: FP32 partial sums of every (tile, K split) into scratch, then one reduce pass into C.
