@@ -12,7 +12,8 @@
 //   warp 1      owns TMEM; one thread copies the scales smem -> TMEM (tcgen05.cp) and issues
 //               tcgen05.mma kind::mxf8f6f4.block_scale (K = 32 per instruction);
 //   warps 2-9   epilogue: each warp pulls 32 rows x 128 columns of the accumulator into
-//               registers, releases the accumulator at once, then converts and stores.
+//               registers, releases the accumulator at once, then converts and stores (swizzled
+//               staging + TMA store, or direct 16-byte stores for split-K partial sums).
 // The 256-column accumulator plus the scale columns do not fit twice in the 512 TMEM columns,
 // so the accumulator is single-buffered; draining it to registers first keeps the tensor pipe
 // idle only for the TMEM read, not for the global stores.
@@ -33,9 +34,11 @@ constexpr int kMxThreads = 320;
 constexpr int kMxSfaCol = 256;     // TMEM columns [256, 260): scales of A
 constexpr int kMxSfbCol = 260;     // TMEM columns [260, 268): scales of B (256 columns of C)
 
-template <int CG_, int STAGES_, bool COMMIT_MASK_>
+// EPI: 0 = direct 16-byte global stores (also the split-K partial sums);
+//      1 = per-warp swizzled staging in shared memory + TMA store (full 128-byte lines).
+template <int CG_, int STAGES_, bool COMMIT_MASK_, int EPI_ = 0>
 struct MxCfg {
-  static constexpr int CG = CG_, STAGES = STAGES_;
+  static constexpr int CG = CG_, STAGES = STAGES_, EPI = EPI_;
   static constexpr bool COMMIT_MASK = COMMIT_MASK_;
   static constexpr int BN_CTA = kBlockN / CG;
   static constexpr int A_BYTES = kBlockM * kMxBlockK;       // 16 KB
@@ -43,8 +46,10 @@ struct MxCfg {
   static constexpr int SFA_BYTES = 512;
   static constexpr int SFB_BYTES = 1024;                    // 256 columns of C
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES + SFA_BYTES + SFB_BYTES;
+  static constexpr int EPI_WARP_BUF = 32 * 128;             // 32 rows x 128 bytes per epilogue warp
+  static constexpr int EPI_BYTES = EPI == 1 ? 8 * EPI_WARP_BUF : 0;
   static constexpr int BAR_BYTES = (2 * STAGES + 2) * 8 + 16;
-  static constexpr int SMEM_BYTES = 1024 + STAGES * STAGE_BYTES + BAR_BYTES;
+  static constexpr int SMEM_BYTES = 1024 + STAGES * STAGE_BYTES + EPI_BYTES + BAR_BYTES;
   static_assert(SMEM_BYTES <= 232448, "shared memory budget");
 };
 
@@ -52,13 +57,17 @@ template <class Cfg, bool OUT_F32>
 __global__ void __launch_bounds__(kMxThreads, 1)
 gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                   const __grid_constant__ CUtensorMap tmSFA, const __grid_constant__ CUtensorMap tmSFB,
-                  void* __restrict__ Cptr, int64_t ldc, const GemmShape shape) {
+                  const __grid_constant__ CUtensorMap tmC, void* __restrict__ Cptr, int64_t ldc,
+                  const GemmShape shape) {
   constexpr int CG = Cfg::CG, STAGES = Cfg::STAGES;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   const uint32_t sA0 = smem_base;
   const uint32_t sB0 = sA0 + STAGES * Cfg::A_BYTES;
-  const uint32_t sSFA0 = sB0 + STAGES * Cfg::B_BYTES;
+  // epilogue staging right after the A/B ring keeps it 1024-byte aligned (128B-swizzled TMA store);
+  // the scale ring (512 / 1024 bytes per stage) and the barriers follow
+  const uint32_t sEpi0 = sB0 + STAGES * Cfg::B_BYTES;
+  const uint32_t sSFA0 = sEpi0 + Cfg::EPI_BYTES;
   const uint32_t sSFB0 = sSFA0 + STAGES * Cfg::SFA_BYTES;
   const uint32_t bar0 = sSFB0 + STAGES * Cfg::SFB_BYTES;
   auto full_bar = [&](int s) { return bar0 + 8u * s; };
@@ -96,6 +105,7 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
     prefetch_tensormap(&tmB);
     prefetch_tensormap(&tmSFA);
     prefetch_tensormap(&tmSFB);
+    if (Cfg::EPI == 1) prefetch_tensormap(&tmC);
   }
   if (warp == 1) {
     tmem_alloc<CG>(tmem_slot, kTmemCols);
@@ -225,7 +235,47 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
         if constexpr (CG == 1) mbar_arrive(tempty_bar);
         else mbar_arrive_cluster(map_to_cta(tempty_bar, 0));
       }
-      if (row < shape.M) {
+      if constexpr (Cfg::EPI == 1) {
+        // 128-byte-wide slabs (64 bf16 or 32 f32 columns) of this warp's 32 rows: swizzled staging,
+        // then one TMA store per slab; rows / columns outside C are clipped by the tensor map
+        const uint32_t buf = sEpi0 + (uint32_t)(warp - 2) * Cfg::EPI_WARP_BUF;
+        const uint32_t row_addr = buf + (uint32_t)lane * 128u;
+        const uint32_t sw = (uint32_t)(lane & 7);
+        const int row0 = (tm * CG + (int)cta_rank) * kBlockM + quad * 32;
+        constexpr int SLABS = OUT_F32 ? 4 : 2;
+#pragma unroll
+        for (int sl = 0; sl < SLABS; ++sl) {
+          if (lane == 0) tma_store_wait_read<0>();   // the previous slab's store has read the buffer
+          __syncwarp();
+          if constexpr (OUT_F32) {
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+              asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(row_addr + (((uint32_t)j ^ sw) << 4)),
+                           "r"(v[sl][4 * j]), "r"(v[sl][4 * j + 1]), "r"(v[sl][4 * j + 2]), "r"(v[sl][4 * j + 3]) : "memory");
+          } else {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              uint32_t p[4];
+#pragma unroll
+              for (int e = 0; e < 4; ++e) {
+                const int idx = (j & 3) * 8 + 2 * e;     // column within the 32-column chunk
+                __nv_bfloat162 h = __floats2bfloat162_rn(__uint_as_float(v[2 * sl + (j >> 2)][idx]),
+                                                         __uint_as_float(v[2 * sl + (j >> 2)][idx + 1]));
+                p[e] = *reinterpret_cast<uint32_t*>(&h);
+              }
+              asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(row_addr + (((uint32_t)j ^ sw) << 4)),
+                           "r"(p[0]), "r"(p[1]), "r"(p[2]), "r"(p[3]) : "memory");
+            }
+          }
+          fence_proxy_async_smem();
+          __syncwarp();
+          const int x = col0 + sl * (OUT_F32 ? 32 : 64);
+          if (lane == 0) {
+            if (row0 < shape.M && x < shape.N) tma_store_2d(&tmC, x, row0, buf);
+            tma_store_commit();
+          }
+        }
+      } else if (row < shape.M) {
 #pragma unroll
         for (int c = 0; c < 4; ++c) {
           const int col = col0 + c * 32;
@@ -255,6 +305,7 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
         }
       }
     }
+    if (Cfg::EPI == 1 && lane == 0) tma_store_wait_all<0>();
   }
 
   // ------------------------------------------------------------------ teardown

@@ -318,7 +318,8 @@ constexpr int kCfgLarge = 2, kCfgMedium = 9, kCfgSmall = 12;
 // Heuristic from a sweep of square problems on a B200 (TFLOP/s at n = 512 / 1024 / 2048 / 4096 /
 // 8192): 128x128x32: 5 / 22 / 47 / 56 / 56;  64x64x32: 14 / 39 / 53 / 55 / 56;  32x64x32:
 // 16 / 34 / 43 / 44 / 45.  So: 128x128x32 once it yields about four tiles per SM, 64x64x32 while
-// those tiles still fill the SMs, 32x64x32 below that.
+// those tiles still fill the SMs, 32x64x32 below that.  Other thread-tile shapes at 128x128x32
+// (4x16: 54.6, 16x4: 46.5 TFLOP/s at 4096) did not beat 8x8 (55.5).
 inline int pick_config(int64_t M, int64_t N, int num_sms) {
   const int64_t t128 = ceil_div64(M, 128) * ceil_div64(N, 128);
   if (t128 >= 4 * (int64_t)num_sms) return kCfgLarge;

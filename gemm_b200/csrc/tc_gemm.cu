@@ -357,6 +357,12 @@ static int launch_mxfp8(const MxArgs& a) {
     return rc;
   if (int rc = make_scale_map(&tmSFA, a.SFA, a.M, a.K, 1)) return rc;
   if (int rc = make_scale_map(&tmSFB, a.SFB, a.N, a.K, 2)) return rc;
+  CUtensorMap tmC = tmA;   // only read by the TMA-store epilogue
+  if (Cfg::EPI == 1) {
+    if (int rc = make_map_2d(&tmC, OUT_F32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16,
+                             OUT_F32 ? 4 : 2, a.C, a.M, a.N, a.ldc, OUT_F32 ? 32 : 64, 32, CU_TENSOR_MAP_SWIZZLE_128B))
+      return rc;
+  }
 
   auto kern = gemm_mxfp8_kernel<Cfg, OUT_F32>;
   int max_clusters = 0;
@@ -376,7 +382,7 @@ static int launch_mxfp8(const MxArgs& a) {
   const int64_t num_tiles = (int64_t)shape.tiles_m * shape.tiles_n * shape.k_splits;
   if (num_tiles > 0x7fffffff) return fail(GEMM_B200_ERR_TOO_LARGE, "gemm_mxfp8: too many tiles");
   const int clusters = (int)(num_tiles < max_clusters ? num_tiles : max_clusters);
-  return launch_clusters(kern, clusters, CG, kMxThreads, Cfg::SMEM_BYTES, a.stream, tmA, tmB, tmSFA, tmSFB, a.C, a.ldc, shape);
+  return launch_clusters(kern, clusters, CG, kMxThreads, Cfg::SMEM_BYTES, a.stream, tmA, tmB, tmSFA, tmSFB, tmC, a.C, a.ldc, shape);
 }
 
 // Split-K: FP32 partial sums of every (tile, K split) into scratch, then one reduce pass into C.
@@ -444,13 +450,15 @@ struct MxConfigEntry {
 using Mx_1cta = MxCfg<1, 4, false>;
 using Mx_2cta = MxCfg<2, 6, false>;
 using Mx_2cta_m = MxCfg<2, 6, true>;
+using Mx_2cta_m_tma = MxCfg<2, 5, true, 1>;
 static const MxConfigEntry kMxConfigs[] = {
     {"1cta_128x256x128_s4", {launch_mxfp8<Mx_1cta, false>, launch_mxfp8<Mx_1cta, true>}},
     {"2cta_256x256x128_s6", {launch_mxfp8<Mx_2cta, false>, launch_mxfp8<Mx_2cta, true>}},
     {"2cta_256x256x128_s6_maskcommit", {launch_mxfp8<Mx_2cta_m, false>, launch_mxfp8<Mx_2cta_m, true>}},
+    {"2cta_256x256x128_s5_maskcommit_tmastore", {launch_mxfp8<Mx_2cta_m_tma, false>, launch_mxfp8<Mx_2cta_m_tma, true>}},
 };
 constexpr int kNumMxConfigs = sizeof(kMxConfigs) / sizeof(kMxConfigs[0]);
-constexpr int kDefaultMxConfig = 2;      // CTA pair, masked commit
+constexpr int kDefaultMxConfig = 3;      // CTA pair, masked commit, TMA-store epilogue
 constexpr int kSkinnyMxConfig = 0;       // M <= 128: single-CTA tiles give more independent column tiles
 
 }  // namespace tc
