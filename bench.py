@@ -222,6 +222,12 @@ def per_dtype_table(peaks: dict) -> dict:
             out[f"mxfp8_{M}x{K}x{N}"] = {"tflops": round(tf, 1), "frac_of_nominal_4500": round(tf / 4500.0, 4),
                                          "gbps": round(bytes_ / t / 1e9, 1),
                                          "frac_of_measured_hbm": round(bytes_ / t / 1e9 / float(peaks.get("hbm_gbs", 6650.0)), 4)}
+            if M >= 1024:
+                # the same GEMM with the quantising epilogue vs GEMM (bf16 out) + separate quantise pass
+                t_f = time_alone(lambda: ops.gemm_mxfp8_quant_out(Aq, Bq), reps=5)
+                t_q = time_alone(lambda: ops.quantize_mxfp8(C), reps=5)
+                out[f"mxfp8_{M}x{K}x{N}_quant_out"] = {"fused_ms": round(t_f * 1e3, 3), "gemm_plus_quantise_ms": round((t + t_q) * 1e3, 3),
+                                                       "tflops_fused": round(2 * M * N * K / t_f / 1e12, 1)}
             del Aq, Bq, C
     return out
 

@@ -31,6 +31,7 @@ SIGNATURES = {
     "gemm_b200_mxfp8_scale_offset": (sz, [i64, i64, i64, i64]),
     "gemm_b200_gemm_mxfp8": (i32, [vp, vp, vp, vp, vp, i64, i64, i64, i64, i32, vp]),
     "gemm_b200_gemm_mxfp8_cfg": (i32, [vp, vp, vp, vp, vp, i64, i64, i64, i64, i32, i32, vp]),
+    "gemm_b200_gemm_mxfp8_quant_out": (i32, [vp, vp, vp, vp, vp, vp, i64, i64, i64, vp]),
     "gemm_b200_gemm_mxfp8_splitk": (i32, [vp, vp, vp, vp, vp, i64, i64, i64, i64, i32, i32, vp, sz, vp]),
     "gemm_b200_gemm_mxfp8_splitk_scratch_bytes": (sz, [i64, i64, i32]),
     "gemm_b200_gemm_mxfp8_splitk_static": (i32, [vp, vp, vp, vp, vp, i64, i64, i64, i64, i32, i32, vp]),

@@ -24,6 +24,7 @@
 #include "common.cuh"
 #include "tc_common.cuh"
 #include "gemm_bf16.cuh"
+#include "quant_mxfp8.cuh"
 
 namespace gemm_b200 {
 namespace tc {
@@ -53,13 +54,17 @@ struct MxCfg {
   static_assert(SMEM_BYTES <= 232448, "shared memory budget");
 };
 
-template <class Cfg, bool OUT_F32>
+// OUT: 0 = bf16, 1 = f32, 2 = MXFP8 (C quantised along its columns: e4m3 data to Cptr, one UE8M0
+// scale per 32 columns to SFC in the packed layout, exactly what quantising the bf16 result gives)
+template <class Cfg, int OUT>
 __global__ void __launch_bounds__(kMxThreads, 1)
 gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                   const __grid_constant__ CUtensorMap tmSFA, const __grid_constant__ CUtensorMap tmSFB,
                   const __grid_constant__ CUtensorMap tmC, void* __restrict__ Cptr, int64_t ldc,
-                  const GemmShape shape) {
+                  uint8_t* __restrict__ SFC, const GemmShape shape) {
   constexpr int CG = Cfg::CG, STAGES = Cfg::STAGES;
+  constexpr bool OUT_F32 = (OUT == 1);
+  static_assert(OUT != 2 || Cfg::EPI == 0, "the quantising epilogue uses direct stores");
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   const uint32_t sA0 = smem_base;
@@ -274,6 +279,31 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
             if (row0 < shape.M && x < shape.N) tma_store_2d(&tmC, x, row0, buf);
             tma_store_commit();
           }
+        }
+      } else if constexpr (OUT == 2) {
+        // each thread holds 32 consecutive columns of its row per chunk: one microscaling block.
+        // Round to bf16 first so the bytes equal "bf16 GEMM output, then quantise".
+        const int64_t kchunks = (((int64_t)shape.N / 32) + 3) / 4;       // scale chunks per row block of C
+        const int64_t rows_pad = (((int64_t)shape.M + 127) / 128) * 128;
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          const int col = col0 + c * 32;
+          const int64_t nb = col / 32;                                   // block index along N
+          if (row >= rows_pad || nb >= kchunks * 4) continue;            // outside the padded scale buffer
+          uint32_t byte = 0;
+          if (row < shape.M && col < shape.N) {
+            uint32_t w[16], q[8];
+#pragma unroll
+            for (int e = 0; e < 16; ++e) {
+              __nv_bfloat162 h = __floats2bfloat162_rn(__uint_as_float(v[c][2 * e]), __uint_as_float(v[c][2 * e + 1]));
+              w[e] = *reinterpret_cast<uint32_t*>(&h);
+            }
+            byte = mx::quantise_block(w, q);
+            uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<uint8_t*>(Cptr) + (int64_t)row * ldc + col);
+            dst[0] = make_uint4(q[0], q[1], q[2], q[3]);
+            dst[1] = make_uint4(q[4], q[5], q[6], q[7]);
+          }
+          SFC[mx::scale_offset(kchunks, row, nb)] = (uint8_t)byte;      // padding rows / blocks get 0
         }
       } else if (row < shape.M) {
 #pragma unroll

@@ -7,7 +7,6 @@
 
 #include "gemm_bf16.cuh"
 #include "gemm_mxfp8.cuh"
-#include "quant_mxfp8.cuh"
 
 namespace gemm_b200 {
 namespace tc {
@@ -325,6 +324,7 @@ struct MxArgs {
   cudaStream_t stream;
   int k_splits = 1;        // > 1: FP32 partials go to `scratch` ([k_splits][M][N]), then a reduce pass
   float* scratch = nullptr;
+  uint8_t* SFC = nullptr;  // packed scales of C for the quantising epilogue
 };
 
 // packed scale buffer of `rows` rows viewed as int32 [row blocks][kchunks * 128]
@@ -343,8 +343,9 @@ static int make_scale_map(CUtensorMap* map, const void* sf, int64_t rows, int64_
   return GEMM_B200_OK;
 }
 
-template <class Cfg, bool OUT_F32>
+template <class Cfg, int OUT>
 static int launch_mxfp8(const MxArgs& a) {
+  constexpr bool OUT_F32 = (OUT == 1);
   constexpr int CG = Cfg::CG;
   DeviceInfo di;
   if (int rc = device_info(&di)) return rc;
@@ -364,7 +365,7 @@ static int launch_mxfp8(const MxArgs& a) {
       return rc;
   }
 
-  auto kern = gemm_mxfp8_kernel<Cfg, OUT_F32>;
+  auto kern = gemm_mxfp8_kernel<Cfg, OUT>;
   int max_clusters = 0;
   if (int rc = persistent_clusters(kern, CG, kMxThreads, Cfg::SMEM_BYTES, di, &max_clusters)) return rc;
 
@@ -382,7 +383,7 @@ static int launch_mxfp8(const MxArgs& a) {
   const int64_t num_tiles = (int64_t)shape.tiles_m * shape.tiles_n * shape.k_splits;
   if (num_tiles > 0x7fffffff) return fail(GEMM_B200_ERR_TOO_LARGE, "gemm_mxfp8: too many tiles");
   const int clusters = (int)(num_tiles < max_clusters ? num_tiles : max_clusters);
-  return launch_clusters(kern, clusters, CG, kMxThreads, Cfg::SMEM_BYTES, a.stream, tmA, tmB, tmSFA, tmSFB, tmC, a.C, a.ldc, shape);
+  return launch_clusters(kern, clusters, CG, kMxThreads, Cfg::SMEM_BYTES, a.stream, tmA, tmB, tmSFA, tmSFB, tmC, a.C, a.ldc, a.SFC, shape);
 }
 
 // Split-K: FP32 partial sums of every (tile, K split) into scratch, then one reduce pass into C.
@@ -391,7 +392,7 @@ static int launch_mxfp8_splitk(const MxArgs& a, int out_dtype) {
   MxArgs part = a;
   part.C = a.scratch;
   part.ldc = a.N;
-  if (int rc = launch_mxfp8<Cfg, true>(part)) return rc;
+  if (int rc = launch_mxfp8<Cfg, 1>(part)) return rc;
   const int num_kb = (int)ceil_div64(a.K, kMxBlockK);
   const int kb_per = (int)ceil_div64(num_kb, a.k_splits);
   const int splits = (int)ceil_div64(num_kb, kb_per);
@@ -452,10 +453,10 @@ using Mx_2cta = MxCfg<2, 6, false>;
 using Mx_2cta_m = MxCfg<2, 6, true>;
 using Mx_2cta_m_tma = MxCfg<2, 5, true, 1>;
 static const MxConfigEntry kMxConfigs[] = {
-    {"1cta_128x256x128_s4", {launch_mxfp8<Mx_1cta, false>, launch_mxfp8<Mx_1cta, true>}},
-    {"2cta_256x256x128_s6", {launch_mxfp8<Mx_2cta, false>, launch_mxfp8<Mx_2cta, true>}},
-    {"2cta_256x256x128_s6_maskcommit", {launch_mxfp8<Mx_2cta_m, false>, launch_mxfp8<Mx_2cta_m, true>}},
-    {"2cta_256x256x128_s5_maskcommit_tmastore", {launch_mxfp8<Mx_2cta_m_tma, false>, launch_mxfp8<Mx_2cta_m_tma, true>}},
+    {"1cta_128x256x128_s4", {launch_mxfp8<Mx_1cta, 0>, launch_mxfp8<Mx_1cta, 1>}},
+    {"2cta_256x256x128_s6", {launch_mxfp8<Mx_2cta, 0>, launch_mxfp8<Mx_2cta, 1>}},
+    {"2cta_256x256x128_s6_maskcommit", {launch_mxfp8<Mx_2cta_m, 0>, launch_mxfp8<Mx_2cta_m, 1>}},
+    {"2cta_256x256x128_s5_maskcommit_tmastore", {launch_mxfp8<Mx_2cta_m_tma, 0>, launch_mxfp8<Mx_2cta_m_tma, 1>}},
 };
 constexpr int kNumMxConfigs = sizeof(kMxConfigs) / sizeof(kMxConfigs[0]);
 constexpr int kDefaultMxConfig = 3;      // CTA pair, masked commit, TMA-store epilogue
@@ -550,6 +551,29 @@ extern "C" int gemm_b200_gemm_mxfp8_cfg(const void* Aq, const void* SFA, const v
     }
   }
   return tc::kMxConfigs[config].launch[out_dtype](args);
+}
+
+extern "C" int gemm_b200_gemm_mxfp8_quant_out(const void* Aq, const void* SFA, const void* Bq, const void* SFB,
+                                              void* Cq, void* SFC, int64_t M, int64_t N, int64_t K, void* stream) {
+  using namespace gemm_b200;
+  if (M < 0 || N < 0 || K < 0) return fail(GEMM_B200_ERR_INVALID_ARG, "gemm_mxfp8_quant_out: negative size");
+  if (M == 0 || N == 0) return GEMM_B200_OK;
+  if (!Cq || !SFC || !Aq || !Bq || !SFA || !SFB) return fail(GEMM_B200_ERR_INVALID_ARG, "gemm_mxfp8_quant_out: null pointer");
+  if (K <= 0 || K % 32 != 0 || N % 32 != 0)
+    return fail(GEMM_B200_ERR_INVALID_ARG, "gemm_mxfp8_quant_out: K=%lld and N=%lld must be positive multiples of 32",
+                (long long)K, (long long)N);
+  if (M > 0x7fffffff || N > 0x7fffffff || K > 0x7fffffff)
+    return fail(GEMM_B200_ERR_TOO_LARGE, "gemm_mxfp8_quant_out: a dimension exceeds 2^31-1");
+  if ((reinterpret_cast<uintptr_t>(Aq) | reinterpret_cast<uintptr_t>(Bq) | reinterpret_cast<uintptr_t>(Cq) |
+       reinterpret_cast<uintptr_t>(SFA) | reinterpret_cast<uintptr_t>(SFB)) % 16 != 0)
+    return fail(GEMM_B200_ERR_ALIGNMENT, "gemm_mxfp8_quant_out: all pointers must be 16-byte aligned");
+  tc::DeviceInfo di;
+  if (int rc = tc::device_info(&di)) return rc;
+  if (di.cc_major != 10)
+    return fail(GEMM_B200_ERR_UNSUPPORTED, "gemm_mxfp8_quant_out: device has compute capability %d.x, need 10.x (sm_100a)", di.cc_major);
+  tc::MxArgs args{Aq, SFA, Bq, SFB, Cq, M, N, K, /*ldc (bytes per row of Cq)*/ N, static_cast<cudaStream_t>(stream)};
+  args.SFC = static_cast<uint8_t*>(SFC);
+  return (M <= 128) ? tc::launch_mxfp8<tc::Mx_1cta, 2>(args) : tc::launch_mxfp8<tc::Mx_2cta_m, 2>(args);
 }
 
 extern "C" int gemm_b200_gemm_mxfp8_auto_splits(int64_t M, int64_t N, int64_t K) {

@@ -16,7 +16,7 @@ from ._lib import lib, check
 __all__ = [
     "sgemm_f32", "gemm_bf16", "check_status", "sgemm_f32_host", "gemm_bf16_host",
     "sgemm_f32_configs", "gemm_bf16_configs", "launch_count",
-    "quantize_mxfp8", "gemm_mxfp8", "gemm_mxfp8_configs", "MxFp8Tensor", "gemm_mxfp8_splitk", "gemm_mxfp8_auto_splits",
+    "quantize_mxfp8", "gemm_mxfp8", "gemm_mxfp8_configs", "MxFp8Tensor", "gemm_mxfp8_splitk", "gemm_mxfp8_auto_splits", "gemm_mxfp8_quant_out",
 ]
 
 
@@ -176,6 +176,21 @@ def gemm_mxfp8(A: MxFp8Tensor, B: MxFp8Tensor, out: torch.Tensor | None = None, 
                                            _lib.OUT_F32 if out_dtype == torch.float32 else _lib.OUT_BF16, config,
                                            _stream(A.data)))
     return out
+
+
+def gemm_mxfp8_quant_out(A: MxFp8Tensor, B: MxFp8Tensor) -> MxFp8Tensor:
+    """GEMM whose epilogue emits C already quantised to MXFP8 along its columns (the A operand of a
+    following GEMM).  Same bytes as ``quantize_mxfp8(gemm_mxfp8(A, B))``."""
+    _require(A.K == B.K, f"K mismatch: {A.K} vs {B.K}")
+    M, N, K = A.rows, B.rows, A.K
+    _require(N % 32 == 0, "N must be a multiple of 32")
+    dev = A.data.device
+    data = torch.empty((M, N), device=dev, dtype=torch.uint8)
+    scales = torch.empty((max(int(lib.gemm_b200_mxfp8_scale_bytes(M, N)), 1),), device=dev, dtype=torch.uint8)
+    with torch.cuda.device(dev):
+        check(lib.gemm_b200_gemm_mxfp8_quant_out(A.data.data_ptr(), A.scales.data_ptr(), B.data.data_ptr(), B.scales.data_ptr(),
+                                                 data.data_ptr(), scales.data_ptr(), M, N, K, _stream(A.data)))
+    return MxFp8Tensor(data, scales, M, N)
 
 
 def gemm_mxfp8_splitk(A: MxFp8Tensor, B: MxFp8Tensor, k_splits: int, out: torch.Tensor | None = None, *,

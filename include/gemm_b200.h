@@ -119,6 +119,15 @@ int gemm_b200_gemm_mxfp8(const void* Aq, const void* SFA, const void* Bq, const 
 int gemm_b200_gemm_mxfp8_cfg(const void* Aq, const void* SFA, const void* Bq, const void* SFB,
                              void* C, int64_t M, int64_t N, int64_t K, int64_t ldc,
                              int out_dtype, int config, void* stream);
+/* Same GEMM with a quantising epilogue: C is rounded to bf16 and quantised to MXFP8 along its
+ * columns inside the kernel (e4m3 to Cq[M,N], ld = N; scales to SFC in the packed layout of
+ * gemm_b200_mxfp8_scale_offset(M, N, row, n / 32), gemm_b200_mxfp8_scale_bytes(M, N) bytes), so
+ * the result can feed the next GEMM as its A operand without a bf16 round trip through memory.
+ * Bit-identical to gemm_b200_gemm_mxfp8 (bf16 output) followed by gemm_b200_quantize_mxfp8.
+ * N % 32 == 0.  No counterpart in the reference. */
+int gemm_b200_gemm_mxfp8_quant_out(const void* Aq, const void* SFA, const void* Bq, const void* SFB,
+                                   void* Cq, void* SFC, int64_t M, int64_t N, int64_t K, void* stream);
+
 /* Split-K form for problems with few output tiles (skinny M): every tile is cut into `k_splits`
  * ranges of K whose FP32 partial sums go to `scratch` ([k_splits][M][N] floats, device memory,
  * 16-byte aligned, at least gemm_b200_gemm_mxfp8_splitk_scratch_bytes() bytes) and are then

@@ -154,3 +154,37 @@ def test_splitk_rejects_a_small_scratch(ops):
     with pytest.raises(L.GemmB200Error) as e:
         ops.gemm_mxfp8_splitk(Aq, Bq, 4, scratch=torch.empty(1024, device="cuda", dtype=torch.uint8))
     assert e.value.code == L.ERR_INVALID_ARG
+
+
+@pytest.mark.parametrize("M,K,N", [(256, 512, 256), (100, 96, 160), (129, 160, 288), (16, 1024, 512), (1000, 992, 1056)])
+def test_quantising_epilogue_equals_gemm_then_quantise(ops, oracle, M, K, N):
+    A, B = oracle.gen_randn_bf16(M, K, N, seed=M + N)
+    A = (A.float() * torch.exp(torch.randn(M, 1, generator=torch.Generator().manual_seed(M)) * 2)).bfloat16()
+    Aq = ops.quantize_mxfp8(A.cuda()); Bq = ops.quantize_mxfp8(B.cuda(), transposed_in=True)
+    fused = ops.gemm_mxfp8_quant_out(Aq, Bq)
+    ops.check_status()
+    C16 = ops.gemm_mxfp8(Aq, Bq, out_dtype=torch.bfloat16, config=(0 if M <= 128 else 2))
+    unfused = ops.quantize_mxfp8(C16)
+    assert torch.equal(fused.data, unfused.data)
+    assert torch.equal(fused.scales, unfused.scales)                    # packed buffers, padding included
+    # and against the oracle's quantiser applied to the same bf16 result
+    q, s = oracle.mxfp8_quantize(C16.cpu())
+    assert torch.equal(fused.data.cpu(), q) and torch.equal(fused.scale_matrix(), s)
+
+
+def test_chained_gemms_through_the_quantising_epilogue(ops, oracle):
+    # Y = (X W1) W2 with the intermediate kept in MXFP8 end to end
+    M, K, H, N = 256, 512, 1024, 256
+    g = torch.Generator().manual_seed(9)
+    X = torch.randn(M, K, generator=g).bfloat16(); W1 = (torch.randn(K, H, generator=g) / 16).bfloat16()
+    W2 = (torch.randn(H, N, generator=g) / 16).bfloat16()
+    Xq = ops.quantize_mxfp8(X.cuda()); W1q = ops.quantize_mxfp8(W1.cuda(), transposed_in=True)
+    W2q = ops.quantize_mxfp8(W2.cuda(), transposed_in=True)
+    Hq = ops.gemm_mxfp8_quant_out(Xq, W1q)
+    Y = ops.gemm_mxfp8(Hq, W2q, out_dtype=torch.float32)
+    ops.check_status()
+    # oracle: dequantise the very same intermediate bytes
+    Hd = oracle.mxfp8_dequantize(Hq.data.cpu(), Hq.scale_matrix())
+    qb, sb = oracle.mxfp8_quantize(W2.t().contiguous())
+    want = torch.matmul(Hd, oracle.mxfp8_dequantize(qb, sb).t())
+    assert oracle.rel_frobenius(Y.cpu(), want) <= REL_TOL
