@@ -24,6 +24,8 @@
 // Tiles on the M/N/K edges are zero-filled by the cp.async source-size operand.
 // A 4-byte cp.async variant of the same kernel serves operands whose pointers
 // or leading dimensions are not 16-byte aligned.
+#include <string.h>
+
 #include "common.cuh"
 
 namespace gemm_b200 {
@@ -295,6 +297,7 @@ using C64x64k16        = Cfg<64, 64, 16, 2, 2, 4, 4, false>;
 using C32x64k16p       = Cfg<32, 64, 16, 2, 2, 4, 6, true>;
 using C32x64k32p       = Cfg<32, 64, 32, 2, 2, 4, 6, true>;
 using C128x128k32      = Cfg<128, 128, 32, 4, 2, 3, 2, false>;
+using C64x128k32p3     = Cfg<64, 128, 32, 2, 2, 3, 2, true>;
 
 static const ConfigEntry kConfigs[] = {
     {"128x128x16_s3", 128, 128, launch_cfg<C128x128k16>},
@@ -311,21 +314,29 @@ static const ConfigEntry kConfigs[] = {
     {"32x64x16_s4_f32x2", 32, 64, launch_cfg<C32x64k16p>},
     {"32x64x32_s4_f32x2", 32, 64, launch_cfg<C32x64k32p>},
     {"128x128x32_s3", 128, 128, launch_cfg<C128x128k32>},
+    {"64x128x32_s3_f32x2", 64, 128, launch_cfg<C64x128k32p3>},
 };
 constexpr int kNumConfigs = sizeof(kConfigs) / sizeof(kConfigs[0]);
-constexpr int kCfgLarge = 2, kCfgMedium = 9, kCfgSmall = 12;
 
-// Heuristic from a sweep of square problems on a B200 (TFLOP/s at n = 512 / 1024 / 2048 / 4096 /
-// 8192): 128x128x32: 5 / 22 / 47 / 56 / 56;  64x64x32: 14 / 39 / 53 / 55 / 56;  32x64x32:
-// 16 / 34 / 43 / 44 / 45.  So: 128x128x32 once it yields about four tiles per SM, 64x64x32 while
-// those tiles still fill the SMs, 32x64x32 below that.  Other thread-tile shapes at 128x128x32
-// (4x16: 54.6, 16x4: 46.5 TFLOP/s at 4096) did not beat 8x8 (55.5).
+inline int config_index(const char* name) {
+  for (int i = 0; i < kNumConfigs; ++i)
+    if (strcmp(kConfigs[i].name, name) == 0) return i;
+  return 0;
+}
+
+// Heuristic from sweeps of square problems on a B200 (TFLOP/s at n = 512 / 1024 / 2048 / 4096 /
+// 8192): 64x128x32: - / 40 / 48 / 56.5 / 57;  128x128x32: 5 / 22 / 47 / 55.6 / 56;  64x64x32:
+// 14 / 39 / 52 / 55 / 56;  32x64x32: 16 / 34 / 43 / 44 / 45.  So: 64x128x32 once it yields about
+// four tiles per SM, 64x64x32 while those tiles still fill the SMs, 32x64x32 below that.  Other
+// thread-tile shapes at 128x128x32 (4x16: 54.6, 16x4: 46.5 TFLOP/s at 4096) did not beat 8x8.
 inline int pick_config(int64_t M, int64_t N, int num_sms) {
-  const int64_t t128 = ceil_div64(M, 128) * ceil_div64(N, 128);
-  if (t128 >= 4 * (int64_t)num_sms) return kCfgLarge;
+  static const int large = config_index("64x128x32_s3_f32x2"), medium = config_index("64x64x32_s4_f32x2"),
+                   small = config_index("32x64x32_s4_f32x2");
+  const int64_t t_large = ceil_div64(M, 64) * ceil_div64(N, 128);
+  if (t_large >= 4 * (int64_t)num_sms) return large;
   const int64_t t64 = ceil_div64(M, 64) * ceil_div64(N, 64);
-  if (t64 >= (int64_t)num_sms + num_sms / 2) return kCfgMedium;
-  return kCfgSmall;
+  if (t64 >= (int64_t)num_sms + num_sms / 2) return medium;
+  return small;
 }
 
 }  // namespace f32
