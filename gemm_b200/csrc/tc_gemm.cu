@@ -413,7 +413,11 @@ static int launch_mxfp8_splitk(const MxArgs& a, int out_dtype) {
 static int auto_splits(int64_t M, int64_t N, int64_t K, int sms) {
   const int64_t tiles = ceil_div64(M, kBlockM) * ceil_div64(N, kBlockN);
   const int64_t num_kb = ceil_div64(K, kMxBlockK);
-  if (tiles >= sms || num_kb < 8) return 1;
+  // Splitting pays for a second (reduce) launch and an M x N FP32 round trip per split: measured on
+  // B200, 112 tiles on 148 SMs run as fast unsplit (16 x 8192 x 28672: 62 us either way; 64 rows:
+  // 62 us unsplit, 70 us split), 32 tiles do not (128 x 8192 x 8192: 42 -> 34 us; 16 x 16384 x 4096
+  // with 16 tiles: 64 -> 28 us).  Split only when the tiles leave more than a third of the SMs idle.
+  if (3 * tiles >= 2 * (int64_t)sms || num_kb < 8) return 1;
   int best = 1;
   double best_score = (double)tiles / (double)(ceil_div64(tiles, sms) * sms);
   for (int s = 2; s <= 16 && num_kb / s >= 4; ++s) {

@@ -58,7 +58,7 @@ def test_static_scratch_matches_caller_scratch_twice_in_a_row(ops, oracle):
 
 def test_static_scratch_against_the_oracle(ops, oracle):
     import gemm_b200._lib as L
-    M, K, N = 16, 4096, 2048
+    M, K, N = 16, 4096, 2048                                                  # 8 tiles: the library picks > 1 split
     A, B = oracle.gen_randn_bf16(M, K, N, seed=77)
     Aq = ops.quantize_mxfp8(A.cuda()); Bq = ops.quantize_mxfp8(B.cuda(), transposed_in=True)
     qa, sa = oracle.mxfp8_quantize(A); qb, sb = oracle.mxfp8_quantize(B.t().contiguous())
