@@ -5,6 +5,7 @@
 #include <stdint.h>
 #include <stdio.h>
 #include <stdarg.h>
+#include <stdlib.h>
 #include <atomic>
 
 #include "../../include/gemm_b200.h"
@@ -42,5 +43,18 @@ inline int cuda_fail(cudaError_t e, const char* what) {
   } while (0)
 
 static inline int64_t ceil_div64(int64_t a, int64_t b) { return (a + b - 1) / b; }
+
+// Environment knobs (read once):
+//   GEMM_B200_LOG=1                 one line on stderr per launch with the kernel variant chosen
+//   GEMM_B200_F32_CONFIG / GEMM_B200_BF16_CONFIG / GEMM_B200_MXFP8_CONFIG = <index>
+//                                   force a variant wherever the caller asked for the heuristic
+inline int env_int(const char* name, int fallback) {
+  const char* e = getenv(name);
+  return (e && *e) ? atoi(e) : fallback;
+}
+inline bool log_enabled() {
+  static const bool on = env_int("GEMM_B200_LOG", 0) != 0;
+  return on;
+}
 
 }  // namespace gemm_b200

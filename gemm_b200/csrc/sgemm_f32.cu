@@ -363,11 +363,15 @@ extern "C" int gemm_b200_sgemm_f32_cfg(const float* A, const float* B, float* C,
       GEMM_B200_CUDA_TRY(cudaDeviceGetAttribute(&cached_sms, cudaDevAttrMultiProcessorCount, dev));
       cached_dev = dev;
     }
-    config = f32::pick_config(M, N, cached_sms);
+    static const int forced = env_int("GEMM_B200_F32_CONFIG", -1);
+    config = (forced >= 0 && forced < f32::kNumConfigs) ? forced : f32::pick_config(M, N, cached_sms);
   }
   const bool vec = (lda % 4 == 0) && (ldb % 4 == 0) && (ldc % 4 == 0) && (K % 4 == 0) && (N % 4 == 0) &&
                    ((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(B) |
                      reinterpret_cast<uintptr_t>(C)) % 16 == 0);
+  if (log_enabled())
+    fprintf(stderr, "[gemm_b200] sgemm_f32 %lldx%lldx%lld -> %s%s\n", (long long)M, (long long)K, (long long)N,
+            f32::kConfigs[config].name, vec ? "" : " (4-byte loads)");
   return f32::kConfigs[config].launch(A, B, C, (int)M, (int)N, (int)K, lda, ldb, ldc, vec,
                                       static_cast<cudaStream_t>(stream));
 }

@@ -280,7 +280,13 @@ extern "C" int gemm_b200_gemm_bf16_cfg(const void* A, const void* B, void* C, in
   if (int rc = tc::device_info(&di)) return rc;
   if (di.cc_major != 10)
     return fail(GEMM_B200_ERR_UNSUPPORTED, "gemm_bf16: device has compute capability %d.x, need 10.x (sm_100a)", di.cc_major);
-  if (config < 0) config = tc::pick_bf16_config(M, N, K, di.sms);
+  if (config < 0) {
+    static const int forced = env_int("GEMM_B200_BF16_CONFIG", -1);
+    config = (forced >= 0 && forced < tc::kNumBf16Configs) ? forced : tc::pick_bf16_config(M, N, K, di.sms);
+  }
+  if (log_enabled())
+    fprintf(stderr, "[gemm_b200] gemm_bf16 %lldx%lldx%lld -> %s\n", (long long)M, (long long)K, (long long)N,
+            tc::kBf16Configs[config].name);
   tc::Bf16Args args{A, B, C, M, N, K, lda, ldb, ldc, st};
   return tc::kBf16Configs[config].launch[b_layout][out_dtype](args);
 }
@@ -541,12 +547,19 @@ extern "C" int gemm_b200_gemm_mxfp8_cfg(const void* Aq, const void* SFA, const v
     return fail(GEMM_B200_ERR_UNSUPPORTED, "gemm_mxfp8: device has compute capability %d.x, need 10.x (sm_100a)", di.cc_major);
   tc::MxArgs args{Aq, SFA, Bq, SFB, C, M, N, K, ldc, st};
   if (config < 0) {
+    static const int forced = env_int("GEMM_B200_MXFP8_CONFIG", -1);
+    if (forced >= 0 && forced < tc::kNumMxConfigs) config = forced;
+  }
+  if (config < 0) {
     if (M <= 128) {
       // skinny: single-CTA tiles, and K splits when the column tiles alone leave SMs idle
       const int splits = tc::auto_splits(M, N, K, di.sms);
       if (splits > 1) {
         if (int rc = tc::cached_scratch(di.dev, (size_t)splits * M * N * sizeof(float), &args.scratch)) return rc;
         args.k_splits = splits;
+        if (log_enabled())
+          fprintf(stderr, "[gemm_b200] gemm_mxfp8 %lldx%lldx%lld -> %s, %d K splits\n", (long long)M, (long long)K,
+                  (long long)N, tc::kMxConfigs[tc::kSkinnyMxConfig].name, splits);
         return tc::launch_mxfp8_splitk<tc::Mx_1cta>(args, out_dtype);
       }
       config = tc::kSkinnyMxConfig;
@@ -554,6 +567,9 @@ extern "C" int gemm_b200_gemm_mxfp8_cfg(const void* Aq, const void* SFA, const v
       config = tc::kDefaultMxConfig;
     }
   }
+  if (log_enabled())
+    fprintf(stderr, "[gemm_b200] gemm_mxfp8 %lldx%lldx%lld -> %s\n", (long long)M, (long long)K, (long long)N,
+            tc::kMxConfigs[config].name);
   return tc::kMxConfigs[config].launch[out_dtype](args);
 }
 

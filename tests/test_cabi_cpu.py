@@ -78,3 +78,9 @@ def test_ops_fail_loudly_without_cuda_tensors():
         ops.sgemm_f32(torch.zeros(4, 4), torch.zeros(4, 4))
     with pytest.raises(ValueError):
         ops.gemm_bf16(torch.zeros(8, 8, dtype=torch.bfloat16), torch.zeros(8, 8, dtype=torch.bfloat16))
+
+
+def test_environment_knobs_are_documented_in_the_sources():
+    text = (ROOT / "gemm_b200" / "csrc" / "common.cuh").read_text()
+    for knob in ("GEMM_B200_LOG", "GEMM_B200_F32_CONFIG", "GEMM_B200_BF16_CONFIG", "GEMM_B200_MXFP8_CONFIG"):
+        assert knob in text

@@ -141,3 +141,14 @@ def test_argument_errors(ops):
     assert rc == L.ERR_INVALID_ARG
     rc = L.lib.gemm_b200_sgemm_f32(A.data_ptr(), A.data_ptr(), A.data_ptr(), -1, 4, 4, 4, 4, 4, None)
     assert rc == L.ERR_INVALID_ARG
+
+
+def test_log_and_forced_config_knobs(oracle):
+    # the knobs are read once per process, so exercise them in a child process
+    import os, subprocess, sys
+    code = ("import torch, gemm_b200.ops as ops; A = torch.ones(256, 64, device='cuda'); B = torch.ones(64, 256, device='cuda');"
+            "C = ops.sgemm_f32(A, B); torch.cuda.synchronize(); assert float(C[0, 0]) == 64.0")
+    env = dict(os.environ, GEMM_B200_LOG="1", GEMM_B200_F32_CONFIG="0")
+    r = subprocess.run([sys.executable, "-c", code], env=env, capture_output=True, text=True, cwd=str(__import__("pathlib").Path(__file__).resolve().parent.parent))
+    assert r.returncode == 0, r.stderr
+    assert "[gemm_b200] sgemm_f32 256x64x256 -> 128x128x16_s3" in r.stderr
