@@ -223,6 +223,7 @@ static const Bf16ConfigEntry kBf16Configs[] = {
     GEMM_B200_BF16_ENTRY("2cta_256x512x64_s3_tmastore2_maskcommit", Bf16_2cta_n512_s3),
 };
 constexpr int kNumBf16Configs = sizeof(kBf16Configs) / sizeof(kBf16Configs[0]);
+constexpr int kBf16Cfg1cta = 1;   // single CTA, 128x256 tiles, TMA store
 constexpr int kBf16Cfg256 = 4;    // CTA pair, 256x256 tiles, double-buffered accumulator
 constexpr int kBf16Cfg512 = 7;    // CTA pair, 256x512 tiles (A shared by two accumulators)
 
@@ -230,6 +231,9 @@ constexpr int kBf16Cfg512 = 7;    // CTA pair, 256x512 tiles (A shared by two ac
 // shapes fill their rounds equally well; with few tiles the coarser grid wastes more of the last
 // round of the persistent schedule.  Pick by estimated round efficiency.
 static int pick_bf16_config(int64_t M, int64_t N, int64_t K, int sms) {
+  // one row tile: the problem streams B from HBM; single-CTA tiles give twice as many independent
+  // streams (16 x 8192 x 28672: 91 us = 5.2 TB/s against 110-118 us with CTA pairs)
+  if (M <= kBlockM) return kBf16Cfg1cta;
   const int64_t clusters = sms / 2 > 0 ? sms / 2 : 1;
   auto eff = [&](int64_t tile_n) {
     const int64_t units = ceil_div64(M, 2 * kBlockM) * ceil_div64(N, tile_n);
