@@ -28,9 +28,47 @@ static EncodeTiledFn encode_tiled_fn() {
   return fn;
 }
 
+// Encoding a tensor map costs a microsecond or two on the host, and a GEMM call needs three to
+// five of them: for small problems that is a visible share of the call.  A descriptor depends only
+// on (address, shape, pitch, box, type, swizzle), so recently used ones are kept per thread.
+struct MapKey {
+  const void* ptr;
+  int64_t rows, cols, ld;
+  int box_cols, box_rows, dtype, swizzle;
+  bool operator==(const MapKey& o) const {
+    return ptr == o.ptr && rows == o.rows && cols == o.cols && ld == o.ld && box_cols == o.box_cols &&
+           box_rows == o.box_rows && dtype == o.dtype && swizzle == o.swizzle;
+  }
+};
+struct MapCache {
+  static constexpr int kEntries = 32;
+  MapKey keys[kEntries];
+  CUtensorMap maps[kEntries];
+  int used = 0, next = 0;
+  const CUtensorMap* find(const MapKey& k) const {
+    for (int i = 0; i < used; ++i)
+      if (keys[i] == k) return &maps[i];
+    return nullptr;
+  }
+  void insert(const MapKey& k, const CUtensorMap& m) {
+    const int slot = used < kEntries ? used++ : (next++ % kEntries);
+    keys[slot] = k;
+    maps[slot] = m;
+  }
+};
+static MapCache& map_cache() {
+  static thread_local MapCache c;
+  return c;
+}
+
 // 2-D row-major tensor [rows, cols] with `ld` elements between rows; box = box_cols x box_rows.
 static int make_map_2d(CUtensorMap* map, CUtensorMapDataType dt, int elem_bytes, const void* ptr, int64_t rows,
                        int64_t cols, int64_t ld, int box_cols, int box_rows, CUtensorMapSwizzle swz) {
+  const MapKey key{ptr, rows, cols, ld, box_cols, box_rows, (int)dt, (int)swz};
+  if (const CUtensorMap* hit = map_cache().find(key)) {
+    *map = *hit;
+    return GEMM_B200_OK;
+  }
   EncodeTiledFn fn = encode_tiled_fn();
   if (!fn) return fail(GEMM_B200_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
   cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
@@ -42,6 +80,7 @@ static int make_map_2d(CUtensorMap* map, CUtensorMapDataType dt, int elem_bytes,
   if (r != CUDA_SUCCESS)
     return fail(GEMM_B200_ERR_CUDA, "cuTensorMapEncodeTiled failed with CUresult %d (rows=%lld cols=%lld ld=%lld box=%dx%d)",
                 (int)r, (long long)rows, (long long)cols, (long long)ld, box_cols, box_rows);
+  map_cache().insert(key, *map);
   return GEMM_B200_OK;
 }
 
@@ -339,18 +378,9 @@ struct MxArgs {
 
 // packed scale buffer of `rows` rows viewed as int32 [row blocks][kchunks * 128]
 static int make_scale_map(CUtensorMap* map, const void* sf, int64_t rows, int64_t K, int box_blocks) {
-  EncodeTiledFn fn = encode_tiled_fn();
-  if (!fn) return fail(GEMM_B200_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
   const int64_t kchunks = ceil_div64(K / 32, 4), blocks = ceil_div64(rows, 128);
-  cuuint64_t dims[2] = {(cuuint64_t)(kchunks * 128), (cuuint64_t)blocks};
-  cuuint64_t strides[1] = {(cuuint64_t)(kchunks * 512)};
-  cuuint32_t box[2] = {128, (cuuint32_t)box_blocks};
-  cuuint32_t estr[2] = {1, 1};
-  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_INT32, 2, const_cast<void*>(sf), dims, strides, box, estr,
-                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  if (r != CUDA_SUCCESS) return fail(GEMM_B200_ERR_CUDA, "cuTensorMapEncodeTiled (scales) failed with CUresult %d", (int)r);
-  return GEMM_B200_OK;
+  return make_map_2d(map, CU_TENSOR_MAP_DATA_TYPE_INT32, 4, sf, blocks, kchunks * 128, kchunks * 128, 128, box_blocks,
+                     CU_TENSOR_MAP_SWIZZLE_NONE);
 }
 
 template <class Cfg, int OUT>

@@ -24,6 +24,29 @@ def _stream(t: torch.Tensor) -> int:
     return torch.cuda.current_stream(t.device).cuda_stream
 
 
+class _OnDevice:
+    """Makes the tensor's device current for the duration of a C-ABI call; free when it already is
+    (the usual case), which keeps the Python overhead of a small GEMM to a few microseconds."""
+
+    __slots__ = ("idx", "prev")
+
+    def __init__(self, device: torch.device):
+        self.idx = device.index if device.index is not None else torch.cuda.current_device()
+        self.prev = -1
+
+    def __enter__(self):
+        cur = torch.cuda.current_device()
+        if cur != self.idx:
+            self.prev = cur
+            torch.cuda.set_device(self.idx)
+        return self
+
+    def __exit__(self, *exc):
+        if self.prev >= 0:
+            torch.cuda.set_device(self.prev)
+        return False
+
+
 def _require(cond: bool, msg: str) -> None:
     if not cond:
         raise ValueError(msg)
@@ -45,7 +68,7 @@ def sgemm_f32(A: torch.Tensor, B: torch.Tensor, out: torch.Tensor | None = None,
     if out is None:
         out = torch.empty((M, N), device=A.device, dtype=torch.float32)
     _require(out.is_cuda and out.dtype == torch.float32 and tuple(out.shape) == (M, N), "bad out tensor")
-    with torch.cuda.device(A.device):
+    with _OnDevice(A.device):
         check(lib.gemm_b200_sgemm_f32_cfg(A.data_ptr(), B.data_ptr(), out.data_ptr(), M, N, K, _row_major_ld(A),
                                           _row_major_ld(B), _row_major_ld(out), config, _stream(A)))
     return out
@@ -70,7 +93,7 @@ def gemm_bf16(A: torch.Tensor, B: torch.Tensor, out: torch.Tensor | None = None,
     if out is None:
         out = torch.empty((M, N), device=A.device, dtype=out_dtype)
     _require(out.is_cuda and out.dtype == out_dtype and tuple(out.shape) == (M, N), "bad out tensor")
-    with torch.cuda.device(A.device):
+    with _OnDevice(A.device):
         check(lib.gemm_b200_gemm_bf16_cfg(
             A.data_ptr(), B.data_ptr(), out.data_ptr(), M, N, K, _row_major_ld(A), _row_major_ld(B), _row_major_ld(out),
             _lib.B_ROW_MAJOR_NK if b_is_nk else _lib.B_ROW_MAJOR_KN,
@@ -155,7 +178,7 @@ def quantize_mxfp8(X: torch.Tensor, transposed_in: bool = False) -> MxFp8Tensor:
     rows, K = int(rows), int(K)
     data = torch.empty((rows, K), device=X.device, dtype=torch.uint8)
     scales = torch.empty((max(int(lib.gemm_b200_mxfp8_scale_bytes(rows, K)), 1),), device=X.device, dtype=torch.uint8)
-    with torch.cuda.device(X.device):
+    with _OnDevice(X.device):
         check(lib.gemm_b200_quantize_mxfp8(X.data_ptr(), rows, K, ldx, 1 if transposed_in else 0, data.data_ptr(),
                                            scales.data_ptr(), _stream(X)))
     return MxFp8Tensor(data, scales, rows, K)
@@ -170,7 +193,7 @@ def gemm_mxfp8(A: MxFp8Tensor, B: MxFp8Tensor, out: torch.Tensor | None = None, 
     if out is None:
         out = torch.empty((M, N), device=A.data.device, dtype=out_dtype)
     _require(out.is_cuda and out.dtype == out_dtype and tuple(out.shape) == (M, N), "bad out tensor")
-    with torch.cuda.device(A.data.device):
+    with _OnDevice(A.data.device):
         check(lib.gemm_b200_gemm_mxfp8_cfg(A.data.data_ptr(), A.scales.data_ptr(), B.data.data_ptr(), B.scales.data_ptr(),
                                            out.data_ptr(), M, N, K, _row_major_ld(out),
                                            _lib.OUT_F32 if out_dtype == torch.float32 else _lib.OUT_BF16, config,
@@ -187,7 +210,7 @@ def gemm_mxfp8_quant_out(A: MxFp8Tensor, B: MxFp8Tensor) -> MxFp8Tensor:
     dev = A.data.device
     data = torch.empty((M, N), device=dev, dtype=torch.uint8)
     scales = torch.empty((max(int(lib.gemm_b200_mxfp8_scale_bytes(M, N)), 1),), device=dev, dtype=torch.uint8)
-    with torch.cuda.device(dev):
+    with _OnDevice(dev):
         check(lib.gemm_b200_gemm_mxfp8_quant_out(A.data.data_ptr(), A.scales.data_ptr(), B.data.data_ptr(), B.scales.data_ptr(),
                                                  data.data_ptr(), scales.data_ptr(), M, N, K, _stream(A.data)))
     return MxFp8Tensor(data, scales, M, N)
@@ -203,7 +226,7 @@ def gemm_mxfp8_splitk(A: MxFp8Tensor, B: MxFp8Tensor, k_splits: int, out: torch.
     need = int(lib.gemm_b200_gemm_mxfp8_splitk_scratch_bytes(M, N, k_splits))
     if scratch is None:
         scratch = torch.empty((max(need, 16),), device=A.data.device, dtype=torch.uint8)
-    with torch.cuda.device(A.data.device):
+    with _OnDevice(A.data.device):
         check(lib.gemm_b200_gemm_mxfp8_splitk(A.data.data_ptr(), A.scales.data_ptr(), B.data.data_ptr(), B.scales.data_ptr(),
                                               out.data_ptr(), M, N, K, _row_major_ld(out),
                                               _lib.OUT_F32 if out_dtype == torch.float32 else _lib.OUT_BF16, k_splits,
