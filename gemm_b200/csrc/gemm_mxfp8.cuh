@@ -285,12 +285,12 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
         // Round to bf16 first so the bytes equal "bf16 GEMM output, then quantise".
         const int64_t kchunks = (((int64_t)shape.N / 32) + 3) / 4;       // scale chunks per row block of C
         const int64_t rows_pad = (((int64_t)shape.M + 127) / 128) * 128;
+        // this thread's 4 blocks are blocks 4q .. 4q+3 of its row (col0 is a multiple of 128): their
+        // scale bytes are 4 consecutive, 4-byte-aligned bytes of the packed layout -> one 32-bit store
+        uint32_t scale_word = 0;
 #pragma unroll
         for (int c = 0; c < 4; ++c) {
           const int col = col0 + c * 32;
-          const int64_t nb = col / 32;                                   // block index along N
-          if (row >= rows_pad || nb >= kchunks * 4) continue;            // outside the padded scale buffer
-          uint32_t byte = 0;
           if (row < shape.M && col < shape.N) {
             uint32_t w[16], q[8];
 #pragma unroll
@@ -298,13 +298,16 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
               __nv_bfloat162 h = __floats2bfloat162_rn(__uint_as_float(v[c][2 * e]), __uint_as_float(v[c][2 * e + 1]));
               w[e] = *reinterpret_cast<uint32_t*>(&h);
             }
-            byte = mx::quantise_block(w, q);
+            const uint32_t byte = mx::quantise_block(w, q);
+            scale_word |= byte << (8 * c);
             uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<uint8_t*>(Cptr) + (int64_t)row * ldc + col);
             dst[0] = make_uint4(q[0], q[1], q[2], q[3]);
             dst[1] = make_uint4(q[4], q[5], q[6], q[7]);
           }
-          SFC[mx::scale_offset(kchunks, row, nb)] = (uint8_t)byte;      // padding rows / blocks get 0
         }
+        const int64_t nb0 = col0 / 32;
+        if (row < rows_pad && nb0 < kchunks * 4)                          // inside the padded scale buffer
+          *reinterpret_cast<uint32_t*>(SFC + mx::scale_offset(kchunks, row, nb0)) = scale_word;   // padding -> 0
       } else if (row < shape.M) {
 #pragma unroll
         for (int c = 0; c < 4; ++c) {

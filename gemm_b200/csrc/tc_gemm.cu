@@ -619,7 +619,7 @@ extern "C" int gemm_b200_gemm_mxfp8_quant_out(const void* Aq, const void* SFA, c
   if (M > 0x7fffffff || N > 0x7fffffff || K > 0x7fffffff)
     return fail(GEMM_B200_ERR_TOO_LARGE, "gemm_mxfp8_quant_out: a dimension exceeds 2^31-1");
   if ((reinterpret_cast<uintptr_t>(Aq) | reinterpret_cast<uintptr_t>(Bq) | reinterpret_cast<uintptr_t>(Cq) |
-       reinterpret_cast<uintptr_t>(SFA) | reinterpret_cast<uintptr_t>(SFB)) % 16 != 0)
+       reinterpret_cast<uintptr_t>(SFA) | reinterpret_cast<uintptr_t>(SFB) | reinterpret_cast<uintptr_t>(SFC)) % 16 != 0)
     return fail(GEMM_B200_ERR_ALIGNMENT, "gemm_mxfp8_quant_out: all pointers must be 16-byte aligned");
   tc::DeviceInfo di;
   if (int rc = tc::device_info(&di)) return rc;
