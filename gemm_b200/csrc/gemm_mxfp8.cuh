@@ -64,7 +64,6 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
                   uint8_t* __restrict__ SFC, const GemmShape shape) {
   constexpr int CG = Cfg::CG, STAGES = Cfg::STAGES;
   constexpr bool OUT_F32 = (OUT == 1);
-  static_assert(OUT != 2 || Cfg::EPI == 0, "the quantising epilogue uses direct stores");
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   const uint32_t sA0 = smem_base;
@@ -240,7 +239,7 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
         if constexpr (CG == 1) mbar_arrive(tempty_bar);
         else mbar_arrive_cluster(map_to_cta(tempty_bar, 0));
       }
-      if constexpr (Cfg::EPI == 1) {
+      if constexpr (Cfg::EPI == 1 && OUT != 2) {
         // 128-byte-wide slabs (64 bf16 or 32 f32 columns) of this warp's 32 rows: swizzled staging,
         // then one TMA store per slab; rows / columns outside C are clipped by the tensor map
         const uint32_t buf = sEpi0 + (uint32_t)(warp - 2) * Cfg::EPI_WARP_BUF;
@@ -288,6 +287,10 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
         // this thread's 4 blocks are blocks 4q .. 4q+3 of its row (col0 is a multiple of 128): their
         // scale bytes are 4 consecutive, 4-byte-aligned bytes of the packed layout -> one 32-bit store
         uint32_t scale_word = 0;
+        if constexpr (Cfg::EPI == 1) {
+          if (lane == 0) tma_store_wait_read<0>();   // the previous tile's store has read the staging buffer
+          __syncwarp();
+        }
 #pragma unroll
         for (int c = 0; c < 4; ++c) {
           const int col = col0 + c * 32;
@@ -300,9 +303,30 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
             }
             const uint32_t byte = mx::quantise_block(w, q);
             scale_word |= byte << (8 * c);
-            uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<uint8_t*>(Cptr) + (int64_t)row * ldc + col);
-            dst[0] = make_uint4(q[0], q[1], q[2], q[3]);
-            dst[1] = make_uint4(q[4], q[5], q[6], q[7]);
+            if constexpr (Cfg::EPI == 1) {
+              // stage this warp's 32 rows x 128 bytes (128-byte swizzle); chunks 2c and 2c + 1 of the row
+              const uint32_t row_addr = sEpi0 + (uint32_t)(warp - 2) * Cfg::EPI_WARP_BUF + (uint32_t)lane * 128u;
+              const uint32_t sw = (uint32_t)(lane & 7);
+              asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(row_addr + (((uint32_t)(2 * c) ^ sw) << 4)),
+                           "r"(q[0]), "r"(q[1]), "r"(q[2]), "r"(q[3]) : "memory");
+              asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(row_addr + (((uint32_t)(2 * c + 1) ^ sw) << 4)),
+                           "r"(q[4]), "r"(q[5]), "r"(q[6]), "r"(q[7]) : "memory");
+            } else {
+              uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<uint8_t*>(Cptr) + (int64_t)row * ldc + col);
+              dst[0] = make_uint4(q[0], q[1], q[2], q[3]);
+              dst[1] = make_uint4(q[4], q[5], q[6], q[7]);
+            }
+          }
+        }
+        if constexpr (Cfg::EPI == 1) {
+          // rows / columns outside C hold stale bytes in the staging buffer; the store clips them
+          fence_proxy_async_smem();
+          __syncwarp();
+          const int row0 = (tm * CG + (int)cta_rank) * kBlockM + quad * 32;
+          if (lane == 0) {
+            if (row0 < shape.M && col0 < shape.N)
+              tma_store_2d(&tmC, col0, row0, sEpi0 + (uint32_t)(warp - 2) * Cfg::EPI_WARP_BUF);
+            tma_store_commit();
           }
         }
         const int64_t nb0 = col0 / 32;

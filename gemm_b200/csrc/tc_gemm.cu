@@ -400,9 +400,13 @@ static int launch_mxfp8(const MxArgs& a) {
   if (int rc = make_scale_map(&tmSFB, a.SFB, a.N, a.K, 2)) return rc;
   CUtensorMap tmC = tmA;   // only read by the TMA-store epilogue
   if (Cfg::EPI == 1) {
-    if (int rc = make_map_2d(&tmC, OUT_F32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16,
-                             OUT_F32 ? 4 : 2, a.C, a.M, a.N, a.ldc, OUT_F32 ? 32 : 64, 32, CU_TENSOR_MAP_SWIZZLE_128B))
+    if (OUT == 2) {   // e4m3 bytes: 128 columns x 32 rows per store
+      if (int rc = make_map_2d(&tmC, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, a.C, a.M, a.N, a.ldc, 128, 32, CU_TENSOR_MAP_SWIZZLE_128B))
+        return rc;
+    } else if (int rc = make_map_2d(&tmC, OUT_F32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16,
+                                    OUT_F32 ? 4 : 2, a.C, a.M, a.N, a.ldc, OUT_F32 ? 32 : 64, 32, CU_TENSOR_MAP_SWIZZLE_128B)) {
       return rc;
+    }
   }
 
   auto kern = gemm_mxfp8_kernel<Cfg, OUT>;
@@ -627,7 +631,7 @@ extern "C" int gemm_b200_gemm_mxfp8_quant_out(const void* Aq, const void* SFA, c
     return fail(GEMM_B200_ERR_UNSUPPORTED, "gemm_mxfp8_quant_out: device has compute capability %d.x, need 10.x (sm_100a)", di.cc_major);
   tc::MxArgs args{Aq, SFA, Bq, SFB, Cq, M, N, K, /*ldc (bytes per row of Cq)*/ N, static_cast<cudaStream_t>(stream)};
   args.SFC = static_cast<uint8_t*>(SFC);
-  return (M <= 128) ? tc::launch_mxfp8<tc::Mx_1cta, 2>(args) : tc::launch_mxfp8<tc::Mx_2cta_m, 2>(args);
+  return (M <= 128) ? tc::launch_mxfp8<tc::Mx_1cta, 2>(args) : tc::launch_mxfp8<tc::Mx_2cta_m_tma, 2>(args);
 }
 
 extern "C" int gemm_b200_gemm_mxfp8_auto_splits(int64_t M, int64_t N, int64_t K) {
