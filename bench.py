@@ -222,6 +222,21 @@ def per_dtype_table(peaks: dict) -> dict:
             out[f"mxfp8_{M}x{K}x{N}"] = {"tflops": round(tf, 1), "frac_of_nominal_4500": round(tf / 4500.0, 4),
                                          "gbps": round(bytes_ / t / 1e9, 1),
                                          "frac_of_measured_hbm": round(bytes_ / t / 1e9 / float(peaks.get("hbm_gbs", 6650.0)), 4)}
+            if M < 1024:
+                # a ~50 us kernel: the host side of the call (Python, ctypes, launch) shows; replaying the
+                # same call from a CUDA graph leaves the device time
+                st = torch.cuda.Stream()
+                st.wait_stream(torch.cuda.current_stream())
+                with torch.cuda.stream(st):
+                    ops.gemm_mxfp8(Aq, Bq, C)
+                    graph = torch.cuda.CUDAGraph()
+                    with torch.cuda.graph(graph, stream=st):
+                        ops.gemm_mxfp8(Aq, Bq, C)
+                torch.cuda.current_stream().wait_stream(st)
+                t_g = time_alone(graph.replay)
+                out[f"mxfp8_{M}x{K}x{N}"]["gbps_cuda_graph"] = round(bytes_ / t_g / 1e9, 1)
+                out[f"mxfp8_{M}x{K}x{N}"]["frac_of_measured_hbm_cuda_graph"] = round(bytes_ / t_g / 1e9 / float(peaks.get("hbm_gbs", 6650.0)), 4)
+                del graph
             if M >= 1024:
                 # the same GEMM with the quantising epilogue vs GEMM (bf16 out) + separate quantise pass
                 t_f = time_alone(lambda: ops.gemm_mxfp8_quant_out(Aq, Bq), reps=5)
