@@ -24,6 +24,7 @@ SIGNATURES = {
     "gemm_b200_sgemm_f32_config_name": (C.c_char_p, [i32]),
     "gemm_b200_gemm_bf16": (i32, [vp, vp, vp, i64, i64, i64, i64, i64, i64, i32, i32, vp]),
     "gemm_b200_gemm_bf16_cfg": (i32, [vp, vp, vp, i64, i64, i64, i64, i64, i64, i32, i32, i32, vp]),
+    "gemm_b200_gemm_bf16_batched": (i32, [vp, vp, vp, i64, i64, i64, i64, i64, i64, i64, i64, i64, i64, i32, i32, vp]),
     "gemm_b200_gemm_bf16_num_configs": (i32, []),
     "gemm_b200_gemm_bf16_config_name": (C.c_char_p, [i32]),
     "gemm_b200_quantize_mxfp8": (i32, [vp, i64, i64, i64, i32, vp, vp, vp]),

@@ -74,6 +74,11 @@ struct GemmShape {
   // tiles, row index fastest) or of `-raster_group` column tiles (< 0: a band spans all row tiles,
   // column index fastest); the operand panel of the band stays in L2 while the other streams.
   int raster_group;
+  // batched BF16 GEMM: `batch` independent problems of the same shape; a work unit is
+  // (matrix, tile).  a_z / b_z are 1 when the operand has one matrix per problem and 0 when all
+  // problems share one (batch stride 0).  c_batch_stride: elements between the C matrices.
+  int batch, a_z, b_z;
+  int64_t c_batch_stride;
 };
 
 __device__ __forceinline__ void tile_coord(int t, const GemmShape& sh, int& tm, int& tn) {
@@ -117,7 +122,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   const uint32_t cta_rank = (CG == 2) ? cluster_ctarank() : 0u;
   const int cluster_id = blockIdx.x / CG;
   const int num_clusters = gridDim.x / CG;
-  const int num_tiles = shape.tiles_m * shape.tiles_n;
+  const int tiles_per_matrix = shape.tiles_m * shape.tiles_n;
+  const int num_tiles = tiles_per_matrix * shape.batch;
   const int num_kb = (shape.K + kBlockK - 1) / kBlockK;
 
   if (threadIdx.x == 0) {
@@ -155,14 +161,16 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
     if (lane == 0) {
-      auto load = [&](uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
-        if constexpr (CG == 1) tma_load_2d(dst, map, x, y, bar);
-        else tma_load_2d_pair(dst, map, x, y, bar);
+      auto load = [&](uint32_t dst, const CUtensorMap* map, int x, int y, int z, uint32_t bar) {
+        if constexpr (CG == 1) tma_load_3d(dst, map, x, y, z, bar);
+        else tma_load_3d_pair(dst, map, x, y, z, bar);
       };
       uint32_t it = 0;
       for (int t = cluster_id; t < num_tiles && !failed; t += num_clusters) {
         int tm, tn;
-        tile_coord(t, shape, tm, tn);
+        const int bi = t / tiles_per_matrix;
+        tile_coord(t - bi * tiles_per_matrix, shape, tm, tn);
+        const int az = bi * shape.a_z, bz = bi * shape.b_z;
         const int m0 = (tm * CG + (int)cta_rank) * kBlockM;
         for (int kb = 0; kb < num_kb; ++kb, ++it) {
           const int s = it % STAGES;
@@ -172,16 +180,16 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           // Both CTAs of a pair report their bytes to the leader's barrier.
           const uint32_t bar = (CG == 1) ? full_bar(s) : map_to_cta(full_bar(s), 0);
           if (cta_rank == 0) mbar_arrive_expect_tx(full_bar(s), CG * Cfg::STAGE_BYTES);
-          load(a_dst, &tmA, kb * kBlockK, m0, bar);
+          load(a_dst, &tmA, kb * kBlockK, m0, az, bar);
 #pragma unroll
           for (int nt = 0; nt < NT; ++nt) {
             const uint32_t b_dst = sB0 + (s * NT + nt) * Cfg::B_BYTES;
             const int n0 = (tn * NT + nt) * kBlockN + (int)cta_rank * Cfg::BN_CTA;
             if constexpr (B_MN) {
 #pragma unroll
-              for (int j = 0; j < Cfg::BN_CTA / 64; ++j) load(b_dst + j * 8192, &tmB, n0 + j * 64, kb * kBlockK, bar);
+              for (int j = 0; j < Cfg::BN_CTA / 64; ++j) load(b_dst + j * 8192, &tmB, n0 + j * 64, kb * kBlockK, bz, bar);
             } else {
-              load(b_dst, &tmB, kb * kBlockK, n0, bar);
+              load(b_dst, &tmB, kb * kBlockK, n0, bz, bar);
             }
           }
         }
@@ -243,7 +251,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     uint32_t acc_it = 0, store_it = 0;
     for (int t = cluster_id; t < num_tiles && !failed; t += num_clusters, ++acc_it) {
       int tm, tn;
-      tile_coord(t, shape, tm, tn);
+      const int bi = t / tiles_per_matrix;
+      tile_coord(t - bi * tiles_per_matrix, shape, tm, tn);
       const int m0 = (tm * CG + (int)cta_rank) * kBlockM + quad * 32;   // first row of this warp
       const int n0 = (tn * NT + nt_w) * kBlockN;
       const uint32_t acc = acc_it % ACC_STAGES, aph = (acc_it / ACC_STAGES) & 1u;
@@ -265,13 +274,13 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           const int col = n0 + c * 32;
           if (row < shape.M) {
             if constexpr (OUT_F32) {
-              float* dst = reinterpret_cast<float*>(Cptr) + (int64_t)row * ldc + col;
+              float* dst = reinterpret_cast<float*>(Cptr) + bi * shape.c_batch_stride + (int64_t)row * ldc + col;
 #pragma unroll
               for (int j = 0; j < 8; ++j)
                 if (col + 4 * j < shape.N)
                   *reinterpret_cast<uint4*>(dst + 4 * j) = make_uint4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
             } else {
-              __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(Cptr) + (int64_t)row * ldc + col;
+              __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(Cptr) + bi * shape.c_batch_stride + (int64_t)row * ldc + col;
 #pragma unroll
               for (int j = 0; j < 4; ++j) {
                 if (col + 8 * j < shape.N) {
@@ -327,7 +336,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           __syncwarp();
           const int x = n0 + c * 64;
           if (lane == 0) {
-            if (m0 < shape.M && x < shape.N) tma_store_2d(&tmC, x, m0, buf);
+            if (m0 < shape.M && x < shape.N) tma_store_3d(&tmC, x, m0, bi, buf);
             tma_store_commit();
           }
         }
@@ -375,7 +384,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           __syncwarp();
           const int x = n0 + c * SLAB_COLS;
           if (lane == 0) {
-            if (m0 < shape.M && x < shape.N) tma_store_2d(&tmC, x, m0, buf);
+            if (m0 < shape.M && x < shape.N) tma_store_3d(&tmC, x, m0, bi, buf);
             tma_store_commit();
           }
         }

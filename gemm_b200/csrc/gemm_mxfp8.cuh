@@ -129,30 +129,34 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
 
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
-    if (lane == 0) {
-      uint32_t it = 0;
-      for (int u = cluster_id; u < num_units && !failed; u += num_clusters) {
-        int t, split, kb0, kb1, tm, tn;
-        unit_range(u, t, split, kb0, kb1);
-        tile_coord(t, shape, tm, tn);
-        const int mblk = tm * CG + (int)cta_rank;            // 128-row block of A / C
-        const int m0 = mblk * kBlockM;
-        const int n0 = tn * kBlockN + (int)cta_rank * Cfg::BN_CTA;
-        for (int kb = kb0; kb < kb1; ++kb, ++it) {
-          const int s = it % STAGES;
-          const uint32_t ph = (it / STAGES) & 1u;
-          if (!mbar_wait(empty_bar(s), ph ^ 1u, kRoleProducer, s)) { failed = true; break; }
-          const uint32_t a_dst = sA0 + s * Cfg::A_BYTES, b_dst = sB0 + s * Cfg::B_BYTES;
-          const uint32_t sfa_dst = sSFA0 + s * Cfg::SFA_BYTES, sfb_dst = sSFB0 + s * Cfg::SFB_BYTES;
-          // scale maps: 32-bit elements, row = 128-row block, 128 elements (512 bytes) per K chunk
-          if constexpr (CG == 1) {
+    // The whole warp walks the schedule; one elected lane issues the copies.
+    const bool issuer = elect_one();
+    uint32_t it = 0;
+    for (int u = cluster_id; u < num_units && !failed; u += num_clusters) {
+      int t, split, kb0, kb1, tm, tn;
+      unit_range(u, t, split, kb0, kb1);
+      tile_coord(t, shape, tm, tn);
+      const int mblk = tm * CG + (int)cta_rank;            // 128-row block of A / C
+      const int m0 = mblk * kBlockM;
+      const int n0 = tn * kBlockN + (int)cta_rank * Cfg::BN_CTA;
+      for (int kb = kb0; kb < kb1; ++kb, ++it) {
+        const int s = it % STAGES;
+        const uint32_t ph = (it / STAGES) & 1u;
+        if (!mbar_wait_warp(empty_bar(s), ph ^ 1u, kRoleProducer, s)) { failed = true; break; }
+        const uint32_t a_dst = sA0 + s * Cfg::A_BYTES, b_dst = sB0 + s * Cfg::B_BYTES;
+        const uint32_t sfa_dst = sSFA0 + s * Cfg::SFA_BYTES, sfb_dst = sSFB0 + s * Cfg::SFB_BYTES;
+        // scale maps: 32-bit elements, row = 128-row block, 128 elements (512 bytes) per K chunk
+        if constexpr (CG == 1) {
+          if (issuer) {
             mbar_arrive_expect_tx(full_bar(s), Cfg::STAGE_BYTES);
             tma_load_2d(a_dst, &tmA, kb * kMxBlockK, m0, full_bar(s));
             tma_load_2d(b_dst, &tmB, kb * kMxBlockK, n0, full_bar(s));
             tma_load_2d(sfa_dst, &tmSFA, kb * 128, mblk, full_bar(s));
             tma_load_2d(sfb_dst, &tmSFB, kb * 128, tn * 2, full_bar(s));
-          } else {
-            const uint32_t lead_full = map_to_cta(full_bar(s), 0);
+          }
+        } else {
+          const uint32_t lead_full = map_to_cta(full_bar(s), 0);
+          if (issuer) {
             if (cta_rank == 0) mbar_arrive_expect_tx(full_bar(s), 2 * Cfg::STAGE_BYTES);
             tma_load_2d_pair(a_dst, &tmA, kb * kMxBlockK, m0, lead_full);
             tma_load_2d_pair(b_dst, &tmB, kb * kMxBlockK, n0, lead_full);
@@ -160,12 +164,15 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
             tma_load_2d_pair(sfb_dst, &tmSFB, kb * 128, tn * 2, lead_full);
           }
         }
+        __syncwarp();
       }
     }
-    __syncwarp();
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer (leader CTA)
-    if (lane == 0 && cta_rank == 0) {
+    // The whole warp runs the loop, so shared-memory addresses, descriptors and TMEM addresses
+    // are warp-uniform; one elected lane issues the tcgen05 instructions.
+    if (cta_rank == 0) {
+      const bool issuer = elect_one();
       constexpr uint64_t ab_hi = make_smem_desc_hi(16, 1024, kLayoutSw128);
       // scale chunk: 32 rows x 16 bytes, unswizzled, 8-row groups 128 bytes apart
       constexpr uint64_t sf_hi = make_smem_desc_hi(16, 128, kLayoutNone);
@@ -185,34 +192,38 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
       for (int u = cluster_id; u < num_units && !failed; u += num_clusters, ++acc_it) {
         int t, split, kb0, kb1;
         unit_range(u, t, split, kb0, kb1);
-        if (!mbar_wait(tempty_bar, (acc_it & 1u) ^ 1u, kRoleMma, 100)) { failed = true; break; }
+        if (!mbar_wait_warp(tempty_bar, (acc_it & 1u) ^ 1u, kRoleMma, 100)) { failed = true; break; }
         tc_fence_after_sync();
         for (int kb = kb0; kb < kb1; ++kb, ++it) {
           const int s = it % STAGES;
           const uint32_t ph = (it / STAGES) & 1u;
-          if (!mbar_wait(full_bar(s), ph, kRoleMma, s)) { failed = true; break; }
+          if (!mbar_wait_warp(full_bar(s), ph, kRoleMma, s)) { failed = true; break; }
           tc_fence_after_sync();
           const uint32_t a_addr = sA0 + s * Cfg::A_BYTES, b_addr = sB0 + s * Cfg::B_BYTES;
           const uint32_t sfa_addr = sSFA0 + s * Cfg::SFA_BYTES, sfb_addr = sSFB0 + s * Cfg::SFB_BYTES;
-          // tcgen05.cp and tcgen05.mma of one thread execute in issue order: these copies land
-          // after the previous block's MMAs have read the scale columns and before the next ones do
-          tmem_cp_32x128b_warpx4<CG>(sfa_tmem, smem_desc(sf_hi, sfa_addr));
-          tmem_cp_32x128b_warpx4<CG>(sfb_tmem, smem_desc(sf_hi, sfb_addr));
-          tmem_cp_32x128b_warpx4<CG>(sfb_tmem + 4, smem_desc(sf_hi, sfb_addr + 512));
+          const uint32_t first = (kb != kb0) ? 1u : 0u;
+          if (issuer) {
+            // tcgen05.cp and tcgen05.mma of one thread execute in issue order: these copies land
+            // after the previous block's MMAs have read the scale columns and before the next ones do
+            tmem_cp_32x128b_warpx4<CG>(sfa_tmem, smem_desc(sf_hi, sfa_addr));
+            tmem_cp_32x128b_warpx4<CG>(sfb_tmem, smem_desc(sf_hi, sfb_addr));
+            tmem_cp_32x128b_warpx4<CG>(sfb_tmem + 4, smem_desc(sf_hi, sfb_addr + 512));
 #pragma unroll
-          for (int k = 0; k < kMxBlockK / kMxUmmaK; ++k) {
-            // byte k of every 32-bit scale column belongs to this 32-wide K slice
-            const uint32_t idesc = make_idesc_mxf8(kBlockM * CG, kBlockN, k, k);
-            mma_mxf8<CG>(d_tmem, smem_desc(ab_hi, a_addr + k * kMxUmmaK), smem_desc(ab_hi, b_addr + k * kMxUmmaK), idesc,
-                         sfa_tmem + ((uint32_t)k << 30), sfb_tmem + ((uint32_t)k << 30), ((kb - kb0) | k) != 0 ? 1u : 0u);
+            for (int k = 0; k < kMxBlockK / kMxUmmaK; ++k) {
+              // byte k of every 32-bit scale column belongs to this 32-wide K slice
+              const uint32_t idesc = make_idesc_mxf8(kBlockM * CG, kBlockN, k, k);
+              mma_mxf8<CG>(d_tmem, smem_desc(ab_hi, a_addr + k * kMxUmmaK), smem_desc(ab_hi, b_addr + k * kMxUmmaK), idesc,
+                           sfa_tmem + ((uint32_t)k << 30), sfb_tmem + ((uint32_t)k << 30), k != 0 ? 1u : first);
+            }
+            commit(empty_bar(s));
           }
-          commit(empty_bar(s));
+          __syncwarp();
         }
         if (failed) break;
-        commit(tfull_bar);
+        if (issuer) commit(tfull_bar);
+        __syncwarp();
       }
     }
-    __syncwarp();
   } else {
     // ------------------------------------------------------------------ epilogue warps 2..9
     const int quad = warp & 3;             // TMEM lanes [32 quad, 32 quad + 32)

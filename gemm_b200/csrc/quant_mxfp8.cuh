@@ -81,53 +81,72 @@ quantize_rows_kernel(const __nv_bfloat16* __restrict__ X, int64_t rows, int64_t 
 }
 
 // X [K, rows] row-major (ldx): quantise every column along K, write Xq [rows, K] K-contiguous.
-// A CTA of 256 threads stages a 32 (k) x 256 (columns) tile in shared memory with 16-byte loads
-// (thread t loads 8 columns of k row t / 32 ... in four passes), then thread c owns column c:
-// it reads its 32 values down the tile, quantises and writes 32 contiguous bytes of Xq.
-__global__ void __launch_bounds__(256)
+// A CTA of 256 threads owns 128 k (one 4-block scale chunk) x 64 columns:
+//   1. the bf16 tile is staged with 16-byte loads, 8 threads per 128-byte row segment;
+//   2. thread (column c = t % 64, block kb = t / 64) reads its 32 values down the tile, quantises
+//      them and parks the 32 e4m3 bytes in a [64][128] byte tile, the scale byte in a [64][4] one;
+//   3. the byte tile leaves as whole 128-byte lines of Xq (8 threads x 16 bytes per row) and the
+//      four scale bytes of a row as one 32-bit word of the packed layout.
+// Every global access is a full line; rows of the shared tiles are padded by 16 bytes so that the
+// 16-byte accesses of a quarter warp and the 2-byte column walks fall in distinct banks.
+constexpr int kQcK = 128, kQcCols = 64;
+template <int COLS>
+__global__ void __launch_bounds__(COLS * 4)
 quantize_cols_kernel(const __nv_bfloat16* __restrict__ X, int64_t rows, int64_t K, int64_t ldx,
                      uint8_t* __restrict__ Xq, uint8_t* __restrict__ SF, int64_t kb_pad, int vec_ok) {
-  __shared__ __align__(16) uint16_t tile[32][256 + 8];
-  const int64_t c0 = (int64_t)blockIdx.x * 256, kb = blockIdx.y;
+  constexpr int kThreads = COLS * 4;
+  // the byte tile reuses the bf16 tile's storage once every thread holds its 32 values in registers
+  __shared__ __align__(16) uint16_t tile[kQcK][COLS + 8];
+  uint8_t (*qtile)[kQcK + 16] = reinterpret_cast<uint8_t (*)[kQcK + 16]>(&tile[0][0]);
+  __shared__ __align__(4) uint8_t sft[COLS][4];
+  const int64_t c0 = (int64_t)blockIdx.x * COLS, kc = blockIdx.y, k0 = kc * kQcK;
   const int64_t KB = K / 32, kchunks = kb_pad / 4;
   const int t = threadIdx.x;
-  const bool kb_ok = kb < KB;
-  if (kb_ok) {
-    const uint16_t* Xu = reinterpret_cast<const uint16_t*>(X);
-    if (vec_ok) {
-      // 32 threads x 8 columns cover the 256 columns of one k row; 8 k rows per pass
-      const int cg = (t & 31) * 8, kr = t >> 5;
+  const uint16_t* Xu = reinterpret_cast<const uint16_t*>(X);
+  if (vec_ok) {
+    constexpr int kPerRow = COLS / 8;          // threads per k row, 8 columns each; 32 k rows per pass
+    const int cg = (t % kPerRow) * 8, kr = t / kPerRow;
 #pragma unroll
-      for (int p = 0; p < 4; ++p) {
-        const int k = kr + 8 * p;
-        const int64_t c = c0 + cg;
-        uint4 v = make_uint4(0, 0, 0, 0);
-        if (c < rows) v = __ldg(reinterpret_cast<const uint4*>(Xu + (kb * 32 + k) * ldx + c));   // rows % 8 == 0 here
-        *reinterpret_cast<uint4*>(&tile[k][cg]) = v;
-      }
-    } else {
+    for (int p = 0; p < 4; ++p) {
+      const int k = kr + 32 * p;
+      uint4 v = make_uint4(0, 0, 0, 0);
+      if (k0 + k < K && c0 + cg < rows) v = __ldg(reinterpret_cast<const uint4*>(Xu + (k0 + k) * ldx + c0 + cg));   // rows % 8 == 0
+      *reinterpret_cast<uint4*>(&tile[k][cg]) = v;
+    }
+  } else {
+    const int c = t % COLS, kr = t / COLS;  // one thread per column, 4 k rows per pass
 #pragma unroll 4
-      for (int k = 0; k < 32; ++k) {
-        const int64_t c = c0 + t;
-        tile[k][t] = (c < rows) ? Xu[(kb * 32 + k) * ldx + c] : (uint16_t)0;
-      }
+    for (int p = 0; p < 32; ++p) {
+      const int k = kr + 4 * p;
+      tile[k][c] = (k0 + k < K && c0 + c < rows) ? Xu[(k0 + k) * ldx + c0 + c] : (uint16_t)0;
     }
   }
   __syncthreads();
-  const int64_t c = c0 + t;   // column of X = row of Xq
-  const int64_t rows_pad = ((rows + 127) / 128) * 128;
-  if (c >= rows_pad) return;
-  uint32_t byte = 0;
-  if (kb_ok && c < rows) {
+  {
+    const int c = t % COLS, kb = t / COLS;
     uint32_t w[16], q[8];
 #pragma unroll
-    for (int i = 0; i < 16; ++i) w[i] = (uint32_t)tile[2 * i][t] | ((uint32_t)tile[2 * i + 1][t] << 16);
-    byte = quantise_block(w, q);
-    uint4* dst = reinterpret_cast<uint4*>(Xq + c * K + kb * 32);
+    for (int i = 0; i < 16; ++i) w[i] = (uint32_t)tile[32 * kb + 2 * i][c] | ((uint32_t)tile[32 * kb + 2 * i + 1][c] << 16);
+    __syncthreads();
+    // columns / K-blocks past the end hold zeros: they quantise to byte 0, the padding value
+    const uint32_t byte = quantise_block(w, q);
+    uint4* dst = reinterpret_cast<uint4*>(&qtile[c][32 * kb]);
     dst[0] = make_uint4(q[0], q[1], q[2], q[3]);
     dst[1] = make_uint4(q[4], q[5], q[6], q[7]);
+    sft[c][kb] = (uint8_t)byte;
   }
-  SF[scale_offset(kchunks, c, kb)] = (uint8_t)byte;
+  __syncthreads();
+  {
+    const int j = t & 7, cr = t >> 3;             // 16-byte piece j of the row; half of the rows per pass
+#pragma unroll
+    for (int p = 0; p < 2; ++p) {
+      const int c = cr + (kThreads / 8) * p;
+      if (c0 + c < rows && kc * 4 + j / 2 < KB)
+        *reinterpret_cast<uint4*>(Xq + (c0 + c) * K + k0 + 16 * j) = *reinterpret_cast<const uint4*>(&qtile[c][16 * j]);
+    }
+  }
+  if (t < COLS)   // the launch covers rows up to a multiple of 128: padding rows get zero scales
+    *reinterpret_cast<uint32_t*>(SF + scale_offset(kchunks, c0 + t, kc * 4)) = *reinterpret_cast<const uint32_t*>(&sft[t][0]);
 }
 
 }  // namespace mx

@@ -33,11 +33,12 @@ static EncodeTiledFn encode_tiled_fn() {
 // on (address, shape, pitch, box, type, swizzle), so recently used ones are kept per thread.
 struct MapKey {
   const void* ptr;
-  int64_t rows, cols, ld;
+  int64_t rows, cols, ld, batch, batch_stride;   // batch == 0: a 2-D map
   int box_cols, box_rows, dtype, swizzle;
   bool operator==(const MapKey& o) const {
-    return ptr == o.ptr && rows == o.rows && cols == o.cols && ld == o.ld && box_cols == o.box_cols &&
-           box_rows == o.box_rows && dtype == o.dtype && swizzle == o.swizzle;
+    return ptr == o.ptr && rows == o.rows && cols == o.cols && ld == o.ld && batch == o.batch &&
+           batch_stride == o.batch_stride && box_cols == o.box_cols && box_rows == o.box_rows && dtype == o.dtype &&
+           swizzle == o.swizzle;
   }
 };
 struct MapCache {
@@ -64,7 +65,7 @@ static MapCache& map_cache() {
 // 2-D row-major tensor [rows, cols] with `ld` elements between rows; box = box_cols x box_rows.
 static int make_map_2d(CUtensorMap* map, CUtensorMapDataType dt, int elem_bytes, const void* ptr, int64_t rows,
                        int64_t cols, int64_t ld, int box_cols, int box_rows, CUtensorMapSwizzle swz) {
-  const MapKey key{ptr, rows, cols, ld, box_cols, box_rows, (int)dt, (int)swz};
+  const MapKey key{ptr, rows, cols, ld, 0, 0, box_cols, box_rows, (int)dt, (int)swz};
   if (const CUtensorMap* hit = map_cache().find(key)) {
     *map = *hit;
     return GEMM_B200_OK;
@@ -80,6 +81,33 @@ static int make_map_2d(CUtensorMap* map, CUtensorMapDataType dt, int elem_bytes,
   if (r != CUDA_SUCCESS)
     return fail(GEMM_B200_ERR_CUDA, "cuTensorMapEncodeTiled failed with CUresult %d (rows=%lld cols=%lld ld=%lld box=%dx%d)",
                 (int)r, (long long)rows, (long long)cols, (long long)ld, box_cols, box_rows);
+  map_cache().insert(key, *map);
+  return GEMM_B200_OK;
+}
+
+// `batch` row-major matrices [rows, cols] (pitch ld), `batch_stride` elements apart, as one 3-D
+// tensor (cols, rows, matrix); a box is one matrix deep.
+static int make_map_3d(CUtensorMap* map, CUtensorMapDataType dt, int elem_bytes, const void* ptr, int64_t rows,
+                       int64_t cols, int64_t ld, int64_t batch, int64_t batch_stride, int box_cols, int box_rows,
+                       CUtensorMapSwizzle swz) {
+  const MapKey key{ptr, rows, cols, ld, batch, batch_stride, box_cols, box_rows, (int)dt, (int)swz};
+  if (const CUtensorMap* hit = map_cache().find(key)) {
+    *map = *hit;
+    return GEMM_B200_OK;
+  }
+  EncodeTiledFn fn = encode_tiled_fn();
+  if (!fn) return fail(GEMM_B200_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
+  cuuint64_t dims[3] = {(cuuint64_t)cols, (cuuint64_t)rows, (cuuint64_t)batch};
+  cuuint64_t strides[2] = {(cuuint64_t)ld * (cuuint64_t)elem_bytes, (cuuint64_t)batch_stride * (cuuint64_t)elem_bytes};
+  cuuint32_t box[3] = {(cuuint32_t)box_cols, (cuuint32_t)box_rows, 1};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = fn(map, dt, 3, const_cast<void*>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, swz,
+                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS)
+    return fail(GEMM_B200_ERR_CUDA,
+                "cuTensorMapEncodeTiled failed with CUresult %d (rows=%lld cols=%lld ld=%lld batch=%lld stride=%lld box=%dx%d)",
+                (int)r, (long long)rows, (long long)cols, (long long)ld, (long long)batch, (long long)batch_stride,
+                box_cols, box_rows);
   map_cache().insert(key, *map);
   return GEMM_B200_OK;
 }
@@ -178,6 +206,8 @@ struct Bf16Args {
   void* C;
   int64_t M, N, K, lda, ldb, ldc;
   cudaStream_t stream;
+  // batched call: `batch` problems; a stride of 0 on A or B shares that operand between them
+  int64_t batch = 1, stride_a = 0, stride_b = 0, stride_c = 0;
 };
 
 // One instantiation per (config, B layout, output type).
@@ -187,21 +217,27 @@ static int launch_bf16(const Bf16Args& a) {
   DeviceInfo di;
   if (int rc = device_info(&di)) return rc;
   CUtensorMap tmA, tmB, tmC;
-  if (int rc = make_map_2d(&tmA, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, a.A, a.M, a.K, a.lda, kBlockK, kBlockM,
+  // a shared operand (stride 0) is mapped as one matrix; the kernel then always asks for matrix 0
+  const int64_t za = a.stride_a ? a.batch : 1, zb = a.stride_b ? a.batch : 1;
+  const int64_t sa = a.stride_a ? a.stride_a : a.M * a.lda;
+  const int64_t sb = a.stride_b ? a.stride_b : (B_MN ? a.K : a.N) * a.ldb;
+  const int64_t sc = a.batch > 1 ? a.stride_c : a.M * a.ldc;
+  if (int rc = make_map_3d(&tmA, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, a.A, a.M, a.K, a.lda, za, sa, kBlockK, kBlockM,
                            CU_TENSOR_MAP_SWIZZLE_128B))
     return rc;
   if (B_MN) {
-    if (int rc = make_map_2d(&tmB, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, a.B, a.K, a.N, a.ldb, 64, kBlockK,
+    if (int rc = make_map_3d(&tmB, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, a.B, a.K, a.N, a.ldb, zb, sb, 64, kBlockK,
                              CU_TENSOR_MAP_SWIZZLE_128B))
       return rc;
   } else {
-    if (int rc = make_map_2d(&tmB, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, a.B, a.N, a.K, a.ldb, kBlockK, Cfg::BN_CTA,
+    if (int rc = make_map_3d(&tmB, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, a.B, a.N, a.K, a.ldb, zb, sb, kBlockK, Cfg::BN_CTA,
                              CU_TENSOR_MAP_SWIZZLE_128B))
       return rc;
   }
   if (Cfg::EPI == 1) {
-    if (int rc = make_map_2d(&tmC, OUT_F32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16,
-                             OUT_F32 ? 4 : 2, a.C, a.M, a.N, a.ldc, OUT_F32 ? 32 : 64, 32, CU_TENSOR_MAP_SWIZZLE_128B))
+    if (int rc = make_map_3d(&tmC, OUT_F32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16,
+                             OUT_F32 ? 4 : 2, a.C, a.M, a.N, a.ldc, a.batch, sc, OUT_F32 ? 32 : 64, 32,
+                             CU_TENSOR_MAP_SWIZZLE_128B))
       return rc;
   } else {
     tmC = tmA;   // unused by the kernel
@@ -221,7 +257,11 @@ static int launch_bf16(const Bf16Args& a) {
   shape.kb_per_split = 0;
   shape.split_stride = 0;
   shape.raster_group = raster_group_for(shape.tiles_m, shape.tiles_n);
-  const int64_t num_tiles = (int64_t)shape.tiles_m * shape.tiles_n;
+  shape.batch = (int)a.batch;
+  shape.a_z = a.stride_a ? 1 : 0;
+  shape.b_z = a.stride_b ? 1 : 0;
+  shape.c_batch_stride = a.batch > 1 ? a.stride_c : 0;
+  const int64_t num_tiles = (int64_t)shape.tiles_m * shape.tiles_n * a.batch;
   if (num_tiles > 0x7fffffff) return fail(GEMM_B200_ERR_TOO_LARGE, "gemm_bf16: too many tiles");
   const int clusters = (int)(num_tiles < max_clusters ? num_tiles : max_clusters);
 
@@ -269,13 +309,13 @@ constexpr int kBf16Cfg512 = 7;    // CTA pair, 256x512 tiles (A shared by two ac
 // 256x512 tiles move 25 % fewer operand bytes per flop and measure ~4 % faster when both tile
 // shapes fill their rounds equally well; with few tiles the coarser grid wastes more of the last
 // round of the persistent schedule.  Pick by estimated round efficiency.
-static int pick_bf16_config(int64_t M, int64_t N, int64_t K, int sms) {
+static int pick_bf16_config(int64_t M, int64_t N, int64_t K, int sms, int64_t batch = 1) {
   // one row tile: the problem streams B from HBM; single-CTA tiles give twice as many independent
   // streams (16 x 8192 x 28672: 91 us = 5.2 TB/s against 110-118 us with CTA pairs)
   if (M <= kBlockM) return kBf16Cfg1cta;
   const int64_t clusters = sms / 2 > 0 ? sms / 2 : 1;
   auto eff = [&](int64_t tile_n) {
-    const int64_t units = ceil_div64(M, 2 * kBlockM) * ceil_div64(N, tile_n);
+    const int64_t units = batch * ceil_div64(M, 2 * kBlockM) * ceil_div64(N, tile_n);
     const double fill = (double)units / (double)(ceil_div64(units, clusters) * clusters);
     const double used = (double)N / (double)(ceil_div64(N, tile_n) * tile_n);   // columns of the last tile in use
     return fill * used;
@@ -289,28 +329,47 @@ static int pick_bf16_config(int64_t M, int64_t N, int64_t K, int sms) {
 }  // namespace tc
 }  // namespace gemm_b200
 
-extern "C" int gemm_b200_gemm_bf16_cfg(const void* A, const void* B, void* C, int64_t M, int64_t N, int64_t K,
-                                       int64_t lda, int64_t ldb, int64_t ldc, int b_layout, int out_dtype,
-                                       int config, void* stream) {
-  using namespace gemm_b200;
-  if (M < 0 || N < 0 || K < 0) return fail(GEMM_B200_ERR_INVALID_ARG, "gemm_bf16: negative size");
+namespace gemm_b200 {
+namespace tc {
+
+// Shared body of the plain and the batched BF16 entry points (batch == 1, strides 0: plain).
+static int bf16_entry(const void* A, const void* B, void* C, int64_t batch, int64_t M, int64_t N, int64_t K, int64_t lda,
+                      int64_t ldb, int64_t ldc, int64_t stride_a, int64_t stride_b, int64_t stride_c, int b_layout,
+                      int out_dtype, int config, void* stream) {
+  if (M < 0 || N < 0 || K < 0 || batch < 0) return fail(GEMM_B200_ERR_INVALID_ARG, "gemm_bf16: negative size");
   if (b_layout != GEMM_B200_B_ROW_MAJOR_KN && b_layout != GEMM_B200_B_ROW_MAJOR_NK)
     return fail(GEMM_B200_ERR_INVALID_ARG, "gemm_bf16: b_layout %d", b_layout);
   if (out_dtype != GEMM_B200_OUT_BF16 && out_dtype != GEMM_B200_OUT_F32)
     return fail(GEMM_B200_ERR_INVALID_ARG, "gemm_bf16: out_dtype %d", out_dtype);
-  if (config >= tc::kNumBf16Configs) return fail(GEMM_B200_ERR_INVALID_ARG, "gemm_bf16: config %d out of range", config);
-  if (M == 0 || N == 0) return GEMM_B200_OK;
+  if (config >= kNumBf16Configs) return fail(GEMM_B200_ERR_INVALID_ARG, "gemm_bf16: config %d out of range", config);
+  if (M == 0 || N == 0 || batch == 0) return GEMM_B200_OK;
   if (!C || (K > 0 && (!A || !B))) return fail(GEMM_B200_ERR_INVALID_ARG, "gemm_bf16: null pointer");
   const int64_t b_row = (b_layout == GEMM_B200_B_ROW_MAJOR_KN) ? N : K;
+  const int64_t b_rows = (b_layout == GEMM_B200_B_ROW_MAJOR_KN) ? K : N;
   if (lda < K || ldb < b_row || ldc < N)
     return fail(GEMM_B200_ERR_INVALID_ARG, "gemm_bf16: leading dimension smaller than the row (lda=%lld ldb=%lld ldc=%lld)",
                 (long long)lda, (long long)ldb, (long long)ldc);
-  if (M > 0x7fffffff || N > 0x7fffffff || K > 0x7fffffff)
+  if (M > 0x7fffffff || N > 0x7fffffff || K > 0x7fffffff || batch > 0x7fffffff)
     return fail(GEMM_B200_ERR_TOO_LARGE, "gemm_bf16: a dimension exceeds 2^31-1");
   const int c_elem = out_dtype == GEMM_B200_OUT_F32 ? 4 : 2;
+  if (batch > 1) {
+    // matrices of one operand must not interleave; 0 shares A or B between the problems
+    if (stride_a < 0 || stride_b < 0 || (stride_a != 0 && stride_a < (M - 1) * lda + K) ||
+        (stride_b != 0 && stride_b < (b_rows - 1) * ldb + b_row) || stride_c < (M - 1) * ldc + N)
+      return fail(GEMM_B200_ERR_INVALID_ARG,
+                  "gemm_bf16_batched: a batch stride is smaller than its matrix (stride_a=%lld stride_b=%lld stride_c=%lld)",
+                  (long long)stride_a, (long long)stride_b, (long long)stride_c);
+    if (stride_a % 8 != 0 || stride_b % 8 != 0 || (stride_c * c_elem) % 16 != 0)
+      return fail(GEMM_B200_ERR_ALIGNMENT,
+                  "gemm_bf16_batched: stride_a and stride_b must be multiples of 8, stride_c*sizeof(C) of 16 bytes");
+  } else {
+    stride_a = stride_b = stride_c = 0;
+  }
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   if (K == 0) {
-    GEMM_B200_CUDA_TRY(cudaMemset2DAsync(C, (size_t)ldc * c_elem, 0, (size_t)N * c_elem, (size_t)M, st));
+    for (int64_t b = 0; b < batch; ++b)
+      GEMM_B200_CUDA_TRY(cudaMemset2DAsync(static_cast<char*>(C) + b * stride_c * c_elem, (size_t)ldc * c_elem, 0,
+                                           (size_t)N * c_elem, (size_t)M, st));
     return GEMM_B200_OK;
   }
   if ((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(B) | reinterpret_cast<uintptr_t>(C)) % 16 != 0)
@@ -319,19 +378,38 @@ extern "C" int gemm_b200_gemm_bf16_cfg(const void* A, const void* B, void* C, in
     return fail(GEMM_B200_ERR_ALIGNMENT,
                 "gemm_bf16: lda and ldb must be multiples of 8, ldc*sizeof(C) and N*sizeof(C) multiples of 16 bytes "
                 "(lda=%lld ldb=%lld ldc=%lld N=%lld)", (long long)lda, (long long)ldb, (long long)ldc, (long long)N);
-  tc::DeviceInfo di;
-  if (int rc = tc::device_info(&di)) return rc;
+  DeviceInfo di;
+  if (int rc = device_info(&di)) return rc;
   if (di.cc_major != 10)
     return fail(GEMM_B200_ERR_UNSUPPORTED, "gemm_bf16: device has compute capability %d.x, need 10.x (sm_100a)", di.cc_major);
   if (config < 0) {
     static const int forced = env_int("GEMM_B200_BF16_CONFIG", -1);
-    config = (forced >= 0 && forced < tc::kNumBf16Configs) ? forced : tc::pick_bf16_config(M, N, K, di.sms);
+    // a batch of single-row-tile problems is a well-filled grid, not a skinny one
+    config = (forced >= 0 && forced < kNumBf16Configs) ? forced
+             : (batch > 1 && M <= kBlockM)             ? kBf16Cfg1cta
+                                                       : pick_bf16_config(M, N, K, di.sms, batch);
   }
   if (log_enabled())
-    fprintf(stderr, "[gemm_b200] gemm_bf16 %lldx%lldx%lld -> %s\n", (long long)M, (long long)K, (long long)N,
-            tc::kBf16Configs[config].name);
-  tc::Bf16Args args{A, B, C, M, N, K, lda, ldb, ldc, st};
-  return tc::kBf16Configs[config].launch[b_layout][out_dtype](args);
+    fprintf(stderr, "[gemm_b200] gemm_bf16 %lld x %lldx%lldx%lld -> %s\n", (long long)batch, (long long)M, (long long)K,
+            (long long)N, kBf16Configs[config].name);
+  Bf16Args args{A, B, C, M, N, K, lda, ldb, ldc, st, batch, stride_a, stride_b, stride_c};
+  return kBf16Configs[config].launch[b_layout][out_dtype](args);
+}
+
+}  // namespace tc
+}  // namespace gemm_b200
+
+extern "C" int gemm_b200_gemm_bf16_cfg(const void* A, const void* B, void* C, int64_t M, int64_t N, int64_t K,
+                                       int64_t lda, int64_t ldb, int64_t ldc, int b_layout, int out_dtype,
+                                       int config, void* stream) {
+  return gemm_b200::tc::bf16_entry(A, B, C, 1, M, N, K, lda, ldb, ldc, 0, 0, 0, b_layout, out_dtype, config, stream);
+}
+
+extern "C" int gemm_b200_gemm_bf16_batched(const void* A, const void* B, void* C, int64_t batch, int64_t M, int64_t N,
+                                           int64_t K, int64_t lda, int64_t ldb, int64_t ldc, int64_t stride_a,
+                                           int64_t stride_b, int64_t stride_c, int b_layout, int out_dtype, void* stream) {
+  return gemm_b200::tc::bf16_entry(A, B, C, batch, M, N, K, lda, ldb, ldc, stride_a, stride_b, stride_c, b_layout,
+                                   out_dtype, -1, stream);
 }
 
 extern "C" int gemm_b200_gemm_bf16(const void* A, const void* B, void* C, int64_t M, int64_t N, int64_t K,
@@ -421,6 +499,9 @@ static int launch_mxfp8(const MxArgs& a) {
   shape.tiles_n = (int)ceil_div64(a.N, kBlockN);
   const int num_kb = (int)ceil_div64(a.K, kMxBlockK);
   shape.kb_per_split = (int)ceil_div64(num_kb, a.k_splits);
+  shape.batch = 1;
+  shape.a_z = shape.b_z = 0;
+  shape.c_batch_stride = 0;
   shape.k_splits = (int)ceil_div64(num_kb, shape.kb_per_split);   // no empty split
   shape.split_stride = a.M * a.N;
   shape.raster_group = raster_group_for(shape.tiles_m, shape.tiles_n);
@@ -543,11 +624,11 @@ extern "C" int gemm_b200_quantize_mxfp8(const void* X, int64_t rows, int64_t K, 
                                                                static_cast<uint8_t*>(Xq), static_cast<uint8_t*>(SF),
                                                                kb_pad, rows_pad);
   } else {
-    if (kb_pad > 65535) return fail(GEMM_B200_ERR_TOO_LARGE, "quantize_mxfp8: K too large for the transposed path");
-    dim3 grid((unsigned)ceil_div64(rows_pad, 256), (unsigned)kb_pad);
+    if (kb_pad / 4 > 65535) return fail(GEMM_B200_ERR_TOO_LARGE, "quantize_mxfp8: K too large for the transposed path");
+    dim3 grid((unsigned)(rows_pad / mx::kQcCols), (unsigned)(kb_pad / 4));
     const int vec_ok = (reinterpret_cast<uintptr_t>(X) % 16 == 0 && ldx % 8 == 0 && rows % 8 == 0) ? 1 : 0;
-    mx::quantize_cols_kernel<<<grid, 256, 0, st>>>(static_cast<const __nv_bfloat16*>(X), rows, K, ldx,
-                                                   static_cast<uint8_t*>(Xq), static_cast<uint8_t*>(SF), kb_pad, vec_ok);
+    mx::quantize_cols_kernel<mx::kQcCols><<<grid, mx::kQcCols * 4, 0, st>>>(
+        static_cast<const __nv_bfloat16*>(X), rows, K, ldx, static_cast<uint8_t*>(Xq), static_cast<uint8_t*>(SF), kb_pad, vec_ok);
   }
   launch_counter().fetch_add(1, std::memory_order_relaxed);
   GEMM_B200_CUDA_TRY(cudaGetLastError());

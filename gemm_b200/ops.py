@@ -101,6 +101,46 @@ def gemm_bf16(A: torch.Tensor, B: torch.Tensor, out: torch.Tensor | None = None,
     return out
 
 
+def _batch_layout(t: torch.Tensor) -> tuple[int, int]:
+    """(row pitch, batch stride) in elements of a [batch, rows, cols] tensor whose matrices are row-major."""
+    _require(t.stride(2) == 1 or t.shape[2] == 1, "the last dimension of every matrix must be contiguous")
+    ld = t.stride(1) if t.shape[1] > 1 else max(t.shape[2], 1)
+    return ld, t.stride(0)
+
+
+def gemm_bf16_batched(A: torch.Tensor, B: torch.Tensor, out: torch.Tensor | None = None, *, b_is_nk: bool = False,
+                      out_dtype: torch.dtype = torch.bfloat16) -> torch.Tensor:
+    """``out[i] = A[i] @ B[i]`` for a batch of equally shaped BF16 problems in one launch.
+
+    ``A`` is ``[batch, M, K]``; ``B`` is ``[batch, K, N]`` (``[batch, N, K]`` with ``b_is_nk``) or a single
+    2-D matrix shared by every problem."""
+    _require(A.is_cuda and B.is_cuda, "A and B must be CUDA tensors")
+    _require(A.dtype == torch.bfloat16 and B.dtype == torch.bfloat16, "expected bfloat16")
+    _require(out_dtype in (torch.bfloat16, torch.float32), "out_dtype must be bfloat16 or float32")
+    _require(A.dim() == 3 and B.dim() in (2, 3), "A must be 3-D and B 2-D or 3-D")
+    batch, M, K = (int(x) for x in A.shape)
+    bk, bn = (-1, -2) if b_is_nk else (-2, -1)
+    N = int(B.shape[bn])
+    _require(B.shape[bk] == K and (B.dim() == 2 or B.shape[0] == batch), f"A is {tuple(A.shape)} but B is {tuple(B.shape)}")
+    lda, sa = _batch_layout(A)
+    if B.dim() == 3:
+        ldb, sb = _batch_layout(B)
+        if batch > 1:
+            _require(sb != 0, "pass a shared B as a 2-D tensor")
+    else:
+        ldb, sb = _row_major_ld(B), 0
+    if out is None:
+        out = torch.empty((batch, M, N), device=A.device, dtype=out_dtype)
+    _require(out.is_cuda and out.dtype == out_dtype and tuple(out.shape) == (batch, M, N), "bad out tensor")
+    ldc, sc = _batch_layout(out)
+    with _OnDevice(A.device):
+        check(lib.gemm_b200_gemm_bf16_batched(
+            A.data_ptr(), B.data_ptr(), out.data_ptr(), batch, M, N, K, lda, ldb, ldc, sa, sb, sc,
+            _lib.B_ROW_MAJOR_NK if b_is_nk else _lib.B_ROW_MAJOR_KN,
+            _lib.OUT_F32 if out_dtype == torch.float32 else _lib.OUT_BF16, _stream(A)))
+    return out
+
+
 def check_status(device: torch.device | None = None) -> None:
     """Synchronises the current stream and raises if a bounded device-side wait gave up."""
     dev = torch.device("cuda", torch.cuda.current_device()) if device is None else device

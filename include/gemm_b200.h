@@ -91,6 +91,20 @@ int gemm_b200_gemm_bf16_cfg(const void* A, const void* B, void* C,
 int gemm_b200_gemm_bf16_num_configs(void);
 const char* gemm_b200_gemm_bf16_config_name(int config);
 
+/* Strided-batched form: `batch` independent problems of one shape in one launch,
+ *   C_i[M,N] = A_i[M,K] @ B_i,   X_i = X + i * stride_x (strides in elements).
+ * The reference multiplies one pair of matrices per call (naive/naive.cpp:6-22);
+ * this is the loop a caller would write around it, scheduled as one persistent
+ * grid over all (matrix, tile) pairs.  stride_a == 0 or stride_b == 0 shares that
+ * operand between the problems (e.g. one weight matrix B for every A_i).
+ * Requirements as above; stride_a and stride_b multiples of 8 elements,
+ * stride_c * sizeof(C) a multiple of 16 bytes, the C matrices must not overlap. */
+int gemm_b200_gemm_bf16_batched(const void* A, const void* B, void* C, int64_t batch,
+                                int64_t M, int64_t N, int64_t K,
+                                int64_t lda, int64_t ldb, int64_t ldc,
+                                int64_t stride_a, int64_t stride_b, int64_t stride_c,
+                                int b_layout, int out_dtype, void* stream);
+
 /* -------------------------------------------------------------------------
  * MXFP8 (OCP microscaling): e4m3 data with one UE8M0 scale per 32 consecutive
  * K elements.  No counterpart in the reference; same operator semantics as
