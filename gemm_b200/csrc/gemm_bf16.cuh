@@ -160,25 +160,28 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
 
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
-    if (lane == 0) {
-      auto load = [&](uint32_t dst, const CUtensorMap* map, int x, int y, int z, uint32_t bar) {
-        if constexpr (CG == 1) tma_load_3d(dst, map, x, y, z, bar);
-        else tma_load_3d_pair(dst, map, x, y, z, bar);
-      };
-      uint32_t it = 0;
-      for (int t = cluster_id; t < num_tiles && !failed; t += num_clusters) {
-        int tm, tn;
-        const int bi = t / tiles_per_matrix;
-        tile_coord(t - bi * tiles_per_matrix, shape, tm, tn);
-        const int az = bi * shape.a_z, bz = bi * shape.b_z;
-        const int m0 = (tm * CG + (int)cta_rank) * kBlockM;
-        for (int kb = 0; kb < num_kb; ++kb, ++it) {
-          const int s = it % STAGES;
-          const uint32_t ph = (it / STAGES) & 1u;
-          if (!mbar_wait(empty_bar(s), ph ^ 1u, kRoleProducer, s)) { failed = true; break; }
-          const uint32_t a_dst = sA0 + s * Cfg::A_BYTES;
-          // Both CTAs of a pair report their bytes to the leader's barrier.
-          const uint32_t bar = (CG == 1) ? full_bar(s) : map_to_cta(full_bar(s), 0);
+    // The whole warp walks the schedule (coordinates and addresses stay warp-uniform); one
+    // elected lane issues the copies.
+    const bool issuer = elect_one();
+    auto load = [&](uint32_t dst, const CUtensorMap* map, int x, int y, int z, uint32_t bar) {
+      if constexpr (CG == 1) tma_load_3d(dst, map, x, y, z, bar);
+      else tma_load_3d_pair(dst, map, x, y, z, bar);
+    };
+    uint32_t it = 0;
+    for (int t = cluster_id; t < num_tiles && !failed; t += num_clusters) {
+      int tm, tn;
+      const int bi = t / tiles_per_matrix;
+      tile_coord(t - bi * tiles_per_matrix, shape, tm, tn);
+      const int az = bi * shape.a_z, bz = bi * shape.b_z;
+      const int m0 = (tm * CG + (int)cta_rank) * kBlockM;
+      for (int kb = 0; kb < num_kb; ++kb, ++it) {
+        const int s = it % STAGES;
+        const uint32_t ph = (it / STAGES) & 1u;
+        if (!mbar_wait_warp(empty_bar(s), ph ^ 1u, kRoleProducer, s)) { failed = true; break; }
+        const uint32_t a_dst = sA0 + s * Cfg::A_BYTES;
+        // Both CTAs of a pair report their bytes to the leader's barrier.
+        const uint32_t bar = (CG == 1) ? full_bar(s) : map_to_cta(full_bar(s), 0);
+        if (issuer) {
           if (cta_rank == 0) mbar_arrive_expect_tx(full_bar(s), CG * Cfg::STAGE_BYTES);
           load(a_dst, &tmA, kb * kBlockK, m0, az, bar);
 #pragma unroll
@@ -193,12 +196,15 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             }
           }
         }
+        __syncwarp();
       }
     }
-    __syncwarp();
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer (leader CTA)
-    if (lane == 0 && cta_rank == 0) {
+    // The whole warp runs the loop, so shared-memory addresses and descriptors are warp-uniform;
+    // one elected lane issues the tcgen05 instructions.
+    if (cta_rank == 0) {
+      const bool issuer = elect_one();
       constexpr uint32_t idesc = make_idesc_bf16(kBlockM * CG, kBlockN, 0, B_MN ? 1 : 0);
       constexpr uint64_t a_hi = make_smem_desc_hi(16, 1024, kLayoutSw128);
       constexpr uint64_t b_hi = B_MN ? make_smem_desc_hi(8192, 1024, kLayoutSw128)
@@ -217,31 +223,35 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       uint32_t it = 0, acc_it = 0;
       for (int t = cluster_id; t < num_tiles && !failed; t += num_clusters, ++acc_it) {
         const uint32_t acc = acc_it % ACC_STAGES, aph = (acc_it / ACC_STAGES) & 1u;
-        if (!mbar_wait(tempty_bar(acc), aph ^ 1u, kRoleMma, 100 + (int)acc)) { failed = true; break; }
+        if (!mbar_wait_warp(tempty_bar(acc), aph ^ 1u, kRoleMma, 100 + (int)acc)) { failed = true; break; }
         tc_fence_after_sync();
         const uint32_t d_tmem = tmem_base + acc * NT * kBlockN;   // NT accumulators of 256 columns
         for (int kb = 0; kb < num_kb; ++kb, ++it) {
           const int s = it % STAGES;
           const uint32_t ph = (it / STAGES) & 1u;
-          if (!mbar_wait(full_bar(s), ph, kRoleMma, s)) { failed = true; break; }
+          if (!mbar_wait_warp(full_bar(s), ph, kRoleMma, s)) { failed = true; break; }
           tc_fence_after_sync();
           const uint32_t a_addr = sA0 + s * Cfg::A_BYTES;
+          const uint32_t first = kb != 0 ? 1u : 0u;
+          if (issuer) {
 #pragma unroll
-          for (int k = 0; k < kBlockK / kUmmaK; ++k) {
+            for (int k = 0; k < kBlockK / kUmmaK; ++k) {
 #pragma unroll
-            for (int nt = 0; nt < NT; ++nt) {
-              const uint32_t b_addr = sB0 + (s * NT + nt) * Cfg::B_BYTES;
-              mma_f16<CG>(d_tmem + nt * kBlockN, smem_desc(a_hi, a_addr + k * (kUmmaK * 2)),
-                          smem_desc(b_hi, b_addr + k * b_kstep), idesc, (kb | k) != 0 ? 1u : 0u);
+              for (int nt = 0; nt < NT; ++nt) {
+                const uint32_t b_addr = sB0 + (s * NT + nt) * Cfg::B_BYTES;
+                mma_f16<CG>(d_tmem + nt * kBlockN, smem_desc(a_hi, a_addr + k * (kUmmaK * 2)),
+                            smem_desc(b_hi, b_addr + k * b_kstep), idesc, k != 0 ? 1u : first);
+              }
             }
+            commit(empty_bar(s));   // frees the smem slot in both CTAs once these MMAs have read it
           }
-          commit(empty_bar(s));   // frees the smem slot in both CTAs once these MMAs have read it
+          __syncwarp();
         }
         if (failed) break;
-        commit(tfull_bar(acc));   // accumulator complete -> epilogue warps of both CTAs
+        if (issuer) commit(tfull_bar(acc));   // accumulator complete -> epilogue warps of both CTAs
+        __syncwarp();
       }
     }
-    __syncwarp();
   } else {
     // ------------------------------------------------------------------ epilogue warps 2..
     const int quad = warp & 3;   // TMEM lanes [32 quad, 32 quad + 32) are the ones this warp may read
