@@ -37,12 +37,18 @@ constexpr int kMxSfbCol = 260;     // TMEM columns [260, 268): scales of B (256 
 
 // EPI: 0 = direct 16-byte global stores (also the split-K partial sums);
 //      1 = per-warp swizzled staging in shared memory + TMA store (full 128-byte lines).
-template <int CG_, int STAGES_, bool COMMIT_MASK_, int EPI_ = 0>
+// A_ROWS: rows of A a stage loads (the TMA box).  128 = the whole row block.  Fewer (skinny
+//      problems, M <= A_ROWS): the MMA still reads 128 rows of shared memory, but only the first
+//      A_ROWS are loaded; consecutive stages sit A_ROWS rows apart, so the rows above a stage's
+//      own are another stage's bytes or stale ones.  They only reach accumulator rows >= M, which
+//      are never stored, and the shared memory saved buys more stages of B in flight.
+template <int CG_, int STAGES_, bool COMMIT_MASK_, int EPI_ = 0, int A_ROWS_ = kBlockM>
 struct MxCfg {
-  static constexpr int CG = CG_, STAGES = STAGES_, EPI = EPI_;
+  static constexpr int CG = CG_, STAGES = STAGES_, EPI = EPI_, A_ROWS = A_ROWS_;
   static constexpr bool COMMIT_MASK = COMMIT_MASK_;
   static constexpr int BN_CTA = kBlockN / CG;
-  static constexpr int A_BYTES = kBlockM * kMxBlockK;       // 16 KB
+  static constexpr int A_BYTES = A_ROWS * kMxBlockK;        // bytes a stage loads and the stage pitch (16 KB for 128 rows)
+  static constexpr int A_RING_BYTES = STAGES * A_BYTES + (kBlockM - A_ROWS) * kMxBlockK;
   static constexpr int B_BYTES = BN_CTA * kMxBlockK;        // 32 KB / 16 KB
   static constexpr int SFA_BYTES = 512;
   static constexpr int SFB_BYTES = 1024;                    // 256 columns of C
@@ -50,7 +56,9 @@ struct MxCfg {
   static constexpr int EPI_WARP_BUF = 32 * 128;             // 32 rows x 128 bytes per epilogue warp
   static constexpr int EPI_BYTES = EPI == 1 ? 8 * EPI_WARP_BUF : 0;
   static constexpr int BAR_BYTES = (2 * STAGES + 2) * 8 + 16;
-  static constexpr int SMEM_BYTES = 1024 + STAGES * STAGE_BYTES + EPI_BYTES + BAR_BYTES;
+  static constexpr int SMEM_BYTES = 1024 + A_RING_BYTES + STAGES * (B_BYTES + SFA_BYTES + SFB_BYTES) + EPI_BYTES + BAR_BYTES;
+  static_assert(A_ROWS % 8 == 0 && A_ROWS >= 8 && A_ROWS <= kBlockM, "A rows per stage: whole 8-row swizzle atoms");
+  static_assert(A_ROWS == kBlockM || CG == 1, "narrow A stages are a single-CTA variant");
   static_assert(SMEM_BYTES <= 232448, "shared memory budget");
 };
 
@@ -67,7 +75,7 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   const uint32_t sA0 = smem_base;
-  const uint32_t sB0 = sA0 + STAGES * Cfg::A_BYTES;
+  const uint32_t sB0 = sA0 + Cfg::A_RING_BYTES;
   // epilogue staging right after the A/B ring keeps it 1024-byte aligned (128B-swizzled TMA store);
   // the scale ring (512 / 1024 bytes per stage) and the barriers follow
   const uint32_t sEpi0 = sB0 + STAGES * Cfg::B_BYTES;

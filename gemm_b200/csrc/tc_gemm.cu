@@ -474,7 +474,9 @@ static int launch_mxfp8(const MxArgs& a) {
   DeviceInfo di;
   if (int rc = device_info(&di)) return rc;
   CUtensorMap tmA, tmB, tmSFA, tmSFB;
-  if (int rc = make_map_2d(&tmA, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, a.Aq, a.M, a.K, a.K, kMxBlockK, kBlockM,
+  if (Cfg::A_ROWS != kBlockM && a.M > Cfg::A_ROWS)
+    return fail(GEMM_B200_ERR_INVALID_ARG, "gemm_mxfp8: this variant handles at most %d rows of A", Cfg::A_ROWS);
+  if (int rc = make_map_2d(&tmA, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, a.Aq, a.M, a.K, a.K, kMxBlockK, Cfg::A_ROWS,
                            CU_TENSOR_MAP_SWIZZLE_128B))
     return rc;
   if (int rc = make_map_2d(&tmB, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, a.Bq, a.N, a.K, a.K, kMxBlockK, Cfg::BN_CTA,
@@ -587,15 +589,18 @@ using Mx_1cta = MxCfg<1, 4, false>;
 using Mx_2cta = MxCfg<2, 6, false>;
 using Mx_2cta_m = MxCfg<2, 6, true>;
 using Mx_2cta_m_tma = MxCfg<2, 5, true, 1>;
+using Mx_1cta_a32 = MxCfg<1, 5, false, 0, 32>;   // M <= 32: 4 KB of A per stage, 5 stages of B in flight
 static const MxConfigEntry kMxConfigs[] = {
     {"1cta_128x256x128_s4", {launch_mxfp8<Mx_1cta, 0>, launch_mxfp8<Mx_1cta, 1>}},
     {"2cta_256x256x128_s6", {launch_mxfp8<Mx_2cta, 0>, launch_mxfp8<Mx_2cta, 1>}},
     {"2cta_256x256x128_s6_maskcommit", {launch_mxfp8<Mx_2cta_m, 0>, launch_mxfp8<Mx_2cta_m, 1>}},
     {"2cta_256x256x128_s5_maskcommit_tmastore", {launch_mxfp8<Mx_2cta_m_tma, 0>, launch_mxfp8<Mx_2cta_m_tma, 1>}},
+    {"1cta_32x256x128_s5_narrowA", {launch_mxfp8<Mx_1cta_a32, 0>, launch_mxfp8<Mx_1cta_a32, 1>}},
 };
 constexpr int kNumMxConfigs = sizeof(kMxConfigs) / sizeof(kMxConfigs[0]);
 constexpr int kDefaultMxConfig = 3;      // CTA pair, masked commit, TMA-store epilogue
 constexpr int kSkinnyMxConfig = 0;       // M <= 128: single-CTA tiles give more independent column tiles
+constexpr int kNarrowMxConfig = 4;       // M <= 32: the same with 32-row A stages and a deeper B pipeline
 
 }  // namespace tc
 }  // namespace gemm_b200
@@ -687,7 +692,7 @@ extern "C" int gemm_b200_gemm_mxfp8_cfg(const void* Aq, const void* SFA, const v
                   (long long)N, tc::kMxConfigs[tc::kSkinnyMxConfig].name, splits);
         return tc::launch_mxfp8_splitk<tc::Mx_1cta>(args, out_dtype);
       }
-      config = tc::kSkinnyMxConfig;
+      config = (M <= tc::Mx_1cta_a32::A_ROWS) ? tc::kNarrowMxConfig : tc::kSkinnyMxConfig;
     } else {
       config = tc::kDefaultMxConfig;
     }

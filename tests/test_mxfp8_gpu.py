@@ -43,6 +43,14 @@ def test_saturation_and_extremes(ops, oracle):
     assert int(q_want[0].max()) == 0x7E             # 448, the e4m3 maximum
 
 
+NARROW = "1cta_32x256x128_s5_narrowA"
+
+
+def _configs_for(ops, M):
+    """Every kernel variant that accepts M rows (the narrow-A variant takes at most 32)."""
+    return [i for i, name in enumerate(ops.gemm_mxfp8_configs()) if name != NARROW or M <= 32]
+
+
 def _gemm_check(ops, oracle, M, K, N, config=-1, seed=0):
     A, B = oracle.gen_randn_bf16(M, K, N, seed=seed)
     Aq = ops.quantize_mxfp8(A.cuda())
@@ -63,14 +71,39 @@ def _gemm_check(ops, oracle, M, K, N, config=-1, seed=0):
 @pytest.mark.parametrize("shape", [(128, 128, 256), (256, 512, 256), (512, 1024, 768), (1024, 4096, 1024)])
 def test_gemm_every_config(ops, oracle, shape):
     M, K, N = shape
-    for cfg in range(len(ops.gemm_mxfp8_configs())):
+    for cfg in _configs_for(ops, M):
         _gemm_check(ops, oracle, M, K, N, config=cfg, seed=cfg)
 
 
 @pytest.mark.parametrize("M,K,N", [(1, 32, 8), (16, 8192, 512), (100, 96, 40), (129, 160, 264), (300, 224, 1000), (2000, 992, 24)])
 def test_gemm_edge_shapes(ops, oracle, M, K, N):
-    for cfg in range(len(ops.gemm_mxfp8_configs())):
+    for cfg in _configs_for(ops, M):
         _gemm_check(ops, oracle, M, K, N, config=cfg, seed=M + N)
+
+
+@pytest.mark.parametrize("M,K,N", [(1, 128, 256), (16, 8192, 1024), (17, 640, 520), (32, 4096, 768), (32, 96, 8)])
+def test_narrow_a_variant(ops, oracle, M, K, N):
+    """M <= 32: stages load 32 rows of A and overlap in shared memory; rows >= M of the
+    accumulator see other stages' bytes and must never reach C."""
+    cfg = ops.gemm_mxfp8_configs().index(NARROW)
+    _gemm_check(ops, oracle, M, K, N, config=cfg, seed=M * 7 + N)
+    # the default path picks it, and agrees bit for bit with the full-height single-CTA variant
+    A, B = oracle.gen_randn_bf16(M, K, N, seed=5)
+    Aq = ops.quantize_mxfp8(A.cuda())
+    Bq = ops.quantize_mxfp8(B.cuda(), transposed_in=True)
+    got = ops.gemm_mxfp8(Aq, Bq, out_dtype=torch.float32, config=cfg)
+    full = ops.gemm_mxfp8(Aq, Bq, out_dtype=torch.float32, config=0)
+    ops.check_status()
+    assert torch.equal(got, full)
+
+
+def test_narrow_a_variant_rejects_taller_problems(ops):
+    import gemm_b200._lib as L
+    cfg = ops.gemm_mxfp8_configs().index(NARROW)
+    X = torch.zeros(64, 128, device="cuda", dtype=torch.bfloat16)
+    q = ops.quantize_mxfp8(X)
+    with pytest.raises(Exception, match="at most 32 rows"):
+        ops.gemm_mxfp8(q, q, config=cfg)
 
 
 def test_scales_matter(ops, oracle):
@@ -85,7 +118,7 @@ def test_scales_matter(ops, oracle):
     Aq = ops.quantize_mxfp8(A.cuda()); Bq = ops.quantize_mxfp8(B.cuda(), transposed_in=True)
     qa, sa = oracle.mxfp8_quantize(A); qb, sb = oracle.mxfp8_quantize(B.t().contiguous())
     want = oracle.mxfp8_matmul_oracle(qa, sa, qb, sb)
-    for cfg in range(len(ops.gemm_mxfp8_configs())):
+    for cfg in _configs_for(ops, M):
         got = ops.gemm_mxfp8(Aq, Bq, out_dtype=torch.float32, config=cfg)
         ops.check_status()
         err = ((got.cpu() - want).abs() / (want.abs() + 1e-30))
