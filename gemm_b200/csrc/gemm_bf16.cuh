@@ -6,7 +6,9 @@
 //
 // One persistent, warp-specialised kernel (192 threads):
 //   warp 0     TMA producer: 128B-swizzled tiles of A and B into a STAGES-deep smem ring;
-//   warp 1     owns TMEM; one thread issues tcgen05.mma (UMMA K = 16) and commits to mbarriers;
+//   warp 1     owns TMEM; issues tcgen05.mma (UMMA K = 16) and commits to mbarriers.  Warps 0
+//              and 1 run their loops as whole warps (warp-uniform addresses and descriptors);
+//              one elect.sync-elected lane executes the issuing instructions;
 //   warps 2-5  epilogue: tcgen05.ld the FP32 accumulator, convert, store (direct 16-byte global
 //              stores, or per-warp swizzled staging + TMA store).
 // The accumulator is double-buffered in TMEM (2 x 256 columns) so the epilogue of tile i

@@ -9,8 +9,10 @@
 // Persistent, warp-specialised, 320 threads:
 //   warp 0      TMA producer: A and B tiles (128 rows x 128 bytes, 128B swizzle) and the packed
 //               scale chunks of the same K range (512 bytes per 128 rows) into a smem ring;
-//   warp 1      owns TMEM; one thread copies the scales smem -> TMEM (tcgen05.cp) and issues
-//               tcgen05.mma kind::mxf8f6f4.block_scale (K = 32 per instruction);
+//   warp 1      owns TMEM; copies the scales smem -> TMEM (tcgen05.cp) and issues
+//               tcgen05.mma kind::mxf8f6f4.block_scale (K = 32 per instruction).  Warps 0 and 1
+//               run their loops as whole warps (warp-uniform addresses and descriptors) and
+//               one elect.sync-elected lane executes the issuing instructions;
 //   warps 2-9   epilogue: each warp pulls 32 rows x 128 columns of the accumulator into
 //               registers, releases the accumulator at once, then converts and stores (swizzled
 //               staging + TMA store, or direct 16-byte stores for split-K partial sums).
