@@ -197,6 +197,16 @@ int gemm_b200_release_workspace(void);
  * they give up.  Synchronises `stream`.  0 = clean, GEMM_B200_ERR_TIMEOUT
  * otherwise; `detail`, if not NULL, receives {code, block, role, stage}. */
 int gemm_b200_check_status(void* stream, int32_t detail[4]);
+/* Bandwidth probe: one launch that only streams the byte matrix X[rows, cols]
+ * through TMA into shared memory (no tensor-core work, no output), every CTA
+ * taking rows_per_cta rows.  pattern 0: 256-row x 128-byte boxes, 4 stages (the
+ * skinny GEMMs' B stream); 1: the same with 6 stages; 2: 64 rows x 512 bytes;
+ * 3: 32 rows x 1024 bytes.  Time it like a GEMM call to get the floor of a
+ * bandwidth-bound call.  rows % rows_per_cta == 0, rows_per_cta a multiple of the
+ * pattern's rows, cols a multiple of the pattern's bytes per row. */
+int gemm_b200_selftest_tma_stream(const void* X, int64_t rows, int64_t cols, int64_t rows_per_cta,
+                                  int pattern, void* stream);
+
 /* Self-test of the bounded-wait machinery: launches one warp that waits `limit_us` microseconds
  * (1 .. 100000) on a barrier nothing arrives on, then records the give-up in the status word and
  * returns normally (writing 1 to *device_flag, an int in device memory).  A following

@@ -34,3 +34,16 @@ def test_selftest_argument_checks():
     assert L.lib.gemm_b200_selftest_wait_timeout(0, None, None) == L.ERR_INVALID_ARG
     assert L.lib.gemm_b200_selftest_wait_timeout(10**7, None, None) == L.ERR_INVALID_ARG
     assert L.lib.gemm_b200_selftest_wait_timeout(100, None, None) == L.ERR_INVALID_ARG
+
+
+def test_tma_stream_probe_runs_and_validates(ops):
+    """The bandwidth probe streams a matrix through TMA and leaves the device status clean."""
+    import gemm_b200._lib as L
+    X = torch.ones(2048, 4096, device="cuda", dtype=torch.uint8)
+    st = torch.cuda.current_stream().cuda_stream
+    for pattern in range(4):
+        assert L.lib.gemm_b200_selftest_tma_stream(X.data_ptr(), 2048, 4096, 256, pattern, st) == L.OK
+    ops.check_status()
+    assert L.lib.gemm_b200_selftest_tma_stream(X.data_ptr(), 2048, 4096, 256, 9, st) == L.ERR_INVALID_ARG
+    assert L.lib.gemm_b200_selftest_tma_stream(X.data_ptr(), 2048, 4096, 100, 0, st) == L.ERR_INVALID_ARG
+    assert L.lib.gemm_b200_selftest_tma_stream(0, 2048, 4096, 256, 0, st) == L.ERR_INVALID_ARG
