@@ -25,6 +25,9 @@ SIGNATURES = {
     "gemm_b200_gemm_bf16": (i32, [vp, vp, vp, i64, i64, i64, i64, i64, i64, i32, i32, vp]),
     "gemm_b200_gemm_bf16_cfg": (i32, [vp, vp, vp, i64, i64, i64, i64, i64, i64, i32, i32, i32, vp]),
     "gemm_b200_gemm_bf16_batched": (i32, [vp, vp, vp, i64, i64, i64, i64, i64, i64, i64, i64, i64, i64, i32, i32, vp]),
+    "gemm_b200_gemm_bf16_splitk": (i32, [vp, vp, vp, i64, i64, i64, i64, i64, i64, i32, i32, i32, vp, sz, vp]),
+    "gemm_b200_gemm_bf16_splitk_scratch_bytes": (sz, [i64, i64, i32]),
+    "gemm_b200_gemm_bf16_auto_splits": (i32, [i64, i64, i64]),
     "gemm_b200_gemm_bf16_num_configs": (i32, []),
     "gemm_b200_gemm_bf16_config_name": (C.c_char_p, [i32]),
     "gemm_b200_quantize_mxfp8": (i32, [vp, i64, i64, i64, i32, vp, vp, vp]),

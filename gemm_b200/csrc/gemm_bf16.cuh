@@ -67,7 +67,7 @@ struct Bf16Cfg {
 struct GemmShape {
   int M, N, K;
   int tiles_m, tiles_n;   // work units of (kBlockM * CG) rows x (kBlockN * NT) columns
-  // split-K (block-scaled kernel only): every tile is cut into k_splits work units of
+  // split-K: every tile is cut into k_splits work units of
   // kb_per_split K blocks; unit (tile, split) writes FP32 partial sums to slice `split` of a
   // scratch buffer [k_splits][M][ldc].  k_splits == 1: the tile's result goes straight to C.
   int k_splits, kb_per_split;
@@ -125,8 +125,17 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   const int cluster_id = blockIdx.x / CG;
   const int num_clusters = gridDim.x / CG;
   const int tiles_per_matrix = shape.tiles_m * shape.tiles_n;
-  const int num_tiles = tiles_per_matrix * shape.batch;
   const int num_kb = (shape.K + kBlockK - 1) / kBlockK;
+  // work units: (matrix, tile, K split); consecutive units share the tile.  k_splits > 1 only with
+  // the direct-store FP32 epilogue: unit (tile, split) writes its partial sums to slice `split`
+  // of the scratch buffer Cptr ([k_splits][M][ldc] floats).
+  const int num_tiles = tiles_per_matrix * shape.batch * shape.k_splits;
+  auto unit_range = [&](int u, int& tile, int& split, int& kb0, int& kb1) {
+    tile = u / shape.k_splits;
+    split = u - tile * shape.k_splits;
+    kb0 = split * shape.kb_per_split;
+    kb1 = min(num_kb, kb0 + shape.kb_per_split);
+  };
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
@@ -170,13 +179,14 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       else tma_load_3d_pair(dst, map, x, y, z, bar);
     };
     uint32_t it = 0;
-    for (int t = cluster_id; t < num_tiles && !failed; t += num_clusters) {
-      int tm, tn;
+    for (int u = cluster_id; u < num_tiles && !failed; u += num_clusters) {
+      int t, split, kb0, kb1, tm, tn;
+      unit_range(u, t, split, kb0, kb1);
       const int bi = t / tiles_per_matrix;
       tile_coord(t - bi * tiles_per_matrix, shape, tm, tn);
       const int az = bi * shape.a_z, bz = bi * shape.b_z;
       const int m0 = (tm * CG + (int)cta_rank) * kBlockM;
-      for (int kb = 0; kb < num_kb; ++kb, ++it) {
+      for (int kb = kb0; kb < kb1; ++kb, ++it) {
         const int s = it % STAGES;
         const uint32_t ph = (it / STAGES) & 1u;
         if (!mbar_wait_warp(empty_bar(s), ph ^ 1u, kRoleProducer, s)) { failed = true; break; }
@@ -223,18 +233,20 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         }
       };
       uint32_t it = 0, acc_it = 0;
-      for (int t = cluster_id; t < num_tiles && !failed; t += num_clusters, ++acc_it) {
+      for (int u = cluster_id; u < num_tiles && !failed; u += num_clusters, ++acc_it) {
+        int t, split, kb0, kb1;
+        unit_range(u, t, split, kb0, kb1);
         const uint32_t acc = acc_it % ACC_STAGES, aph = (acc_it / ACC_STAGES) & 1u;
         if (!mbar_wait_warp(tempty_bar(acc), aph ^ 1u, kRoleMma, 100 + (int)acc)) { failed = true; break; }
         tc_fence_after_sync();
         const uint32_t d_tmem = tmem_base + acc * NT * kBlockN;   // NT accumulators of 256 columns
-        for (int kb = 0; kb < num_kb; ++kb, ++it) {
+        for (int kb = kb0; kb < kb1; ++kb, ++it) {
           const int s = it % STAGES;
           const uint32_t ph = (it / STAGES) & 1u;
           if (!mbar_wait_warp(full_bar(s), ph, kRoleMma, s)) { failed = true; break; }
           tc_fence_after_sync();
           const uint32_t a_addr = sA0 + s * Cfg::A_BYTES;
-          const uint32_t first = kb != 0 ? 1u : 0u;
+          const uint32_t first = kb != kb0 ? 1u : 0u;
           if (issuer) {
 #pragma unroll
             for (int k = 0; k < kBlockK / kUmmaK; ++k) {
@@ -261,8 +273,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     const uint32_t lane_base = (uint32_t)(quad * 32) << 16;
     const uint32_t stage0 = sEpi0 + (uint32_t)(warp - 2) * (uint32_t)Cfg::EPI_BUFS * Cfg::EPI_WARP_BUF;
     uint32_t acc_it = 0, store_it = 0;
-    for (int t = cluster_id; t < num_tiles && !failed; t += num_clusters, ++acc_it) {
-      int tm, tn;
+    for (int u = cluster_id; u < num_tiles && !failed; u += num_clusters, ++acc_it) {
+      int t, split, kb0, kb1, tm, tn;
+      unit_range(u, t, split, kb0, kb1);
       const int bi = t / tiles_per_matrix;
       tile_coord(t - bi * tiles_per_matrix, shape, tm, tn);
       const int m0 = (tm * CG + (int)cta_rank) * kBlockM + quad * 32;   // first row of this warp
@@ -286,7 +299,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           const int col = n0 + c * 32;
           if (row < shape.M) {
             if constexpr (OUT_F32) {
-              float* dst = reinterpret_cast<float*>(Cptr) + bi * shape.c_batch_stride + (int64_t)row * ldc + col;
+              float* dst = reinterpret_cast<float*>(Cptr) + bi * shape.c_batch_stride + split * shape.split_stride + (int64_t)row * ldc + col;
 #pragma unroll
               for (int j = 0; j < 8; ++j)
                 if (col + 4 * j < shape.N)

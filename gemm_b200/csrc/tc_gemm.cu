@@ -207,6 +207,55 @@ static int launch_clusters(Kern kern, int clusters, int cg, int threads, int sme
   return GEMM_B200_OK;
 }
 
+// Number of K splits for a problem whose tiles alone do not fill the GPU: the split count that
+// wastes the fewest CTA slots in the last round, mildly preferring fewer splits (each split
+// writes and re-reads an M x N FP32 slice).  1 = do not split.
+static int auto_splits_units(int64_t tiles, int64_t num_kb, int sms) {
+  // Splitting pays for a second (reduce) launch and an M x N FP32 round trip per split: measured on
+  // B200, 112 tiles on 148 SMs run as fast unsplit (16 x 8192 x 28672: 62 us either way; 64 rows:
+  // 62 us unsplit, 70 us split), 32 tiles do not (128 x 8192 x 8192: 42 -> 34 us; 16 x 16384 x 4096
+  // with 16 tiles: 64 -> 28 us).  Split only when the tiles leave more than a third of the SMs idle.
+  if (3 * tiles >= 2 * (int64_t)sms || num_kb < 8) return 1;
+  int best = 1;
+  double best_score = (double)tiles / (double)(ceil_div64(tiles, sms) * sms);
+  for (int s = 2; s <= 16 && num_kb / s >= 4; ++s) {
+    const int64_t kb_per = ceil_div64(num_kb, s);
+    if (ceil_div64(num_kb, kb_per) != s) continue;
+    const int64_t units = tiles * s;
+    const double score = (double)units / (double)(ceil_div64(units, sms) * sms) - 0.01 * s;
+    if (score > best_score + 1e-9) { best_score = score; best = s; }
+  }
+  return best;
+}
+
+static int auto_splits(int64_t M, int64_t N, int64_t K, int sms) {
+  return auto_splits_units(ceil_div64(M, kBlockM) * ceil_div64(N, kBlockN), ceil_div64(K, kMxBlockK), sms);
+}
+
+// library-owned scratch for the automatic split-K path, one buffer per device, grown on demand
+static std::mutex g_scratch_mu;
+static void* g_scratch[64] = {nullptr};
+static size_t g_scratch_bytes[64] = {0};
+// *out stays null (and the call succeeds) when the buffer would have to grow while `stream` is
+// being captured into a graph: allocation is not allowed there, and the caller runs unsplit.
+static int cached_scratch(int dev, size_t bytes, float** out, cudaStream_t stream) {
+  std::lock_guard<std::mutex> lk(g_scratch_mu);
+  const int slot = dev & 63;
+  *out = nullptr;
+  if (g_scratch_bytes[slot] < bytes) {
+    cudaStreamCaptureStatus cs = cudaStreamCaptureStatusNone;
+    GEMM_B200_CUDA_TRY(cudaStreamIsCapturing(stream, &cs));
+    if (cs != cudaStreamCaptureStatusNone) return GEMM_B200_OK;
+    if (g_scratch[slot]) GEMM_B200_CUDA_TRY(cudaFree(g_scratch[slot]));
+    g_scratch[slot] = nullptr;
+    g_scratch_bytes[slot] = 0;
+    GEMM_B200_CUDA_TRY(cudaMalloc(&g_scratch[slot], bytes));
+    g_scratch_bytes[slot] = bytes;
+  }
+  *out = static_cast<float*>(g_scratch[slot]);
+  return GEMM_B200_OK;
+}
+
 struct Bf16Args {
   const void *A, *B;
   void* C;
@@ -214,6 +263,8 @@ struct Bf16Args {
   cudaStream_t stream;
   // batched call: `batch` problems; a stride of 0 on A or B shares that operand between them
   int64_t batch = 1, stride_a = 0, stride_b = 0, stride_c = 0;
+  // split-K (direct-store FP32 variants only): C is then the scratch [k_splits][M][N], ldc = N
+  int k_splits = 1;
 };
 
 // One instantiation per (config, B layout, output type).
@@ -259,15 +310,18 @@ static int launch_bf16(const Bf16Args& a) {
   shape.K = (int)a.K;
   shape.tiles_m = (int)ceil_div64(a.M, kBlockM * CG);
   shape.tiles_n = (int)ceil_div64(a.N, Cfg::TILE_N);
-  shape.k_splits = 1;
-  shape.kb_per_split = 0;
-  shape.split_stride = 0;
+  const int num_kb = (int)ceil_div64(a.K, kBlockK);
+  if (a.k_splits > 1 && !(Cfg::EPI == 0 && OUT_F32 && a.batch == 1))
+    return fail(GEMM_B200_ERR_INVALID_ARG, "gemm_bf16: K splits need the direct-store FP32 variant and one problem");
+  shape.kb_per_split = (int)ceil_div64(num_kb, a.k_splits);
+  shape.k_splits = (int)ceil_div64(num_kb, shape.kb_per_split);   // no empty split
+  shape.split_stride = a.M * a.ldc;
   shape.raster_group = raster_group_for(shape.tiles_m, shape.tiles_n);
   shape.batch = (int)a.batch;
   shape.a_z = a.stride_a ? 1 : 0;
   shape.b_z = a.stride_b ? 1 : 0;
   shape.c_batch_stride = a.batch > 1 ? a.stride_c : 0;
-  const int64_t num_tiles = (int64_t)shape.tiles_m * shape.tiles_n * a.batch;
+  const int64_t num_tiles = (int64_t)shape.tiles_m * shape.tiles_n * a.batch * shape.k_splits;
   if (num_tiles > 0x7fffffff) return fail(GEMM_B200_ERR_TOO_LARGE, "gemm_bf16: too many tiles");
   const int clusters = (int)(num_tiles < max_clusters ? num_tiles : max_clusters);
 
@@ -332,6 +386,37 @@ static int pick_bf16_config(int64_t M, int64_t N, int64_t K, int sms, int64_t ba
   return (gain * eff(2 * kBlockN) >= eff(kBlockN)) ? kBf16Cfg512 : kBf16Cfg256;
 }
 
+// Split-K BF16 GEMM: FP32 partial sums of every (tile, K range) unit go to `scratch`
+// ([k_splits][M][N] floats) from single-CTA direct-store tiles, then one pass sums the slices in
+// ascending split order and writes C.
+static int launch_bf16_splitk(const Bf16Args& a, int b_layout, int out_dtype, int k_splits, float* scratch) {
+  Bf16Args part = a;
+  part.C = scratch;
+  part.ldc = a.N;
+  part.k_splits = k_splits;
+  if (int rc = (b_layout == GEMM_B200_B_ROW_MAJOR_KN) ? launch_bf16<Bf16_1cta_direct, true, true>(part)
+                                                      : launch_bf16<Bf16_1cta_direct, false, true>(part))
+    return rc;
+  const int num_kb = (int)ceil_div64(a.K, kBlockK);
+  const int kb_per = (int)ceil_div64(num_kb, k_splits);
+  const int splits = (int)ceil_div64(num_kb, kb_per);
+  const int64_t threads = a.M * (a.N / 4);
+  const unsigned blocks = (unsigned)ceil_div64(threads, 256);
+  if (out_dtype == GEMM_B200_OUT_F32)
+    splitk_reduce_kernel<true><<<blocks, 256, 0, a.stream>>>(scratch, a.M * a.N, a.N, splits, a.C, a.ldc, (int)a.M, (int)a.N);
+  else
+    splitk_reduce_kernel<false><<<blocks, 256, 0, a.stream>>>(scratch, a.M * a.N, a.N, splits, a.C, a.ldc, (int)a.M, (int)a.N);
+  launch_counter().fetch_add(1, std::memory_order_relaxed);
+  GEMM_B200_CUDA_TRY(cudaGetLastError());
+  return GEMM_B200_OK;
+}
+
+static int bf16_auto_splits(int64_t M, int64_t N, int64_t K, int sms) {
+  // K blocks of 64 here; ask for at least 8 of them per split
+  const int s = auto_splits_units(ceil_div64(M, kBlockM) * ceil_div64(N, kBlockN), ceil_div64(K, 2 * kBlockK), sms);
+  return (N % 4 == 0) ? s : 1;
+}
+
 }  // namespace tc
 }  // namespace gemm_b200
 
@@ -339,9 +424,11 @@ namespace gemm_b200 {
 namespace tc {
 
 // Shared body of the plain and the batched BF16 entry points (batch == 1, strides 0: plain).
+// k_splits: 0 = let the library decide (its own scratch), 1 = never split, > 1 = split into that
+// many K ranges on `scratch` (k_splits * M * N floats).
 static int bf16_entry(const void* A, const void* B, void* C, int64_t batch, int64_t M, int64_t N, int64_t K, int64_t lda,
                       int64_t ldb, int64_t ldc, int64_t stride_a, int64_t stride_b, int64_t stride_c, int b_layout,
-                      int out_dtype, int config, void* stream) {
+                      int out_dtype, int config, void* stream, int k_splits = 0, float* scratch = nullptr) {
   if (M < 0 || N < 0 || K < 0 || batch < 0) return fail(GEMM_B200_ERR_INVALID_ARG, "gemm_bf16: negative size");
   if (b_layout != GEMM_B200_B_ROW_MAJOR_KN && b_layout != GEMM_B200_B_ROW_MAJOR_NK)
     return fail(GEMM_B200_ERR_INVALID_ARG, "gemm_bf16: b_layout %d", b_layout);
@@ -388,6 +475,22 @@ static int bf16_entry(const void* A, const void* B, void* C, int64_t batch, int6
   if (int rc = device_info(&di)) return rc;
   if (di.cc_major != 10)
     return fail(GEMM_B200_ERR_UNSUPPORTED, "gemm_bf16: device has compute capability %d.x, need 10.x (sm_100a)", di.cc_major);
+  Bf16Args args{A, B, C, M, N, K, lda, ldb, ldc, st, batch, stride_a, stride_b, stride_c};
+  if (k_splits > 1) return launch_bf16_splitk(args, b_layout, out_dtype, k_splits, scratch);
+  if (config < 0 && k_splits == 0 && batch == 1) {
+    // few output tiles and a long K: cut K so the whole GPU works on the problem
+    const int splits = bf16_auto_splits(M, N, K, di.sms);
+    if (splits > 1) {
+      float* ws = nullptr;
+      if (int rc = cached_scratch(di.dev, (size_t)splits * M * N * sizeof(float), &ws, st)) return rc;
+      if (ws) {
+        if (log_enabled())
+          fprintf(stderr, "[gemm_b200] gemm_bf16 %lldx%lldx%lld -> %s, %d K splits\n", (long long)M, (long long)K,
+                  (long long)N, kBf16Configs[0].name, splits);
+        return launch_bf16_splitk(args, b_layout, out_dtype, splits, ws);
+      }
+    }
+  }
   if (config < 0) {
     static const int forced = env_int("GEMM_B200_BF16_CONFIG", -1);
     // a batch of single-row-tile problems is a well-filled grid, not a skinny one
@@ -398,7 +501,6 @@ static int bf16_entry(const void* A, const void* B, void* C, int64_t batch, int6
   if (log_enabled())
     fprintf(stderr, "[gemm_b200] gemm_bf16 %lld x %lldx%lldx%lld -> %s\n", (long long)batch, (long long)M, (long long)K,
             (long long)N, kBf16Configs[config].name);
-  Bf16Args args{A, B, C, M, N, K, lda, ldb, ldc, st, batch, stride_a, stride_b, stride_c};
   return kBf16Configs[config].launch[b_layout][out_dtype](args);
 }
 
@@ -409,6 +511,34 @@ extern "C" int gemm_b200_gemm_bf16_cfg(const void* A, const void* B, void* C, in
                                        int64_t lda, int64_t ldb, int64_t ldc, int b_layout, int out_dtype,
                                        int config, void* stream) {
   return gemm_b200::tc::bf16_entry(A, B, C, 1, M, N, K, lda, ldb, ldc, 0, 0, 0, b_layout, out_dtype, config, stream);
+}
+
+extern "C" size_t gemm_b200_gemm_bf16_splitk_scratch_bytes(int64_t M, int64_t N, int k_splits) {
+  if (M <= 0 || N <= 0 || k_splits <= 0) return 0;
+  return (size_t)k_splits * (size_t)M * (size_t)N * sizeof(float);
+}
+
+extern "C" int gemm_b200_gemm_bf16_auto_splits(int64_t M, int64_t N, int64_t K) {
+  gemm_b200::tc::DeviceInfo di;
+  if (gemm_b200::tc::device_info(&di)) return 1;
+  return gemm_b200::tc::bf16_auto_splits(M, N, K, di.sms);
+}
+
+extern "C" int gemm_b200_gemm_bf16_splitk(const void* A, const void* B, void* C, int64_t M, int64_t N, int64_t K,
+                                          int64_t lda, int64_t ldb, int64_t ldc, int b_layout, int out_dtype,
+                                          int k_splits, void* scratch, size_t scratch_bytes, void* stream) {
+  using namespace gemm_b200;
+  if (k_splits < 1 || k_splits > 64) return fail(GEMM_B200_ERR_INVALID_ARG, "gemm_bf16_splitk: k_splits %d not in [1, 64]", k_splits);
+  if (k_splits > 1) {
+    if (!scratch || reinterpret_cast<uintptr_t>(scratch) % 16 != 0)
+      return fail(GEMM_B200_ERR_INVALID_ARG, "gemm_bf16_splitk: scratch must be a 16-byte aligned device buffer");
+    if (M > 0 && N > 0 && scratch_bytes < gemm_b200_gemm_bf16_splitk_scratch_bytes(M, N, k_splits))
+      return fail(GEMM_B200_ERR_INVALID_ARG, "gemm_bf16_splitk: scratch holds %zu bytes, %zu needed", scratch_bytes,
+                  gemm_b200_gemm_bf16_splitk_scratch_bytes(M, N, k_splits));
+    if (N % 4 != 0) return fail(GEMM_B200_ERR_ALIGNMENT, "gemm_bf16_splitk: N must be a multiple of 4");
+  }
+  return tc::bf16_entry(A, B, C, 1, M, N, K, lda, ldb, ldc, 0, 0, 0, b_layout, out_dtype, -1, stream, k_splits,
+                        static_cast<float*>(scratch));
 }
 
 extern "C" int gemm_b200_gemm_bf16_batched(const void* A, const void* B, void* C, int64_t batch, int64_t M, int64_t N,
@@ -540,47 +670,6 @@ static int launch_mxfp8_splitk(const MxArgs& a, int out_dtype) {
   return GEMM_B200_OK;
 }
 
-// Number of K splits for a problem whose tiles alone do not fill the GPU: the split count that
-// wastes the fewest CTA slots in the last round, mildly preferring fewer splits (each split
-// writes and re-reads an M x N FP32 slice).  1 = do not split.
-static int auto_splits(int64_t M, int64_t N, int64_t K, int sms) {
-  const int64_t tiles = ceil_div64(M, kBlockM) * ceil_div64(N, kBlockN);
-  const int64_t num_kb = ceil_div64(K, kMxBlockK);
-  // Splitting pays for a second (reduce) launch and an M x N FP32 round trip per split: measured on
-  // B200, 112 tiles on 148 SMs run as fast unsplit (16 x 8192 x 28672: 62 us either way; 64 rows:
-  // 62 us unsplit, 70 us split), 32 tiles do not (128 x 8192 x 8192: 42 -> 34 us; 16 x 16384 x 4096
-  // with 16 tiles: 64 -> 28 us).  Split only when the tiles leave more than a third of the SMs idle.
-  if (3 * tiles >= 2 * (int64_t)sms || num_kb < 8) return 1;
-  int best = 1;
-  double best_score = (double)tiles / (double)(ceil_div64(tiles, sms) * sms);
-  for (int s = 2; s <= 16 && num_kb / s >= 4; ++s) {
-    const int64_t kb_per = ceil_div64(num_kb, s);
-    if (ceil_div64(num_kb, kb_per) != s) continue;
-    const int64_t units = tiles * s;
-    const double score = (double)units / (double)(ceil_div64(units, sms) * sms) - 0.01 * s;
-    if (score > best_score + 1e-9) { best_score = score; best = s; }
-  }
-  return best;
-}
-
-// library-owned scratch for the automatic split-K path, one buffer per device, grown on demand
-static std::mutex g_scratch_mu;
-static void* g_scratch[64] = {nullptr};
-static size_t g_scratch_bytes[64] = {0};
-static int cached_scratch(int dev, size_t bytes, float** out) {
-  std::lock_guard<std::mutex> lk(g_scratch_mu);
-  const int slot = dev & 63;
-  if (g_scratch_bytes[slot] < bytes) {
-    if (g_scratch[slot]) GEMM_B200_CUDA_TRY(cudaFree(g_scratch[slot]));
-    g_scratch[slot] = nullptr;
-    g_scratch_bytes[slot] = 0;
-    GEMM_B200_CUDA_TRY(cudaMalloc(&g_scratch[slot], bytes));
-    g_scratch_bytes[slot] = bytes;
-  }
-  *out = static_cast<float*>(g_scratch[slot]);
-  return GEMM_B200_OK;
-}
-
 struct MxConfigEntry {
   const char* name;
   int (*launch[2])(const MxArgs&);   // [out_dtype]
@@ -685,12 +774,14 @@ extern "C" int gemm_b200_gemm_mxfp8_cfg(const void* Aq, const void* SFA, const v
       // skinny: single-CTA tiles, and K splits when the column tiles alone leave SMs idle
       const int splits = tc::auto_splits(M, N, K, di.sms);
       if (splits > 1) {
-        if (int rc = tc::cached_scratch(di.dev, (size_t)splits * M * N * sizeof(float), &args.scratch)) return rc;
-        args.k_splits = splits;
-        if (log_enabled())
-          fprintf(stderr, "[gemm_b200] gemm_mxfp8 %lldx%lldx%lld -> %s, %d K splits\n", (long long)M, (long long)K,
-                  (long long)N, tc::kMxConfigs[tc::kSkinnyMxConfig].name, splits);
-        return tc::launch_mxfp8_splitk<tc::Mx_1cta>(args, out_dtype);
+        if (int rc = tc::cached_scratch(di.dev, (size_t)splits * M * N * sizeof(float), &args.scratch, st)) return rc;
+        if (args.scratch) {
+          args.k_splits = splits;
+          if (log_enabled())
+            fprintf(stderr, "[gemm_b200] gemm_mxfp8 %lldx%lldx%lld -> %s, %d K splits\n", (long long)M, (long long)K,
+                    (long long)N, tc::kMxConfigs[tc::kSkinnyMxConfig].name, splits);
+          return tc::launch_mxfp8_splitk<tc::Mx_1cta>(args, out_dtype);
+        }
       }
       config = (M <= tc::Mx_1cta_a32::A_ROWS) ? tc::kNarrowMxConfig : tc::kSkinnyMxConfig;
     } else {

@@ -91,6 +91,23 @@ int gemm_b200_gemm_bf16_cfg(const void* A, const void* B, void* C,
 int gemm_b200_gemm_bf16_num_configs(void);
 const char* gemm_b200_gemm_bf16_config_name(int config);
 
+/* Split-K form for problems with few output tiles and a long K (e.g. 256 x 256 x 65536): every
+ * tile is cut into `k_splits` ranges of K whose FP32 partial sums go to `scratch`
+ * ([k_splits][M][N] floats, device memory, 16-byte aligned, at least
+ * gemm_b200_gemm_bf16_splitk_scratch_bytes() bytes) and are then summed in ascending split order
+ * into C by a second kernel.  k_splits == 1 runs the plain kernel and never splits.
+ * gemm_b200_gemm_bf16() takes the split path by itself, on a library-owned scratch buffer, with
+ * the count of gemm_b200_gemm_bf16_auto_splits() (1 = it does not split; it also stays unsplit
+ * when the buffer would have to grow during stream capture).  N % 4 == 0.  The reference always
+ * walks K inside one thread (naive/naive_1.cu:9-12); it has no counterpart. */
+int gemm_b200_gemm_bf16_splitk(const void* A, const void* B, void* C,
+                               int64_t M, int64_t N, int64_t K,
+                               int64_t lda, int64_t ldb, int64_t ldc,
+                               int b_layout, int out_dtype, int k_splits,
+                               void* scratch, size_t scratch_bytes, void* stream);
+size_t gemm_b200_gemm_bf16_splitk_scratch_bytes(int64_t M, int64_t N, int k_splits);
+int gemm_b200_gemm_bf16_auto_splits(int64_t M, int64_t N, int64_t K);
+
 /* Strided-batched form: `batch` independent problems of one shape in one launch,
  *   C_i[M,N] = A_i[M,K] @ B_i,   X_i = X + i * stride_x (strides in elements).
  * The reference multiplies one pair of matrices per call (naive/naive.cpp:6-22);

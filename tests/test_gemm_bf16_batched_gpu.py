@@ -1,7 +1,7 @@
 """Strided-batched BF16 GEMM through the C-ABI (gemm_b200_gemm_bf16_batched).
 
 The reference multiplies one pair of matrices per call (naive/naive.cpp:6-22); the batched entry
-must equal that call made once per problem: checked bit-for-bit against the single-problem entry
+must equal that call made once per problem: checked bit-for-bit against the (unsplit) single-problem entry
 point and, within the BF16 tolerance, against the FP32 oracle."""
 import pytest
 import torch
@@ -29,7 +29,7 @@ def test_batched_equals_one_call_per_problem(ops, oracle, batch, M, K, N, out_dt
     ops.check_status()
     assert out.data_ptr() == C.data_ptr()
     for i in range(batch):
-        single = ops.gemm_bf16(Ad[i], Bd[i], out_dtype=out_dtype)
+        single = ops.gemm_bf16(Ad[i], Bd[i], out_dtype=out_dtype, k_splits=1)
         assert torch.equal(C[i], single), f"problem {i}"
         want = oracle.bf16_matmul_oracle(A[i], B[i])
         torch.testing.assert_close(C[i].float().cpu(), want, rtol=RTOL, atol=ATOL)
@@ -44,9 +44,9 @@ def test_shared_b_and_transposed_b(ops, oracle):
     C = ops.gemm_bf16_batched(Ad, W, out_dtype=torch.float32)
     ops.check_status()
     for i in range(batch):
-        assert torch.equal(C[i], ops.gemm_bf16(Ad[i], W, out_dtype=torch.float32))
+        assert torch.equal(C[i], ops.gemm_bf16(Ad[i], W, out_dtype=torch.float32, k_splits=1))
     # the same result as one tall GEMM over the stacked rows
-    tall = ops.gemm_bf16(Ad.reshape(batch * M, K), W, out_dtype=torch.float32)
+    tall = ops.gemm_bf16(Ad.reshape(batch * M, K), W, out_dtype=torch.float32, k_splits=1)
     assert torch.equal(C.reshape(batch * M, N), tall)
     # B given per problem as its transpose [batch, N, K]
     Bt = B.transpose(1, 2).contiguous().cuda()

@@ -106,3 +106,46 @@ def test_alignment_errors(ops):
     with pytest.raises(L.GemmB200Error) as e:
         ops.gemm_bf16(A, B)
     assert e.value.code == L.ERR_ALIGNMENT
+
+
+@pytest.mark.parametrize("M,K,N,splits", [(256, 8192, 256, 8), (128, 4096, 264, 3), (16, 2048, 512, 5), (300, 1000, 520, 4),
+                                          (1, 512, 8, 2), (256, 65536, 256, 64)])
+@pytest.mark.parametrize("b_is_nk", [False, True])
+def test_splitk_matches_the_oracle(ops, oracle, M, K, N, splits, b_is_nk):
+    """K cut into ranges whose FP32 partial sums are added in split order: within the FP32 bound of
+    the unsplit kernel, and the bf16 output is the rounding of the FP32 one."""
+    A, B = oracle.gen_randn_bf16(M, K, N, seed=splits)
+    want = oracle.bf16_matmul_oracle(A, B)
+    Bdev = B.t().contiguous().cuda() if b_is_nk else B.cuda()
+    got32 = ops.gemm_bf16(A.cuda(), Bdev, b_is_nk=b_is_nk, out_dtype=torch.float32, k_splits=splits)
+    ops.check_status()
+    assert oracle.rel_frobenius(got32.cpu(), want) < 1e-5
+    got16 = ops.gemm_bf16(A.cuda(), Bdev, b_is_nk=b_is_nk, k_splits=splits)
+    ops.check_status()
+    assert torch.equal(got16, got32.bfloat16())
+
+
+def test_few_tiles_long_k_takes_the_split_path_by_itself(ops, oracle):
+    import gemm_b200._lib as L
+    M, K, N = 256, 32768, 512
+    assert L.lib.gemm_b200_gemm_bf16_auto_splits(M, N, K) > 1
+    assert L.lib.gemm_b200_gemm_bf16_auto_splits(8192, 8192, 8192) == 1
+    A, B = oracle.gen_randn_bf16(M, K, N, seed=11)
+    want = oracle.bf16_matmul_oracle(A, B)
+    got = ops.gemm_bf16(A.cuda(), B.cuda(), out_dtype=torch.float32)          # library decides
+    unsplit = ops.gemm_bf16(A.cuda(), B.cuda(), out_dtype=torch.float32, k_splits=1)
+    ops.check_status()
+    # one FP32 accumulator over 32768 products drifts further than 16 shorter partial sums
+    assert oracle.rel_frobenius(got.cpu(), want) < 1e-5
+    assert oracle.rel_frobenius(unsplit.cpu(), want) < 1e-4
+
+
+def test_splitk_rejects_a_small_scratch(ops):
+    import gemm_b200._lib as L
+    A = torch.zeros(128, 1024, device="cuda", dtype=torch.bfloat16)
+    B = torch.zeros(1024, 256, device="cuda", dtype=torch.bfloat16)
+    C = torch.zeros(128, 256, device="cuda", dtype=torch.bfloat16)
+    scratch = torch.zeros(1024, device="cuda", dtype=torch.uint8)
+    rc = L.lib.gemm_b200_gemm_bf16_splitk(A.data_ptr(), B.data_ptr(), C.data_ptr(), 128, 256, 1024, 1024, 256, 256,
+                                          L.B_ROW_MAJOR_KN, L.OUT_BF16, 4, scratch.data_ptr(), 1024, 0)
+    assert rc == L.ERR_INVALID_ARG and b"scratch" in L.lib.gemm_b200_last_error()
