@@ -166,6 +166,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   tc_fence_after_sync();
   uint32_t tmem_base;
   asm volatile("ld.shared.u32 %0, [%1];" : "=r"(tmem_base) : "r"(tmem_slot) : "memory");
+  // split-K: lets the reduce kernel behind this one be scheduled early; it waits for this grid
+  if (shape.k_splits > 1) pdl_launch_dependents();
 
   bool failed = false;
 

@@ -118,6 +118,13 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int rol
   }
 }
 
+// Programmatic dependent launch: a kernel launched behind this one with the programmatic-
+// serialization attribute may be scheduled once every CTA here has called pdl_launch_dependents()
+// (or exited); it must call pdl_wait() before touching anything this grid wrote, which returns
+// when this grid has completed and its writes are visible.  Both are no-ops otherwise.
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
 // Whole-warp form: every lane waits, and the warp goes on only if every lane saw the phase
 // complete.  Keeps the producer and MMA-issuing warps convergent, so the values they compute
 // (addresses, descriptors, coordinates) are warp-uniform and only the issuing instruction itself

@@ -256,6 +256,30 @@ static int cached_scratch(int dev, size_t bytes, float** out, cudaStream_t strea
   return GEMM_B200_OK;
 }
 
+// The split-K reduce pass, launched with programmatic stream serialization so that its launch
+// overlaps the tail of the GEMM that feeds it (the kernel itself waits for that grid).
+static int launch_splitk_reduce(const float* scratch, int64_t M, int64_t N, int splits, void* C, int64_t ldc, int out_dtype,
+                                cudaStream_t stream) {
+  const int64_t threads = M * (N / 4);
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)ceil_div64(threads, 256));
+  cfg.blockDim = dim3(256);
+  cfg.dynamicSmemBytes = 0;
+  cfg.stream = stream;
+  cudaLaunchAttribute attrs[1];
+  attrs[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attrs[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attrs;
+  cfg.numAttrs = 1;
+  const int64_t split_stride = M * N;
+  if (out_dtype == GEMM_B200_OUT_F32)
+    GEMM_B200_CUDA_TRY(cudaLaunchKernelEx(&cfg, splitk_reduce_kernel<true>, scratch, split_stride, N, splits, C, ldc, (int)M, (int)N));
+  else
+    GEMM_B200_CUDA_TRY(cudaLaunchKernelEx(&cfg, splitk_reduce_kernel<false>, scratch, split_stride, N, splits, C, ldc, (int)M, (int)N));
+  launch_counter().fetch_add(1, std::memory_order_relaxed);
+  return GEMM_B200_OK;
+}
+
 struct Bf16Args {
   const void *A, *B;
   void* C;
@@ -400,15 +424,7 @@ static int launch_bf16_splitk(const Bf16Args& a, int b_layout, int out_dtype, in
   const int num_kb = (int)ceil_div64(a.K, kBlockK);
   const int kb_per = (int)ceil_div64(num_kb, k_splits);
   const int splits = (int)ceil_div64(num_kb, kb_per);
-  const int64_t threads = a.M * (a.N / 4);
-  const unsigned blocks = (unsigned)ceil_div64(threads, 256);
-  if (out_dtype == GEMM_B200_OUT_F32)
-    splitk_reduce_kernel<true><<<blocks, 256, 0, a.stream>>>(scratch, a.M * a.N, a.N, splits, a.C, a.ldc, (int)a.M, (int)a.N);
-  else
-    splitk_reduce_kernel<false><<<blocks, 256, 0, a.stream>>>(scratch, a.M * a.N, a.N, splits, a.C, a.ldc, (int)a.M, (int)a.N);
-  launch_counter().fetch_add(1, std::memory_order_relaxed);
-  GEMM_B200_CUDA_TRY(cudaGetLastError());
-  return GEMM_B200_OK;
+  return launch_splitk_reduce(scratch, a.M, a.N, splits, a.C, a.ldc, out_dtype, a.stream);
 }
 
 static int bf16_auto_splits(int64_t M, int64_t N, int64_t K, int sms) {
@@ -659,15 +675,7 @@ static int launch_mxfp8_splitk(const MxArgs& a, int out_dtype) {
   const int num_kb = (int)ceil_div64(a.K, kMxBlockK);
   const int kb_per = (int)ceil_div64(num_kb, a.k_splits);
   const int splits = (int)ceil_div64(num_kb, kb_per);
-  const int64_t threads = a.M * (a.N / 4);
-  const unsigned blocks = (unsigned)ceil_div64(threads, 256);
-  if (out_dtype == GEMM_B200_OUT_F32)
-    splitk_reduce_kernel<true><<<blocks, 256, 0, a.stream>>>(a.scratch, a.M * a.N, a.N, splits, a.C, a.ldc, (int)a.M, (int)a.N);
-  else
-    splitk_reduce_kernel<false><<<blocks, 256, 0, a.stream>>>(a.scratch, a.M * a.N, a.N, splits, a.C, a.ldc, (int)a.M, (int)a.N);
-  launch_counter().fetch_add(1, std::memory_order_relaxed);
-  GEMM_B200_CUDA_TRY(cudaGetLastError());
-  return GEMM_B200_OK;
+  return launch_splitk_reduce(a.scratch, a.M, a.N, splits, a.C, a.ldc, out_dtype, a.stream);
 }
 
 struct MxConfigEntry {
