@@ -278,14 +278,15 @@ def run_reference_arm(args) -> int:
     import torch
     from oracle import oracle as O
     M, K, N = WORKLOADS[args.workload]
+    is_mx = args.workload.startswith("mxfp8")      # same host computation: FP32 matmul of the operands
     g = torch.Generator().manual_seed(0)
     B = torch.randn(K, N, generator=g).bfloat16()
     rows = 256
     A = torch.randn(rows, K, generator=g).bfloat16()
     O.bf16_matmul_oracle(A, B)
     t0 = time.perf_counter(); O.bf16_matmul_oracle(A, B); dt = time.perf_counter() - t0
-    # each step ~ 60 s / (steps + warmup) of CPU work
-    per_step = 60.0 / max(1, args.steps + args.warmup)
+    # each step ~ 60 s / (steps + warmup) of CPU work (GEMM_B200_REF_BUDGET_S overrides the 60 s)
+    per_step = float(os.environ.get("GEMM_B200_REF_BUDGET_S", "60")) / max(1, args.steps + args.warmup)
     rows = int(max(256, min(M, (per_step / max(dt, 1e-4)) * 256 // 256 * 256)))
     A = torch.randn(rows, K, generator=g).bfloat16()
     for _ in range(args.warmup):
