@@ -4,6 +4,7 @@ call them as opaque ops:
     import gemm_b200.torch_ops
     C = torch.ops.gemm_b200.sgemm_f32(A, B)
     C = torch.ops.gemm_b200.gemm_bf16(A, B, b_is_nk=False, out_f32=False)
+    C = torch.ops.gemm_b200.gemm_bf16_batched(A3, B3)         # [batch, M, K] x [batch, K, N] (or a shared 2-D B)
 
 The allocating forms are registered (out-parameter forms alias their argument, which the
 reference's wrappers do by design, naive/naive.cpp:17-21, and which functional graphs cannot
@@ -35,3 +36,15 @@ def gemm_bf16(A: torch.Tensor, B: torch.Tensor, b_is_nk: bool = False, out_f32: 
 def _(A, B, b_is_nk=False, out_f32=False):
     n = B.shape[0] if b_is_nk else B.shape[1]
     return A.new_empty((A.shape[0], n), dtype=torch.float32 if out_f32 else torch.bfloat16)
+
+
+@torch.library.custom_op("gemm_b200::gemm_bf16_batched", mutates_args=())
+def gemm_bf16_batched(A: torch.Tensor, B: torch.Tensor, b_is_nk: bool = False, out_f32: bool = False) -> torch.Tensor:
+    return ops.gemm_bf16_batched(A, B, b_is_nk=b_is_nk, out_dtype=torch.float32 if out_f32 else torch.bfloat16)
+
+
+@gemm_bf16_batched.register_fake
+def _(A, B, b_is_nk=False, out_f32=False):
+    torch._check(A.dim() == 3 and B.dim() in (2, 3))
+    n = B.shape[-2] if b_is_nk else B.shape[-1]
+    return A.new_empty((A.shape[0], A.shape[1], n), dtype=torch.float32 if out_f32 else torch.bfloat16)

@@ -16,6 +16,9 @@ def test_custom_ops_match_direct_calls(ops, oracle):
     assert torch.equal(c1, ops.gemm_bf16(Ab.cuda(), Bb.cuda()))
     c2 = torch.ops.gemm_b200.gemm_bf16(Ab.cuda(), Bb.t().contiguous().cuda(), True, True)
     torch.testing.assert_close(c2.cpu(), oracle.bf16_matmul_oracle(Ab, Bb), rtol=2e-2, atol=2e-2)
+    A3 = torch.stack([Ab, Ab * 0.5, -Ab]).cuda()
+    c3 = torch.ops.gemm_b200.gemm_bf16_batched(A3, Bb.cuda())
+    assert torch.equal(c3, ops.gemm_bf16_batched(A3, Bb.cuda())) and c3.shape == (3, 256, 264)
 
 
 def test_fake_tensor_shapes():
@@ -27,3 +30,5 @@ def test_fake_tensor_shapes():
         Ab = torch.empty(64, 32, device="cuda", dtype=torch.bfloat16); Bt = torch.empty(48, 32, device="cuda", dtype=torch.bfloat16)
         out = torch.ops.gemm_b200.gemm_bf16(Ab, Bt, True, True)
         assert out.shape == (64, 48) and out.dtype == torch.float32
+        A3 = torch.empty(5, 64, 32, device="cuda", dtype=torch.bfloat16)
+        assert torch.ops.gemm_b200.gemm_bf16_batched(A3, Bt, True, False).shape == (5, 64, 48)
