@@ -186,6 +186,28 @@ def time_alone(fn, reps: int = 10, warmup: int = 3) -> float:
     return ts[len(ts) // 2]
 
 
+def time_interleaved(fns, reps: int = 7, warmup: int = 2) -> list:
+    """Median device time (s) of each callable, launched in turn (a, b, c, a, b, c, ...), L2 flushed
+    before every launch."""
+    import torch
+    flush = torch.empty(2 * L2_BYTES, dtype=torch.uint8, device="cuda")
+    for _ in range(warmup):
+        for fn in fns:
+            fn()
+    ts = [[] for _ in fns]
+    for _ in range(reps):
+        for i, fn in enumerate(fns):
+            flush.zero_()
+            e0 = torch.cuda.Event(enable_timing=True)
+            e1 = torch.cuda.Event(enable_timing=True)
+            e0.record()
+            fn()
+            e1.record()
+            torch.cuda.synchronize()
+            ts[i].append(e0.elapsed_time(e1) / 1e3)
+    return [sorted(t)[len(t) // 2] for t in ts]
+
+
 def per_dtype_table(peaks: dict) -> dict:
     """The other benchmark configurations at N = 1, each kernel timed alone (median, L2 flushed)."""
     import torch
@@ -241,10 +263,13 @@ def per_dtype_table(peaks: dict) -> dict:
                 out[f"mxfp8_{M}x{K}x{N}"]["frac_of_measured_hbm_cuda_graph"] = round(bytes_ / t_g / 1e9 / float(peaks.get("hbm_gbs", 6650.0)), 4)
                 del graph
             if M >= 1024:
-                # the same GEMM with the quantising epilogue vs GEMM (bf16 out) + separate quantise pass
-                t_f = time_alone(lambda: ops.gemm_mxfp8_quant_out(Aq, Bq), reps=5)
-                t_q = time_alone(lambda: ops.quantize_mxfp8(C), reps=5)
-                out[f"mxfp8_{M}x{K}x{N}_quant_out"] = {"fused_ms": round(t_f * 1e3, 3), "gemm_plus_quantise_ms": round((t + t_q) * 1e3, 3),
+                # the same GEMM with the quantising epilogue vs GEMM (bf16 out) + separate quantise pass,
+                # timed alternately: on a power-capped board the clock drifts with what ran just before
+                t_f, t_p, t_q = time_interleaved([lambda: ops.gemm_mxfp8_quant_out(Aq, Bq),
+                                                  lambda: ops.gemm_mxfp8(Aq, Bq, C),
+                                                  lambda: ops.quantize_mxfp8(C)], reps=7)
+                out[f"mxfp8_{M}x{K}x{N}_quant_out"] = {"fused_ms": round(t_f * 1e3, 3), "gemm_ms": round(t_p * 1e3, 3),
+                                                       "gemm_plus_quantise_ms": round((t_p + t_q) * 1e3, 3),
                                                        "tflops_fused": round(2 * M * N * K / t_f / 1e12, 1)}
             del Aq, Bq, C
     return out
