@@ -286,13 +286,18 @@ def cpu_baseline(M: int, K: int, N: int, budget_s: float = 15.0) -> dict:
     A = torch.randn(rows, K, generator=g).bfloat16()
     O.bf16_matmul_oracle(A, B)                       # warm-up
     t0 = time.perf_counter(); O.bf16_matmul_oracle(A, B); dt = time.perf_counter() - t0
-    rows = int(min(M, max(256, (budget_s / max(dt, 1e-4)) * 256 // 256 * 256)))
-    rows = min(rows, 16384)
+    # about budget_s of CPU work in all: three passes over a row slice (best pass reported), the slice
+    # capped at 65536 rows so the FP32 copies of A and C stay within a few GB of host memory
+    rows = int(min(M, max(256, (budget_s / 3 / max(dt, 1e-4)) * 256 // 256 * 256)))
+    rows = min(rows, 65536)
     A = torch.randn(rows, K, generator=g).bfloat16()
-    t0 = time.perf_counter(); O.bf16_matmul_oracle(A, B); dt = time.perf_counter() - t0
-    return {"value": round(2 * rows * N * K / dt / 1e12, 4), "unit": "TFLOP/s", "cores": O.cpu_threads(),
+    best = None
+    for _ in range(3):
+        t0 = time.perf_counter(); O.bf16_matmul_oracle(A, B); dt = time.perf_counter() - t0
+        best = dt if best is None else min(best, dt)
+    return {"value": round(2 * rows * N * K / best / 1e12, 4), "unit": "TFLOP/s", "cores": O.cpu_threads(),
             "kind": "port", "sample": f"torch.matmul (FP32 of the bf16 operands) on the first {rows} of {M} rows, "
-                                      f"{dt:.2f} s, os.cpu_count()={os.cpu_count()}"}
+                                      f"best of 3 passes of {best:.2f} s, os.cpu_count()={os.cpu_count()}"}
 
 
 def run_reference_arm(args) -> int:
