@@ -44,16 +44,19 @@ constexpr int kMxSfbCol = 260;     // TMEM columns [260, 268): scales of B (256 
 //      A_ROWS are loaded; consecutive stages sit A_ROWS rows apart, so the rows above a stage's
 //      own are another stage's bytes or stale ones.  They only reach accumulator rows >= M, which
 //      are never stored, and the shared memory saved buys more stages of B in flight.
-template <int CG_, int STAGES_, bool COMMIT_MASK_, int EPI_ = 0, int A_ROWS_ = kBlockM>
+// BN:  columns of C per tile (per CTA for CG = 1, per CTA pair for CG = 2): 256, or 128 for problems
+//      whose 256-column tiles would not fill one round of the persistent grid.
+template <int CG_, int STAGES_, bool COMMIT_MASK_, int EPI_ = 0, int A_ROWS_ = kBlockM, int BN_ = kBlockN>
 struct MxCfg {
-  static constexpr int CG = CG_, STAGES = STAGES_, EPI = EPI_, A_ROWS = A_ROWS_;
+  static constexpr int CG = CG_, STAGES = STAGES_, EPI = EPI_, A_ROWS = A_ROWS_, BN = BN_;
   static constexpr bool COMMIT_MASK = COMMIT_MASK_;
-  static constexpr int BN_CTA = kBlockN / CG;
+  static constexpr int NCH = BN / 64;                       // 32-column accumulator chunks per epilogue warp
+  static constexpr int BN_CTA = BN / CG;
   static constexpr int A_BYTES = A_ROWS * kMxBlockK;        // bytes a stage loads and the stage pitch (16 KB for 128 rows)
   static constexpr int A_RING_BYTES = STAGES * A_BYTES + (kBlockM - A_ROWS) * kMxBlockK;
   static constexpr int B_BYTES = BN_CTA * kMxBlockK;        // 32 KB / 16 KB
   static constexpr int SFA_BYTES = 512;
-  static constexpr int SFB_BYTES = 1024;                    // 256 columns of C
+  static constexpr int SFB_BYTES = (BN / 128) * 512;        // one scale chunk per 128 columns of C
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES + SFA_BYTES + SFB_BYTES;
   static constexpr int EPI_WARP_BUF = 32 * 128;             // 32 rows x 128 bytes per epilogue warp
   static constexpr int EPI_BYTES = EPI == 1 ? 8 * EPI_WARP_BUF : 0;
@@ -61,6 +64,7 @@ struct MxCfg {
   static constexpr int SMEM_BYTES = 1024 + A_RING_BYTES + STAGES * (B_BYTES + SFA_BYTES + SFB_BYTES) + EPI_BYTES + BAR_BYTES;
   static_assert(A_ROWS % 8 == 0 && A_ROWS >= 8 && A_ROWS <= kBlockM, "A rows per stage: whole 8-row swizzle atoms");
   static_assert(A_ROWS == kBlockM || CG == 1, "narrow A stages are a single-CTA variant");
+  static_assert(BN == 256 || BN == 128, "tile width");
   static_assert(SMEM_BYTES <= 232448, "shared memory budget");
 };
 
@@ -150,7 +154,7 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
       tile_coord(t, shape, tm, tn);
       const int mblk = tm * CG + (int)cta_rank;            // 128-row block of A / C
       const int m0 = mblk * kBlockM;
-      const int n0 = tn * kBlockN + (int)cta_rank * Cfg::BN_CTA;
+      const int n0 = tn * Cfg::BN + (int)cta_rank * Cfg::BN_CTA;
       for (int kb = kb0; kb < kb1; ++kb, ++it) {
         const int s = it % STAGES;
         const uint32_t ph = (it / STAGES) & 1u;
@@ -164,7 +168,7 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
             tma_load_2d(a_dst, &tmA, kb * kMxBlockK, m0, full_bar(s));
             tma_load_2d(b_dst, &tmB, kb * kMxBlockK, n0, full_bar(s));
             tma_load_2d(sfa_dst, &tmSFA, kb * 128, mblk, full_bar(s));
-            tma_load_2d(sfb_dst, &tmSFB, kb * 128, tn * 2, full_bar(s));
+            tma_load_2d(sfb_dst, &tmSFB, kb * 128, tn * (Cfg::BN / 128), full_bar(s));
           }
         } else {
           const uint32_t lead_full = map_to_cta(full_bar(s), 0);
@@ -173,7 +177,7 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
             tma_load_2d_pair(a_dst, &tmA, kb * kMxBlockK, m0, lead_full);
             tma_load_2d_pair(b_dst, &tmB, kb * kMxBlockK, n0, lead_full);
             tma_load_2d_pair(sfa_dst, &tmSFA, kb * 128, mblk, lead_full);
-            tma_load_2d_pair(sfb_dst, &tmSFB, kb * 128, tn * 2, lead_full);
+            tma_load_2d_pair(sfb_dst, &tmSFB, kb * 128, tn * (Cfg::BN / 128), lead_full);
           }
         }
         __syncwarp();
@@ -218,12 +222,13 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
             // tcgen05.cp and tcgen05.mma of one thread execute in issue order: these copies land
             // after the previous block's MMAs have read the scale columns and before the next ones do
             tmem_cp_32x128b_warpx4<CG>(sfa_tmem, smem_desc(sf_hi, sfa_addr));
-            tmem_cp_32x128b_warpx4<CG>(sfb_tmem, smem_desc(sf_hi, sfb_addr));
-            tmem_cp_32x128b_warpx4<CG>(sfb_tmem + 4, smem_desc(sf_hi, sfb_addr + 512));
+#pragma unroll
+            for (int c = 0; c < Cfg::BN / 128; ++c)
+              tmem_cp_32x128b_warpx4<CG>(sfb_tmem + 4 * c, smem_desc(sf_hi, sfb_addr + 512 * c));
 #pragma unroll
             for (int k = 0; k < kMxBlockK / kMxUmmaK; ++k) {
               // byte k of every 32-bit scale column belongs to this 32-wide K slice
-              const uint32_t idesc = make_idesc_mxf8(kBlockM * CG, kBlockN, k, k);
+              const uint32_t idesc = make_idesc_mxf8(kBlockM * CG, Cfg::BN, k, k);
               mma_mxf8<CG>(d_tmem, smem_desc(ab_hi, a_addr + k * kMxUmmaK), smem_desc(ab_hi, b_addr + k * kMxUmmaK), idesc,
                            sfa_tmem + ((uint32_t)k << 30), sfb_tmem + ((uint32_t)k << 30), k != 0 ? 1u : first);
             }
@@ -239,21 +244,22 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
   } else {
     // ------------------------------------------------------------------ epilogue warps 2..9
     const int quad = warp & 3;             // TMEM lanes [32 quad, 32 quad + 32)
-    const int half = (warp - 2) >> 2;      // columns [128 half, 128 half + 128)
-    const uint32_t t_addr = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(half * 128);
+    constexpr int NCH = Cfg::NCH;
+    const int half = (warp - 2) >> 2;      // columns [BN/2 half, BN/2 half + BN/2) of the tile
+    const uint32_t t_addr = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(half * (Cfg::BN / 2));
     uint32_t acc_it = 0;
     for (int u = cluster_id; u < num_units && !failed; u += num_clusters, ++acc_it) {
       int t, split, kb0, kb1, tm, tn;
       unit_range(u, t, split, kb0, kb1);
       tile_coord(t, shape, tm, tn);
       const int row = (tm * CG + (int)cta_rank) * kBlockM + quad * 32 + lane;
-      const int col0 = tn * kBlockN + half * 128;
+      const int col0 = tn * Cfg::BN + half * (Cfg::BN / 2);
       const bool ready = mbar_wait(tfull_bar, acc_it & 1u, kRoleEpilogue, 200);
       if (!__all_sync(0xffffffffu, ready)) { failed = true; break; }
       tc_fence_after_sync();
-      uint32_t v[4][32];
+      uint32_t v[NCH][32];
 #pragma unroll
-      for (int c = 0; c < 4; ++c) tmem_ld_32x32b_x32(t_addr + c * 32, v[c]);
+      for (int c = 0; c < NCH; ++c) tmem_ld_32x32b_x32(t_addr + c * 32, v[c]);
       tmem_ld_wait();
       // accumulator is in registers: the next tile's MMAs may overwrite it
       tc_fence_before_sync();
@@ -269,7 +275,7 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
         const uint32_t row_addr = buf + (uint32_t)lane * 128u;
         const uint32_t sw = (uint32_t)(lane & 7);
         const int row0 = (tm * CG + (int)cta_rank) * kBlockM + quad * 32;
-        constexpr int SLABS = OUT_F32 ? 4 : 2;
+        constexpr int SLABS = OUT_F32 ? NCH : NCH / 2;
 #pragma unroll
         for (int sl = 0; sl < SLABS; ++sl) {
           if (lane == 0) tma_store_wait_read<0>();   // the previous slab's store has read the buffer
@@ -303,6 +309,7 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
           }
         }
       } else if constexpr (OUT == 2) {
+        static_assert(Cfg::BN == 256, "the quantising epilogue is written for 256-column tiles");
         // each thread holds 32 consecutive columns of its row per chunk: one microscaling block.
         // Round to bf16 first so the bytes equal "bf16 GEMM output, then quantise".
         const int64_t kchunks = (((int64_t)shape.N / 32) + 3) / 4;       // scale chunks per row block of C
@@ -357,7 +364,7 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
           *reinterpret_cast<uint32_t*>(SFC + mx::scale_offset(kchunks, row, nb0)) = scale_word;   // padding -> 0
       } else if (row < shape.M) {
 #pragma unroll
-        for (int c = 0; c < 4; ++c) {
+        for (int c = 0; c < NCH; ++c) {
           const int col = col0 + c * 32;
           if constexpr (OUT_F32) {
             float* dst = reinterpret_cast<float*>(Cptr) + (int64_t)split * shape.split_stride + (int64_t)row * ldc + col;

@@ -223,3 +223,17 @@ def test_chained_gemms_through_the_quantising_epilogue(ops, oracle):
     qb, sb = oracle.mxfp8_quantize(W2.t().contiguous())
     want = torch.matmul(Hd, oracle.mxfp8_dequantize(qb, sb).t())
     assert oracle.rel_frobenius(Y.cpu(), want) <= REL_TOL
+
+
+@pytest.mark.parametrize("M,K,N", [(256, 2048, 4096), (300, 1024, 1000), (512, 512, 2048)])
+def test_half_round_problems_take_the_128_column_tiles(ops, oracle, M, K, N):
+    """Few 256-column tiles: the library switches to 256 x 128 tiles by itself; same bits as the
+    256-column variant."""
+    A, B = oracle.gen_randn_bf16(M, K, N, seed=M + K)
+    Aq = ops.quantize_mxfp8(A.cuda())
+    Bq = ops.quantize_mxfp8(B.cuda(), transposed_in=True)
+    auto = ops.gemm_mxfp8(Aq, Bq, out_dtype=torch.float32)
+    wide = ops.gemm_mxfp8(Aq, Bq, out_dtype=torch.float32, config=3)
+    ops.check_status()
+    assert torch.equal(auto, wide)
+    _gemm_check(ops, oracle, M, K, N, config=ops.gemm_mxfp8_configs().index("2cta_256x128x128_s7_maskcommit_tmastore"), seed=1)
