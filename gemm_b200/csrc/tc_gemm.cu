@@ -691,6 +691,7 @@ using Mx_2cta_m = MxCfg<2, 6, true>;
 using Mx_2cta_m_tma = MxCfg<2, 5, true, 1>;
 using Mx_1cta_a32 = MxCfg<1, 5, false, 0, 32>;   // M <= 32: 4 KB of A per stage, 5 stages of B in flight
 using Mx_2cta_n128 = MxCfg<2, 7, true, 1, kBlockM, 128>;   // 256 x 128 tiles for one-round problems
+using Mx_1cta_n128 = MxCfg<1, 6, false, 0, kBlockM, 128>;   // 128 x 128 tiles: 32 < M <= 128 with few column tiles
 static const MxConfigEntry kMxConfigs[] = {
     {"1cta_128x256x128_s4", {launch_mxfp8<Mx_1cta, 0>, launch_mxfp8<Mx_1cta, 1>}},
     {"2cta_256x256x128_s6", {launch_mxfp8<Mx_2cta, 0>, launch_mxfp8<Mx_2cta, 1>}},
@@ -698,12 +699,14 @@ static const MxConfigEntry kMxConfigs[] = {
     {"2cta_256x256x128_s5_maskcommit_tmastore", {launch_mxfp8<Mx_2cta_m_tma, 0>, launch_mxfp8<Mx_2cta_m_tma, 1>}},
     {"1cta_32x256x128_s5_narrowA", {launch_mxfp8<Mx_1cta_a32, 0>, launch_mxfp8<Mx_1cta_a32, 1>}},
     {"2cta_256x128x128_s7_maskcommit_tmastore", {launch_mxfp8<Mx_2cta_n128, 0>, launch_mxfp8<Mx_2cta_n128, 1>}},
+    {"1cta_128x128x128_s6", {launch_mxfp8<Mx_1cta_n128, 0>, launch_mxfp8<Mx_1cta_n128, 1>}},
 };
 constexpr int kNumMxConfigs = sizeof(kMxConfigs) / sizeof(kMxConfigs[0]);
 constexpr int kDefaultMxConfig = 3;      // CTA pair, masked commit, TMA-store epilogue
 constexpr int kSkinnyMxConfig = 0;       // M <= 128: single-CTA tiles give more independent column tiles
 constexpr int kNarrowMxConfig = 4;       // M <= 32: the same with 32-row A stages and a deeper B pipeline
 constexpr int kN128MxConfig = 5;         // CTA pair, 256 x 128 tiles: problems of at most half a round of 256-wide tiles
+constexpr int k1ctaN128MxConfig = 6;     // single CTA, 128 x 128 tiles
 
 }  // namespace tc
 }  // namespace gemm_b200
@@ -788,6 +791,16 @@ extern "C" int gemm_b200_gemm_mxfp8_cfg(const void* Aq, const void* SFA, const v
       // skinny: single-CTA tiles, and K splits when the column tiles alone leave SMs idle.  (Taller
       // problems with few tiles were tried on this path too: 256-384 x 8192 x 8192 ran 40-50 us
       // split against 38 us on CTA-pair tiles.)
+      // 33..128 rows and so few 256-column tiles that half the SMs would idle: 128-column tiles in
+      // one launch beat K splits with their reduce pass (128 x 8192 x 8192: 31.6 vs 33.5 us,
+      // 128 x 4096 x 4096: 19.2 vs 23.3 us); below 24 such tiles K splits fill the GPU better
+      const int64_t tiles128 = ceil_div64(N, 128);
+      if (M > 32 && tiles128 >= 24 && tiles128 <= (int64_t)di.sms) {
+        if (log_enabled())
+          fprintf(stderr, "[gemm_b200] gemm_mxfp8 %lldx%lldx%lld -> %s\n", (long long)M, (long long)K, (long long)N,
+                  tc::kMxConfigs[tc::k1ctaN128MxConfig].name);
+        return tc::kMxConfigs[tc::k1ctaN128MxConfig].launch[out_dtype](args);
+      }
       const int splits = (N % 4 == 0) ? tc::auto_splits(M, N, K, di.sms) : 1;
       if (splits > 1) {
         if (int rc = tc::cached_scratch(di.dev, (size_t)splits * M * N * sizeof(float), &args.scratch, st)) return rc;
