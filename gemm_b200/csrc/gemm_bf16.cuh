@@ -43,16 +43,19 @@ constexpr int kTmemCols = 512;
 //           tile fetched from L2 feeds twice the math, i.e. 25 % fewer operand bytes per flop
 //           (less L2 / fabric power on a power-capped board) at the price of an epilogue that
 //           is not overlapped; 8 epilogue warps keep that short.
-template <int CG_, int STAGES_, int EPI_, bool COMMIT_MASK_, int NT_ = 1, int EPI_BUFS_ = (NT_ == 1 ? 2 : 1)>
+// BN: columns of C per MMA / accumulator (256, or 128 for problems whose 256-column tiles would
+//     leave most of the SMs without work).
+template <int CG_, int STAGES_, int EPI_, bool COMMIT_MASK_, int NT_ = 1, int EPI_BUFS_ = (NT_ == 1 ? 2 : 1),
+          int BN_ = kBlockN>
 struct Bf16Cfg {
-  static constexpr int CG = CG_, STAGES = STAGES_, EPI = EPI_, NT = NT_;
+  static constexpr int CG = CG_, STAGES = STAGES_, EPI = EPI_, NT = NT_, BN = BN_;
   static constexpr bool COMMIT_MASK = COMMIT_MASK_;
   static constexpr int ACC_STAGES = (NT == 1) ? 2 : 1;
   static constexpr int EPI_WARPS = 4 * NT;
   static constexpr int THREADS = 64 + 32 * EPI_WARPS;
   static constexpr int EPI_BUFS = EPI_BUFS_;                       // staging buffers per epilogue warp
-  static constexpr int TILE_N = kBlockN * NT;                       // columns of C per work unit
-  static constexpr int BN_CTA = kBlockN / CG;                       // columns of B each CTA loads per column tile
+  static constexpr int TILE_N = BN * NT;                       // columns of C per work unit
+  static constexpr int BN_CTA = BN / CG;                       // columns of B each CTA loads per column tile
   static constexpr int A_BYTES = kBlockM * kBlockK * 2;             // 16 KB
   static constexpr int B_BYTES = BN_CTA * kBlockK * 2;              // 32 KB / 16 KB, per column tile
   static constexpr int STAGE_BYTES = A_BYTES + NT * B_BYTES;
@@ -61,6 +64,7 @@ struct Bf16Cfg {
   static constexpr int BAR_BYTES = (2 * STAGES + 4) * 8 + 16;
   static constexpr int SMEM_BYTES = 1024 + STAGES * STAGE_BYTES + EPI_BYTES + BAR_BYTES;
   static_assert(NT == 1 || NT == 2, "column tiles per unit");
+  static_assert(BN == 256 || (BN == 128 && NT == 1), "tile width");
   static_assert(SMEM_BYTES <= 232448, "shared memory budget");
 };
 
@@ -106,7 +110,7 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                  const __grid_constant__ CUtensorMap tmC, void* __restrict__ Cptr, int64_t ldc,
                  const GemmShape shape) {
-  constexpr int CG = Cfg::CG, STAGES = Cfg::STAGES, NT = Cfg::NT, ACC_STAGES = Cfg::ACC_STAGES;
+  constexpr int CG = Cfg::CG, STAGES = Cfg::STAGES, NT = Cfg::NT, ACC_STAGES = Cfg::ACC_STAGES, BN = Cfg::BN;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   const uint32_t sA0 = smem_base;
@@ -201,7 +205,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
 #pragma unroll
           for (int nt = 0; nt < NT; ++nt) {
             const uint32_t b_dst = sB0 + (s * NT + nt) * Cfg::B_BYTES;
-            const int n0 = (tn * NT + nt) * kBlockN + (int)cta_rank * Cfg::BN_CTA;
+            const int n0 = (tn * NT + nt) * BN + (int)cta_rank * Cfg::BN_CTA;
             if constexpr (B_MN) {
 #pragma unroll
               for (int j = 0; j < Cfg::BN_CTA / 64; ++j) load(b_dst + j * 8192, &tmB, n0 + j * 64, kb * kBlockK, bz, bar);
@@ -219,7 +223,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     // one elected lane issues the tcgen05 instructions.
     if (cta_rank == 0) {
       const bool issuer = elect_one();
-      constexpr uint32_t idesc = make_idesc_bf16(kBlockM * CG, kBlockN, 0, B_MN ? 1 : 0);
+      constexpr uint32_t idesc = make_idesc_bf16(kBlockM * CG, BN, 0, B_MN ? 1 : 0);
       constexpr uint64_t a_hi = make_smem_desc_hi(16, 1024, kLayoutSw128);
       constexpr uint64_t b_hi = B_MN ? make_smem_desc_hi(8192, 1024, kLayoutSw128)
                                      : make_smem_desc_hi(16, 1024, kLayoutSw128);
@@ -241,7 +245,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         const uint32_t acc = acc_it % ACC_STAGES, aph = (acc_it / ACC_STAGES) & 1u;
         if (!mbar_wait_warp(tempty_bar(acc), aph ^ 1u, kRoleMma, 100 + (int)acc)) { failed = true; break; }
         tc_fence_after_sync();
-        const uint32_t d_tmem = tmem_base + acc * NT * kBlockN;   // NT accumulators of 256 columns
+        const uint32_t d_tmem = tmem_base + acc * NT * BN;   // NT accumulators of 256 columns
         for (int kb = kb0; kb < kb1; ++kb, ++it) {
           const int s = it % STAGES;
           const uint32_t ph = (it / STAGES) & 1u;
@@ -255,7 +259,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
 #pragma unroll
               for (int nt = 0; nt < NT; ++nt) {
                 const uint32_t b_addr = sB0 + (s * NT + nt) * Cfg::B_BYTES;
-                mma_f16<CG>(d_tmem + nt * kBlockN, smem_desc(a_hi, a_addr + k * (kUmmaK * 2)),
+                mma_f16<CG>(d_tmem + nt * BN, smem_desc(a_hi, a_addr + k * (kUmmaK * 2)),
                             smem_desc(b_hi, b_addr + k * b_kstep), idesc, k != 0 ? 1u : first);
               }
             }
@@ -281,20 +285,20 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       const int bi = t / tiles_per_matrix;
       tile_coord(t - bi * tiles_per_matrix, shape, tm, tn);
       const int m0 = (tm * CG + (int)cta_rank) * kBlockM + quad * 32;   // first row of this warp
-      const int n0 = (tn * NT + nt_w) * kBlockN;
+      const int n0 = (tn * NT + nt_w) * BN;
       const uint32_t acc = acc_it % ACC_STAGES, aph = (acc_it / ACC_STAGES) & 1u;
       // every lane waits, and the warp moves on only if every lane saw the phase complete: the
       // TMEM loads below are warp-collective and must not run with part of the warp missing
       const bool ready = mbar_wait(tfull_bar(acc), aph, kRoleEpilogue, 200 + (int)acc);
       if (!__all_sync(0xffffffffu, ready)) { failed = true; break; }
       tc_fence_after_sync();
-      const uint32_t t_addr = tmem_base + lane_base + (acc * NT + nt_w) * kBlockN;
+      const uint32_t t_addr = tmem_base + lane_base + (acc * NT + nt_w) * BN;
       bool released = false;   // TMEM already handed back inside the branch below
       const int row = m0 + lane;
 
       if constexpr (Cfg::EPI == 0) {
 #pragma unroll 1
-        for (int c = 0; c < kBlockN / 32; ++c) {
+        for (int c = 0; c < BN / 32; ++c) {
           uint32_t v[32];
           tmem_ld_32x32b_x32(t_addr + c * 32, v);
           tmem_ld_wait();
@@ -328,9 +332,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         // Single-buffered accumulator: the MMA issuer is waiting for this TMEM.  Pull all 256
         // columns into registers as packed bf16 first (128 registers), hand TMEM back, and only
         // then stage and store, so the stores overlap the next tile's main loop.
-        uint32_t packed[kBlockN / 2];
+        uint32_t packed[BN / 2];
 #pragma unroll
-        for (int c = 0; c < kBlockN / 32; ++c) {
+        for (int c = 0; c < BN / 32; ++c) {
           uint32_t v[32];
           tmem_ld_32x32b_x32(t_addr + c * 32, v);
           tmem_ld_wait();
@@ -348,7 +352,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         }
         released = true;
 #pragma unroll
-        for (int c = 0; c < kBlockN / 64; ++c, ++store_it) {
+        for (int c = 0; c < BN / 64; ++c, ++store_it) {
           const uint32_t buf = stage0 + (store_it % Cfg::EPI_BUFS) * Cfg::EPI_WARP_BUF;
           if (lane == 0) tma_store_wait_read<Cfg::EPI_BUFS - 1>();
           __syncwarp();
@@ -371,7 +375,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         // 128-byte-wide column slabs: 64 bf16 or 32 f32 columns per TMA store of 32 rows.
         constexpr int SLAB_COLS = OUT_F32 ? 32 : 64;
 #pragma unroll 1
-        for (int c = 0; c < kBlockN / SLAB_COLS; ++c, ++store_it) {
+        for (int c = 0; c < BN / SLAB_COLS; ++c, ++store_it) {
           const uint32_t buf = stage0 + (store_it % Cfg::EPI_BUFS) * Cfg::EPI_WARP_BUF;
           // the store that last read this buffer was committed EPI_BUFS slabs ago
           if (lane == 0) tma_store_wait_read<Cfg::EPI_BUFS - 1>();

@@ -376,6 +376,8 @@ using Bf16_2cta_tma_m  = Bf16Cfg<2, 6, 1, true>;
 using Bf16_2cta_n512    = Bf16Cfg<2, 4, 1, true, 2>;
 using Bf16_2cta_n512_d  = Bf16Cfg<2, 4, 0, true, 2>;
 using Bf16_2cta_n512_s3 = Bf16Cfg<2, 3, 1, true, 2, 2>;
+using Bf16_2cta_n128    = Bf16Cfg<2, 7, 1, true, 1, 2, 128>;
+using Bf16_1cta_n128    = Bf16Cfg<1, 6, 1, false, 1, 2, 128>;
 
 static const Bf16ConfigEntry kBf16Configs[] = {
     GEMM_B200_BF16_ENTRY("1cta_128x256x64_s4_direct", Bf16_1cta_direct),
@@ -386,11 +388,15 @@ static const Bf16ConfigEntry kBf16Configs[] = {
     GEMM_B200_BF16_ENTRY("2cta_256x512x64_s4_tmastore_maskcommit", Bf16_2cta_n512),
     GEMM_B200_BF16_ENTRY("2cta_256x512x64_s4_direct_maskcommit", Bf16_2cta_n512_d),
     GEMM_B200_BF16_ENTRY("2cta_256x512x64_s3_tmastore2_maskcommit", Bf16_2cta_n512_s3),
+    GEMM_B200_BF16_ENTRY("2cta_256x128x64_s7_tmastore_maskcommit", Bf16_2cta_n128),
+    GEMM_B200_BF16_ENTRY("1cta_128x128x64_s6_tmastore", Bf16_1cta_n128),
 };
 constexpr int kNumBf16Configs = sizeof(kBf16Configs) / sizeof(kBf16Configs[0]);
 constexpr int kBf16Cfg1cta = 1;   // single CTA, 128x256 tiles, TMA store
 constexpr int kBf16Cfg256 = 4;    // CTA pair, 256x256 tiles, double-buffered accumulator
 constexpr int kBf16Cfg512 = 7;    // CTA pair, 256x512 tiles (A shared by two accumulators)
+constexpr int kBf16Cfg2ctaN128 = 8;   // CTA pair, 256x128 tiles: at most half a round of 256-wide tiles
+constexpr int kBf16Cfg1ctaN128 = 9;   // single CTA, 128x128 tiles: one row tile and few column tiles
 
 // 256x512 tiles move 25 % fewer operand bytes per flop and measure ~4 % faster when both tile
 // shapes fill their rounds equally well; with few tiles the coarser grid wastes more of the last
@@ -496,6 +502,19 @@ static int bf16_entry(const void* A, const void* B, void* C, int64_t batch, int6
     return fail(GEMM_B200_ERR_UNSUPPORTED, "gemm_bf16: device has compute capability %d.x, need 10.x (sm_100a)", di.cc_major);
   Bf16Args args{A, B, C, M, N, K, lda, ldb, ldc, st, batch, stride_a, stride_b, stride_c};
   if (k_splits > 1) return launch_bf16_splitk(args, b_layout, out_dtype, k_splits, scratch);
+  if (config < 0 && batch == 1 && static_cast<int>(env_int("GEMM_B200_BF16_CONFIG", -1)) < 0) {
+    // Problems whose 256-column tiles leave most SMs idle and whose K is not long enough for K
+    // splits to pay: 128-column tiles give twice the units in one launch (256 x 8192 x 8192:
+    // 54 -> 48 us, 512 x 4096 x 4096: 31.5 -> 25.4 us, 1024^3: 15.2 -> 13.2 us, 128 x 4096 x 4096:
+    // 25.6 us with K splits -> 22.6 us; from 64 tiles of 256 columns up the wider tile wins again).
+    const int64_t row_pairs = ceil_div64(M, 2 * kBlockM);
+    const int64_t units256 = row_pairs * ceil_div64(N, kBlockN), units128 = row_pairs * ceil_div64(N, 128);
+    const int64_t tiles128 = ceil_div64(N, 128);
+    if (M > kBlockM && 4 * units256 <= di.sms && 8 * units128 >= di.sms && K <= 8192)
+      config = kBf16Cfg2ctaN128;
+    else if (M > 32 && M <= kBlockM && tiles128 >= 24 && tiles128 <= di.sms && K <= 4096)
+      config = kBf16Cfg1ctaN128;
+  }
   if (config < 0 && k_splits == 0 && batch == 1) {
     // few output tiles and a long K: cut K so the whole GPU works on the problem
     const int splits = bf16_auto_splits(M, N, K, di.sms);
