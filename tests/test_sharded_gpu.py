@@ -36,7 +36,11 @@ def _worker(rank, world, port, q):
 def test_two_ranks_match_one_gpu(ops):
     import torch.multiprocessing as mp
     from gemm_b200 import sharded
-    world, port = 2, 29541
+    import socket
+    with socket.socket(socket.AF_INET, socket.SOCK_STREAM) as sk:
+        sk.bind(("127.0.0.1", 0))
+        port = sk.getsockname()[1]
+    world = 2
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
     procs = [ctx.Process(target=_worker, args=(r, world, port, q)) for r in range(world)]
