@@ -838,6 +838,21 @@ extern "C" int gemm_b200_gemm_mxfp8_cfg(const void* Aq, const void* SFA, const v
       // 64 tiles of 256 columns up the wider tile wins again)
       const int64_t units256 = ceil_div64(M, 2 * tc::kBlockM) * ceil_div64(N, tc::kBlockN);
       config = (4 * units256 <= (int64_t)di.sms) ? tc::kN128MxConfig : tc::kDefaultMxConfig;
+      // a handful of tiles and a very long K (e.g. 256 x 65536 x 256): only K splits put the GPU to work
+      const int64_t tiles_1cta = ceil_div64(M, tc::kBlockM) * ceil_div64(N, tc::kBlockN);
+      if (8 * tiles_1cta <= (int64_t)di.sms && K >= 16384 && N % 4 == 0) {
+        const int splits = tc::auto_splits(M, N, K, di.sms);
+        if (splits > 1) {
+          if (int rc = tc::cached_scratch(di.dev, (size_t)splits * M * N * sizeof(float), &args.scratch, st)) return rc;
+          if (args.scratch) {
+            args.k_splits = splits;
+            if (log_enabled())
+              fprintf(stderr, "[gemm_b200] gemm_mxfp8 %lldx%lldx%lld -> %s, %d K splits\n", (long long)M, (long long)K,
+                      (long long)N, tc::kMxConfigs[tc::kSkinnyMxConfig].name, splits);
+            return tc::launch_mxfp8_splitk<tc::Mx_1cta>(args, out_dtype);
+          }
+        }
+      }
     }
   }
   if (log_enabled())

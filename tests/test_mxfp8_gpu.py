@@ -237,3 +237,19 @@ def test_half_round_problems_take_the_128_column_tiles(ops, oracle, M, K, N):
     ops.check_status()
     assert torch.equal(auto, wide)
     _gemm_check(ops, oracle, M, K, N, config=ops.gemm_mxfp8_configs().index("2cta_256x128x128_s7_maskcommit_tmastore"), seed=1)
+
+
+def test_handful_of_tiles_and_long_k_splits_by_itself(ops, oracle):
+    """M > 128 with two tiles and K = 32768: the library cuts K on its own scratch; only the
+    summation order differs from the unsplit kernel."""
+    M, K, N = 256, 32768, 264
+    A, B = oracle.gen_randn_bf16(M, K, N, seed=21)
+    Aq = ops.quantize_mxfp8(A.cuda())
+    Bq = ops.quantize_mxfp8(B.cuda(), transposed_in=True)
+    auto = ops.gemm_mxfp8(Aq, Bq, out_dtype=torch.float32)
+    unsplit = ops.gemm_mxfp8(Aq, Bq, out_dtype=torch.float32, config=3)
+    ops.check_status()
+    assert oracle.rel_frobenius(auto.cpu(), unsplit.cpu()) <= 1e-5
+    qa, sa = oracle.mxfp8_quantize(A)
+    qb, sb = oracle.mxfp8_quantize(B.t().contiguous())
+    assert oracle.rel_frobenius(auto.cpu(), oracle.mxfp8_matmul_oracle(qa, sa, qb, sb)) <= REL_TOL
