@@ -115,3 +115,29 @@ def test_scale_packing(oracle):
     for r, kb in [(0, 0), (31, 3), (32, 0), (127, 9), (128, 4), (299, 9)]:
         assert int(packed[oracle.mxfp8_scale_offset(rows, K, r, kb)]) == int(s[r, kb])
     assert int(packed.sum()) == int(s.long().sum())                   # padding is zero
+
+
+def test_mxfp8_quantiser_matches_torch_casts_per_block(oracle):
+    """Independent pin of the recipe: the same quantisation composed from torch's own float8 casts
+    (float8_e8m0fnu for the power-of-two scale, float8_e4m3fn for the data), block by block."""
+    g = torch.Generator().manual_seed(11)
+    X = (torch.randn(96, 512, generator=g) * torch.exp(torch.randn(96, 1, generator=g) * 5)).bfloat16()
+    X[3, 64:96] = 0                                                   # all-zero block
+    X[5, :32] = torch.linspace(1.0, 1.99, 32).bfloat16()              # values that clip at 448
+    q, s = oracle.mxfp8_quantize(X)
+    blocks = X.float().view(96, 16, 32)
+    amax = blocks.abs().amax(dim=2)
+    nz = amax > 0
+    scale = torch.exp2(torch.floor(torch.log2(amax.clamp_min(2.0 ** -126))) - 8)
+    scale_byte = scale.to(torch.float8_e8m0fnu).view(torch.uint8)
+    assert torch.equal(s[nz], scale_byte[nz])
+    assert int(s[~nz].max()) == 0
+    back = scale_byte.view(torch.float8_e8m0fnu).float()              # what the scale byte decodes to
+    data = (blocks / back[:, :, None]).clamp(-448, 448).to(torch.float8_e4m3fn).view(torch.uint8)
+    keep = nz[:, :, None].expand_as(blocks)
+    assert torch.equal(q.view(96, 16, 32)[keep], data[keep])
+    assert int(q.view(96, 16, 32)[~keep].max()) == 0
+    # and the dequantiser against torch's decode of the same bytes
+    dq = oracle.mxfp8_dequantize(q, s).view(96, 16, 32)
+    want = q.view(torch.float8_e4m3fn).float().view(96, 16, 32) * s.view(torch.float8_e8m0fnu).float()[:, :, None]
+    assert torch.equal(dq[keep], want[keep])

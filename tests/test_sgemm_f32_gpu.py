@@ -118,6 +118,39 @@ def test_linearity_at_full_size(ops):
     assert torch.equal(C1[rows].cpu(), want)
 
 
+def _tile_edge_rows(n, extra=48, seed=1):
+    """First and last rows of C, the rows either side of every 64/128-row tile boundary near both
+    ends, and `extra` random rows."""
+    edge = [0, 1, 63, 64, 127, 128, n // 2 - 1, n // 2, n - 129, n - 128, n - 65, n - 64, n - 2, n - 1]
+    rnd = torch.randint(0, n, (extra,), generator=torch.Generator().manual_seed(seed)).tolist()
+    return torch.tensor(sorted(set(edge + rnd)))
+
+
+def test_sweep_2048_full_frobenius_and_sampled_bits(ops, oracle):
+    # sweep point 2048^3 (uniform[-1,1), seed 0): the whole result against torch.matmul on the CPU,
+    # sampled rows bit for bit against the restated reference arithmetic
+    n = 2048
+    A, B = oracle.gen_uniform_f32(n, n, n, seed=0)
+    C = _run(ops, A, B)
+    assert oracle.rel_frobenius(C, oracle.matmul_cpu(A, B)) <= REL_FRO_TOL
+    rows = _tile_edge_rows(n)
+    assert torch.equal(C[rows], oracle.sgemm_seq(A[rows], B))
+
+
+def test_sweep_8192_sampled(ops, oracle):
+    # sweep point 8192^3: sampled rows (tile edges included) bit for bit, and the same rows within
+    # the Frobenius tolerance of torch.matmul on the CPU
+    n = 8192
+    A, B = oracle.gen_uniform_f32(n, n, n, seed=0)
+    C = _run(ops, A, B)
+    rows = _tile_edge_rows(n, extra=50, seed=2)
+    got = C[rows]
+    assert torch.equal(got, oracle.sgemm_seq(A[rows], B))
+    assert oracle.rel_frobenius(got, oracle.matmul_cpu(A[rows], B)) <= REL_FRO_TOL
+    # no row of the result was left unwritten (C starts as NaN)
+    assert not bool(torch.isnan(C).any())
+
+
 @pytest.mark.parametrize("variant", ["naive", "shared", "blocktile_1d"])
 @pytest.mark.parametrize("shape", [(128, 128, 128), (512, 512, 512), (200, 77, 130)])
 def test_bit_identical_to_reference_kernels(ops, oracle, variant, shape):

@@ -83,3 +83,54 @@ def test_two_gloo_ranks_reproduce_the_single_rank_result():
         assert torch.equal(C, full[row0:row0 + rows])     # same rows, same bits, whatever the rank count
         assert bsum == float(B.sum())                     # every rank holds the broadcast B
         assert t == 0.5 and n == 6.0                      # max / sum over ranks
+
+
+# ----------------------------------------------------------------------------------------------
+# failure detection on the host: a rank that leaves between steps, and one that stops answering
+# ----------------------------------------------------------------------------------------------
+def _live_worker(rank, world, port, q, mode):
+    import datetime
+    import time
+    store = dist.TCPStore("127.0.0.1", port, world, is_master=(rank == 0), timeout=datetime.timedelta(seconds=30))
+    live = sharded.Liveness(store, rank, world, timeout_s=1.0)
+    done, outcome = 0, "finished"
+    try:
+        for step in range(4):
+            if rank == 1 and step == 2:
+                if mode == "leaves":
+                    live.leave()              # between steps, nothing in flight
+                    outcome = "left"
+                else:
+                    time.sleep(3.0)           # stops answering: never checks in for step 2
+                    outcome = "silent"
+                break
+            live.check_in(step)
+            done += 1                         # the step itself (this rank's rows) would run here
+    except sharded.PeerLeft as e:
+        outcome = "peer-left: " + str(e)
+    except sharded.PeerLost as e:
+        outcome = "peer-lost: " + str(e)
+    q.put((rank, done, outcome))
+    if rank == 0:
+        time.sleep(0.5 if mode == "leaves" else 3.5)   # the store's host outlives its clients
+
+
+@pytest.mark.parametrize("mode", ["leaves", "silent"])
+def test_a_rank_that_goes_away_is_noticed_before_the_next_step(mode):
+    world, port = 2, _free_port()
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    procs = [ctx.Process(target=_live_worker, args=(r, world, port, q, mode)) for r in range(world)]
+    for p in procs:
+        p.start()
+    results = dict((r, (d, o)) for r, d, o in [q.get(timeout=60) for _ in range(world)])
+    for p in procs:
+        p.join(timeout=30)
+        assert p.exitcode == 0
+    assert results[1][0] == 2                                   # rank 1 ran steps 0 and 1
+    done0, outcome0 = results[0]
+    assert done0 == 2                                            # rank 0 launched nothing for step 2
+    if mode == "leaves":
+        assert outcome0.startswith("peer-left: rank 1 left before step 2")
+    else:
+        assert outcome0.startswith("peer-lost: rank 1 did not check in for step 2")

@@ -1,5 +1,5 @@
-"""Row-sharded BF16 GEMM on two GPUs (NCCL): every rank's rows equal the single-GPU result.
-Skipped on machines with fewer than two GPUs."""
+"""Row-sharded BF16 and MXFP8 GEMM on two GPUs (NCCL): every rank's rows equal the single-GPU
+result bit for bit.  Skipped on machines with fewer than two GPUs."""
 import os
 
 import pytest
@@ -8,7 +8,7 @@ import torch
 pytestmark = pytest.mark.gpu
 
 
-def _worker(rank, world, port, q):
+def _worker(rank, world, port, q, mx=False):
     import torch.distributed as dist
     import gemm_b200.ops as ops
     from gemm_b200 import sharded
@@ -24,7 +24,13 @@ def _worker(rank, world, port, q):
         A = torch.cat([sharded.gen_a_block_cuda(b, rows_per_block, K, dev) for b in shard.blocks])
         B = sharded.gen_b_cuda(K, N, dev) if rank == 0 else torch.empty(K, N, device=dev, dtype=torch.bfloat16)
         sharded.broadcast_b(B, src=0)
-        Cd = ops.gemm_bf16(A, B)
+        if mx:
+            # rank 0's quantised B is the one every rank multiplies by
+            Bq = ops.quantize_mxfp8(B if rank == 0 else torch.zeros_like(B), transposed_in=True)
+            sharded.broadcast_mxfp8(Bq, src=0)
+            Cd = ops.gemm_mxfp8(ops.quantize_mxfp8(A), Bq)
+        else:
+            Cd = ops.gemm_bf16(A, B)
         ops.check_status(dev)
         t = sharded.max_over_ranks(float(rank + 1), device=dev)
         q.put((rank, shard.row0, shard.rows, Cd.cpu(), t))
@@ -33,7 +39,8 @@ def _worker(rank, world, port, q):
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
-def test_two_ranks_match_one_gpu(ops):
+@pytest.mark.parametrize("mx", [False, True], ids=["bf16", "mxfp8"])
+def test_two_ranks_match_one_gpu(ops, mx):
     import torch.multiprocessing as mp
     from gemm_b200 import sharded
     import socket
@@ -43,7 +50,7 @@ def test_two_ranks_match_one_gpu(ops):
     world = 2
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
-    procs = [ctx.Process(target=_worker, args=(r, world, port, q)) for r in range(world)]
+    procs = [ctx.Process(target=_worker, args=(r, world, port, q, mx)) for r in range(world)]
     for p in procs:
         p.start()
     results = sorted([q.get(timeout=300) for _ in range(world)], key=lambda x: x[0])
@@ -54,7 +61,10 @@ def test_two_ranks_match_one_gpu(ops):
     dev = torch.device("cuda", 0)
     A = torch.cat([sharded.gen_a_block_cuda(b, M // sharded.BLOCKS, K, dev) for b in range(sharded.BLOCKS)])
     B = sharded.gen_b_cuda(K, N, dev)
-    full = ops.gemm_bf16(A, B).cpu()
+    if mx:
+        full = ops.gemm_mxfp8(ops.quantize_mxfp8(A), ops.quantize_mxfp8(B, transposed_in=True)).cpu()
+    else:
+        full = ops.gemm_bf16(A, B).cpu()
     for rank, row0, rows, Cd, t in results:
         assert torch.equal(Cd, full[row0:row0 + rows])
         assert t == 2.0
