@@ -47,7 +47,6 @@ SIGNATURES = {
     "gemm_b200_release_workspace": (i32, []),
     "gemm_b200_check_status": (i32, [vp, C.POINTER(C.c_int32)]),
     "gemm_b200_selftest_wait_timeout": (i32, [i64, vp, vp]),
-    "gemm_b200_selftest_tma_stream": (i32, [vp, i64, i64, i64, i32, vp]),
     "gemm_b200_last_error": (C.c_char_p, []),
     "gemm_b200_version": (i32, []),
     "gemm_b200_device_supported": (i32, [i32]),

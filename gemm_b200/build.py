@@ -5,6 +5,8 @@ Produces, next to the sources (all git-ignored, all shipped with the working tre
 * ``gemm_b200/libgemm_b200.so`` — the C-ABI library declared in ``include/gemm_b200.h``
   (FP32 CUDA-core kernels + sm_100a tensor-core kernels), built with nvcc for
   ``arch=compute_100a,code=sm_100a``;
+* ``gemm_b200/profiling/libgemm_b200_probe.so`` — the TMA streaming probe (a measurement helper,
+  not part of the GEMM library);
 * ``gemm_b200/variants/<variant>/<module>.so`` — one PyTorch extension module per reference
   variant, with the reference's module and function names
   (naive/test.py:5-11, shared/test.py:5-11, blocktile_1d/test.py:5-11).
@@ -28,9 +30,12 @@ CSRC = PKG / "csrc"
 INCLUDE = ROOT / "include"
 BUILD = PKG / "build"
 LIB = PKG / "libgemm_b200.so"
+PROBE_LIB = PKG / "profiling" / "libgemm_b200_probe.so"
 
 ARCH = ["-gencode", "arch=compute_100a,code=sm_100a"]
 NVCC_COMMON = ["-O3", "-std=c++17", "-lineinfo", "-Xcompiler", "-fPIC"]
+# host-side warnings are errors (the device front end's own diagnostics stay warnings)
+HOST_WARNINGS = ["-Xcompiler", "-Wall,-Wextra,-Werror,-Wno-unused-parameter"]
 
 # translation unit -> extra flags.  The FP32 kernel flushes denormals like the reference, which
 # is built with --use_fast_math (naive/test.py:8).
@@ -47,6 +52,10 @@ VARIANTS = {
     "shared": ("shared_gemm", ["shared.cpp", "shared_2.cu"]),
     "blocktile_1d": ("blocktile_1d", ["blocktile_1d.cpp", "blocktile_1d.cu"]),
 }
+
+
+# `python -m gemm_b200.build --tuning` also compiles the kernel variants the heuristics never pick
+TUNING: list[str] = []
 
 
 def nvcc() -> str:
@@ -83,7 +92,7 @@ def build_library(force: bool = False, verbose: bool = False) -> Path:
         o = BUILD / (s.stem + ".o")
         objs.append(o)
         if force or not _newer(o, [s] + hdrs):
-            cmd = [nvcc(), *ARCH, *NVCC_COMMON, *extra, "-c", str(s), "-o", str(o)]
+            cmd = [nvcc(), *ARCH, *NVCC_COMMON, *HOST_WARNINGS, *extra, *TUNING, "-c", str(s), "-o", str(o)]
             if verbose:
                 cmd.insert(1, "-Xptxas=-v")
             jobs.append(cmd)
@@ -93,6 +102,14 @@ def build_library(force: bool = False, verbose: bool = False) -> Path:
     if force or jobs or not _newer(LIB, objs):
         _run([nvcc(), *ARCH, "-shared", "-o", str(LIB), *map(str, objs)])
     return LIB
+
+
+def build_probe(force: bool = False) -> Path:
+    """The TMA streaming probe of gemm_b200.profiling, a shared library of its own."""
+    src = PKG / "profiling" / "probe_tma_stream.cu"
+    if force or not _newer(PROBE_LIB, [src] + _headers()):
+        _run([nvcc(), *ARCH, *NVCC_COMMON, *HOST_WARNINGS, "-shared", str(src), "-o", str(PROBE_LIB)])
+    return PROBE_LIB
 
 
 def _torch_flags() -> tuple[list[str], list[str]]:
@@ -137,6 +154,7 @@ def build_variant(variant: str, force: bool = False) -> Path:
 
 def build_all(variants: bool = True, force: bool = False, verbose: bool = False) -> None:
     build_library(force=force, verbose=verbose)
+    build_probe(force=force)
     if variants:
         with cf.ThreadPoolExecutor(max_workers=3) as ex:
             list(ex.map(lambda v: build_variant(v, force=force), VARIANTS))
@@ -147,7 +165,11 @@ def main(argv: list[str] | None = None) -> int:
     ap.add_argument("--no-variants", action="store_true", help="build only libgemm_b200.so")
     ap.add_argument("--force", action="store_true")
     ap.add_argument("--verbose", action="store_true", help="pass -Xptxas=-v")
+    ap.add_argument("--tuning", action="store_true", help="also build the kernel variants only tuning sweeps use")
     a = ap.parse_args(argv)
+    if a.tuning:
+        TUNING.append("-DGEMM_B200_TUNING")
+        a.force = True
     build_all(variants=not a.no_variants, force=a.force, verbose=a.verbose)
     print(LIB)
     return 0

@@ -52,10 +52,36 @@ static int workspace(size_t bytes, Workspace** out) {
 
 static size_t align_up(size_t x) { return (x + 255) & ~(size_t)255; }
 
+// Queues everything: B up, then per slab A up -> GEMM -> C down, on the three streams.
+template <class Launch>
+static int enqueue(Workspace* w, const void* hA, const void* hB, void* hC, int64_t M, int64_t N, int64_t K, size_t ea,
+                   size_t eb, size_t ec, char* dA, char* dB, char* dC, int64_t slab, int nslabs, Launch launch) {
+  if (K > 0) GEMM_B200_CUDA_TRY(cudaMemcpyAsync(dB, hB, (size_t)K * N * eb, cudaMemcpyHostToDevice, w->s_in));
+  GEMM_B200_CUDA_TRY(cudaEventRecord(w->b_up, w->s_in));
+  GEMM_B200_CUDA_TRY(cudaStreamWaitEvent(w->s_mm, w->b_up, 0));
+  for (int i = 0; i < nslabs; ++i) {
+    const int64_t r0 = (int64_t)i * slab, rows = (M - r0 < slab) ? (M - r0) : slab;
+    if (K > 0)
+      GEMM_B200_CUDA_TRY(cudaMemcpyAsync(dA + (size_t)r0 * K * ea, static_cast<const char*>(hA) + (size_t)r0 * K * ea,
+                                         (size_t)rows * K * ea, cudaMemcpyHostToDevice, w->s_in));
+    GEMM_B200_CUDA_TRY(cudaEventRecord(w->up[i], w->s_in));
+    GEMM_B200_CUDA_TRY(cudaStreamWaitEvent(w->s_mm, w->up[i], 0));
+    if (int rc = launch(dA + (size_t)r0 * K * ea, dB, dC + (size_t)r0 * N * ec, rows, w->s_mm)) return rc;
+    GEMM_B200_CUDA_TRY(cudaEventRecord(w->done[i], w->s_mm));
+    GEMM_B200_CUDA_TRY(cudaStreamWaitEvent(w->s_out, w->done[i], 0));
+    GEMM_B200_CUDA_TRY(cudaMemcpyAsync(static_cast<char*>(hC) + (size_t)r0 * N * ec, dC + (size_t)r0 * N * ec,
+                                       (size_t)rows * N * ec, cudaMemcpyDeviceToHost, w->s_out));
+  }
+  return GEMM_B200_OK;
+}
+
 // launch(dA, dB, dC, rows, stream) runs the GEMM of `rows` rows of A on device pointers.
+// check_tc: the launch runs tensor-core kernels, whose bounded waits report through the device
+// status word; it is read (and cleared) before returning, so a wait that gave up comes back as
+// GEMM_B200_ERR_TIMEOUT instead of a silently wrong hC.
 template <class Launch>
 static int run(const void* hA, const void* hB, void* hC, int64_t M, int64_t N, int64_t K, size_t ea, size_t eb,
-               size_t ec, Launch launch) {
+               size_t ec, bool check_tc, Launch launch) {
   if (M < 0 || N < 0 || K < 0) return fail(GEMM_B200_ERR_INVALID_ARG, "host gemm: negative size");
   if (M == 0 || N == 0) return GEMM_B200_OK;
   if (!hC || (K > 0 && (!hA || !hB))) return fail(GEMM_B200_ERR_INVALID_ARG, "host gemm: null pointer");
@@ -78,25 +104,17 @@ static int run(const void* hA, const void* hB, void* hC, int64_t M, int64_t N, i
   }
   const int nslabs = (int)ceil_div64(M, slab);
 
-  if (K > 0) GEMM_B200_CUDA_TRY(cudaMemcpyAsync(dB, hB, (size_t)K * N * eb, cudaMemcpyHostToDevice, w->s_in));
-  GEMM_B200_CUDA_TRY(cudaEventRecord(w->b_up, w->s_in));
-  GEMM_B200_CUDA_TRY(cudaStreamWaitEvent(w->s_mm, w->b_up, 0));
-  for (int i = 0; i < nslabs; ++i) {
-    const int64_t r0 = (int64_t)i * slab, rows = (M - r0 < slab) ? (M - r0) : slab;
-    if (K > 0)
-      GEMM_B200_CUDA_TRY(cudaMemcpyAsync(dA + (size_t)r0 * K * ea, static_cast<const char*>(hA) + (size_t)r0 * K * ea,
-                                         (size_t)rows * K * ea, cudaMemcpyHostToDevice, w->s_in));
-    GEMM_B200_CUDA_TRY(cudaEventRecord(w->up[i], w->s_in));
-    GEMM_B200_CUDA_TRY(cudaStreamWaitEvent(w->s_mm, w->up[i], 0));
-    if (int rc = launch(dA + (size_t)r0 * K * ea, dB, dC + (size_t)r0 * N * ec, rows, w->s_mm)) return rc;
-    GEMM_B200_CUDA_TRY(cudaEventRecord(w->done[i], w->s_mm));
-    GEMM_B200_CUDA_TRY(cudaStreamWaitEvent(w->s_out, w->done[i], 0));
-    GEMM_B200_CUDA_TRY(cudaMemcpyAsync(static_cast<char*>(hC) + (size_t)r0 * N * ec, dC + (size_t)r0 * N * ec,
-                                       (size_t)rows * N * ec, cudaMemcpyDeviceToHost, w->s_out));
-  }
-  GEMM_B200_CUDA_TRY(cudaStreamSynchronize(w->s_out));
-  GEMM_B200_CUDA_TRY(cudaStreamSynchronize(w->s_mm));
-  GEMM_B200_CUDA_TRY(cudaStreamSynchronize(w->s_in));
+  const int rc = enqueue(w, hA, hB, hC, M, N, K, ea, eb, ec, dA, dB, dC, slab, nslabs, launch);
+  // Success or not, nothing queued above may outlive this call: copies still in flight read and
+  // write the caller's host buffers, and the next call reuses the workspace.
+  const cudaError_t e_out = cudaStreamSynchronize(w->s_out);
+  const cudaError_t e_mm = cudaStreamSynchronize(w->s_mm);
+  const cudaError_t e_in = cudaStreamSynchronize(w->s_in);
+  if (rc != GEMM_B200_OK) return rc;   // the message of the first failure stays in last_error
+  GEMM_B200_CUDA_TRY(e_out);
+  GEMM_B200_CUDA_TRY(e_mm);
+  GEMM_B200_CUDA_TRY(e_in);
+  if (check_tc) return gemm_b200_check_status(w->s_mm, nullptr);
   return GEMM_B200_OK;
 }
 
@@ -104,7 +122,7 @@ static int run(const void* hA, const void* hB, void* hC, int64_t M, int64_t N, i
 }  // namespace gemm_b200
 
 extern "C" int gemm_b200_sgemm_f32_host(const float* hA, const float* hB, float* hC, int64_t M, int64_t N, int64_t K) {
-  return gemm_b200::host::run(hA, hB, hC, M, N, K, 4, 4, 4,
+  return gemm_b200::host::run(hA, hB, hC, M, N, K, 4, 4, 4, /*check_tc=*/false,
                               [&](const void* dA, const void* dB, void* dC, int64_t rows, cudaStream_t st) {
                                 return gemm_b200_sgemm_f32(static_cast<const float*>(dA), static_cast<const float*>(dB),
                                                            static_cast<float*>(dC), rows, N, K, K, N, N, st);
@@ -115,7 +133,7 @@ extern "C" int gemm_b200_gemm_bf16_host(const void* hA, const void* hB, void* hC
                                         int b_layout, int out_dtype) {
   const size_t ec = out_dtype == GEMM_B200_OUT_F32 ? 4 : 2;
   const int64_t ldb = b_layout == GEMM_B200_B_ROW_MAJOR_KN ? N : K;
-  return gemm_b200::host::run(hA, hB, hC, M, N, K, 2, 2, ec,
+  return gemm_b200::host::run(hA, hB, hC, M, N, K, 2, 2, ec, /*check_tc=*/true,
                               [&](const void* dA, const void* dB, void* dC, int64_t rows, cudaStream_t st) {
                                 return gemm_b200_gemm_bf16(dA, dB, dC, rows, N, K, K, ldb, N, b_layout, out_dtype, st);
                               });

@@ -14,10 +14,10 @@
 //   * A and B tiles staged in shared memory by 16-byte cp.async, STAGES deep,
 //     one __syncthreads per K tile;
 //   * A is kept K-contiguous in shared memory with rows padded to BK+4 floats:
-//     a thread reads four consecutive k of one row with one LDS.128 and the four
-//     row addresses of a warp fall into different bank groups (the row stride is
-//     an odd multiple of 16 bytes); B fragments are LDS.128 along N, 128
-//     contiguous bytes per warp;
+//     a thread reads two consecutive k of one row with one LDS.64 (AK = 2; AK = 4
+//     reads four with one LDS.128) and the four row addresses of a warp fall into
+//     different bank groups (the row stride is an odd multiple of 16 bytes); B
+//     fragments are LDS.128 along N, 128 contiguous bytes per warp;
 //   * optionally the multiply-adds are issued as packed fma.rn.f32x2 (two
 //     columns of C per instruction), which halves the issue slots the FMA
 //     stream needs.
@@ -283,6 +283,11 @@ static int launch_cfg(const float* A, const float* B, float* Cm, int M, int N, i
 }
 
 //                        BM   BN  BK WMW WNW ST MINB X2  AK
+using C64x128k32p3     = Cfg<64, 128, 32, 2, 2, 3, 2, true>;
+using C64x64k32p       = Cfg<64, 64, 32, 2, 2, 4, 4, true>;
+using C32x64k32p       = Cfg<32, 64, 32, 2, 2, 4, 6, true>;
+#ifdef GEMM_B200_TUNING
+// tile shapes the heuristic never picks; built only for tuning sweeps
 using C128x128k16      = Cfg<128, 128, 16, 4, 2, 3, 2, false>;
 using C128x128k16p     = Cfg<128, 128, 16, 4, 2, 3, 2, true>;
 using C128x128k32p     = Cfg<128, 128, 32, 4, 2, 3, 2, true>;
@@ -292,14 +297,16 @@ using C128x256k32p     = Cfg<128, 256, 32, 4, 2, 3, 1, true>;
 using C256x128k32p     = Cfg<256, 128, 32, 8, 1, 3, 1, true>;
 using C128x64k32p      = Cfg<128, 64, 32, 4, 2, 3, 2, true>;
 using C64x64k16p       = Cfg<64, 64, 16, 2, 2, 4, 4, true>;
-using C64x64k32p       = Cfg<64, 64, 32, 2, 2, 4, 4, true>;
 using C64x64k16        = Cfg<64, 64, 16, 2, 2, 4, 4, false>;
 using C32x64k16p       = Cfg<32, 64, 16, 2, 2, 4, 6, true>;
-using C32x64k32p       = Cfg<32, 64, 32, 2, 2, 4, 6, true>;
 using C128x128k32      = Cfg<128, 128, 32, 4, 2, 3, 2, false>;
-using C64x128k32p3     = Cfg<64, 128, 32, 2, 2, 3, 2, true>;
+#endif
 
 static const ConfigEntry kConfigs[] = {
+    {"64x128x32_s3_f32x2", 64, 128, launch_cfg<C64x128k32p3>},
+    {"64x64x32_s4_f32x2", 64, 64, launch_cfg<C64x64k32p>},
+    {"32x64x32_s4_f32x2", 32, 64, launch_cfg<C32x64k32p>},
+#ifdef GEMM_B200_TUNING
     {"128x128x16_s3", 128, 128, launch_cfg<C128x128k16>},
     {"128x128x16_s3_f32x2", 128, 128, launch_cfg<C128x128k16p>},
     {"128x128x32_s3_f32x2", 128, 128, launch_cfg<C128x128k32p>},
@@ -309,12 +316,10 @@ static const ConfigEntry kConfigs[] = {
     {"256x128x32_s3_f32x2", 256, 128, launch_cfg<C256x128k32p>},
     {"128x64x32_s3_f32x2", 128, 64, launch_cfg<C128x64k32p>},
     {"64x64x16_s4_f32x2", 64, 64, launch_cfg<C64x64k16p>},
-    {"64x64x32_s4_f32x2", 64, 64, launch_cfg<C64x64k32p>},
     {"64x64x16_s4", 64, 64, launch_cfg<C64x64k16>},
     {"32x64x16_s4_f32x2", 32, 64, launch_cfg<C32x64k16p>},
-    {"32x64x32_s4_f32x2", 32, 64, launch_cfg<C32x64k32p>},
     {"128x128x32_s3", 128, 128, launch_cfg<C128x128k32>},
-    {"64x128x32_s3_f32x2", 64, 128, launch_cfg<C64x128k32p3>},
+#endif
 };
 constexpr int kNumConfigs = sizeof(kConfigs) / sizeof(kConfigs[0]);
 

@@ -234,27 +234,54 @@ static int auto_splits(int64_t M, int64_t N, int64_t K, int sms) {
   return auto_splits_units(ceil_div64(M, kBlockM) * ceil_div64(N, kBlockN), ceil_div64(K, 2 * kMxBlockK), sms);
 }
 
-// library-owned scratch for the automatic split-K path, one buffer per device, grown on demand
+// Library-owned scratch of the automatic split-K path: one buffer per (device, stream), grown on
+// demand.  Work on one stream is ordered, so calls that share a buffer never overlap; calls on
+// different streams get different buffers and may run side by side.  At most kScratchSlots
+// streams per process keep a buffer; beyond that the least recently used one is released
+// (cudaFree waits for the device, so nothing still reads it).
+struct ScratchSlot {
+  int dev = -1;
+  cudaStream_t stream = nullptr;
+  void* ptr = nullptr;
+  size_t bytes = 0;
+  uint64_t last_use = 0;
+};
+constexpr int kScratchSlots = 32;
 static std::mutex g_scratch_mu;
-static void* g_scratch[64] = {nullptr};
-static size_t g_scratch_bytes[64] = {0};
-// *out stays null (and the call succeeds) when the buffer would have to grow while `stream` is
-// being captured into a graph: allocation is not allowed there, and the caller runs unsplit.
+static ScratchSlot g_scratch[kScratchSlots];
+static uint64_t g_scratch_clock = 0;
+// *out stays null (and the call succeeds) when a buffer would have to be allocated or grown while
+// `stream` is being captured into a graph: allocation is not allowed there, and the caller runs
+// unsplit.
 static int cached_scratch(int dev, size_t bytes, float** out, cudaStream_t stream) {
   std::lock_guard<std::mutex> lk(g_scratch_mu);
-  const int slot = dev & 63;
   *out = nullptr;
-  if (g_scratch_bytes[slot] < bytes) {
+  ScratchSlot* slot = nullptr;      // this stream's buffer, if it has one
+  ScratchSlot* victim = nullptr;    // else: a free slot, or the least recently used one
+  for (ScratchSlot& c : g_scratch) {
+    if (c.ptr && c.dev == dev && c.stream == stream) { slot = &c; break; }
+    if (!victim || (victim->ptr && (!c.ptr || c.last_use < victim->last_use))) victim = &c;
+  }
+  if (!slot || slot->bytes < bytes) {
     cudaStreamCaptureStatus cs = cudaStreamCaptureStatusNone;
     GEMM_B200_CUDA_TRY(cudaStreamIsCapturing(stream, &cs));
     if (cs != cudaStreamCaptureStatusNone) return GEMM_B200_OK;
-    if (g_scratch[slot]) GEMM_B200_CUDA_TRY(cudaFree(g_scratch[slot]));
-    g_scratch[slot] = nullptr;
-    g_scratch_bytes[slot] = 0;
-    GEMM_B200_CUDA_TRY(cudaMalloc(&g_scratch[slot], bytes));
-    g_scratch_bytes[slot] = bytes;
+    if (!slot) slot = victim;
+    if (slot->ptr) {
+      int cur = dev;
+      if (slot->dev != dev) GEMM_B200_CUDA_TRY(cudaSetDevice(slot->dev));
+      cudaError_t e = cudaFree(slot->ptr);
+      if (slot->dev != dev) GEMM_B200_CUDA_TRY(cudaSetDevice(cur));
+      GEMM_B200_CUDA_TRY(e);
+    }
+    *slot = ScratchSlot();
+    GEMM_B200_CUDA_TRY(cudaMalloc(&slot->ptr, bytes));
+    slot->dev = dev;
+    slot->stream = stream;
+    slot->bytes = bytes;
   }
-  *out = static_cast<float*>(g_scratch[slot]);
+  slot->last_use = ++g_scratch_clock;
+  *out = static_cast<float*>(slot->ptr);
   return GEMM_B200_OK;
 }
 
@@ -370,33 +397,47 @@ struct Bf16ConfigEntry {
 //                          CG ST EPI MASK
 using Bf16_1cta_direct = Bf16Cfg<1, 4, 0, false>;
 using Bf16_1cta_tma    = Bf16Cfg<1, 4, 1, false>;
-using Bf16_2cta_direct = Bf16Cfg<2, 6, 0, false>;
-using Bf16_2cta_tma    = Bf16Cfg<2, 6, 1, false>;
 using Bf16_2cta_tma_m  = Bf16Cfg<2, 6, 1, true>;
-using Bf16_2cta_n512    = Bf16Cfg<2, 4, 1, true, 2>;
-using Bf16_2cta_n512_d  = Bf16Cfg<2, 4, 0, true, 2>;
 using Bf16_2cta_n512_s3 = Bf16Cfg<2, 3, 1, true, 2, 2>;
 using Bf16_2cta_n128    = Bf16Cfg<2, 7, 1, true, 1, 2, 128>;
 using Bf16_1cta_n128    = Bf16Cfg<1, 6, 1, false, 1, 2, 128>;
+#ifdef GEMM_B200_TUNING
+// variants the heuristics never pick; built only for tuning sweeps
+using Bf16_2cta_direct = Bf16Cfg<2, 6, 0, false>;
+using Bf16_2cta_tma    = Bf16Cfg<2, 6, 1, false>;
+using Bf16_2cta_n512    = Bf16Cfg<2, 4, 1, true, 2>;
+using Bf16_2cta_n512_d  = Bf16Cfg<2, 4, 0, true, 2>;
+#endif
+
+// index of every variant in kBf16Configs (the order of the table below)
+enum Bf16ConfigId : int {
+  kBf16Cfg1ctaDirect = 0,   // single CTA, 128x256 tiles, direct stores: the split-K partial sums
+  kBf16Cfg1cta,             // single CTA, 128x256 tiles, TMA store
+  kBf16Cfg256,              // CTA pair, 256x256 tiles, double-buffered accumulator
+  kBf16Cfg512,              // CTA pair, 256x512 tiles (A shared by two accumulators)
+  kBf16Cfg2ctaN128,         // CTA pair, 256x128 tiles: at most half a round of 256-wide tiles
+  kBf16Cfg1ctaN128,         // single CTA, 128x128 tiles: one row tile and few column tiles
+#ifdef GEMM_B200_TUNING
+  kBf16Tune2ctaDirect, kBf16Tune2ctaTma, kBf16Tune512s4, kBf16Tune512Direct,
+#endif
+  kNumBf16Configs
+};
 
 static const Bf16ConfigEntry kBf16Configs[] = {
     GEMM_B200_BF16_ENTRY("1cta_128x256x64_s4_direct", Bf16_1cta_direct),
     GEMM_B200_BF16_ENTRY("1cta_128x256x64_s4_tmastore", Bf16_1cta_tma),
-    GEMM_B200_BF16_ENTRY("2cta_256x256x64_s6_direct", Bf16_2cta_direct),
-    GEMM_B200_BF16_ENTRY("2cta_256x256x64_s6_tmastore", Bf16_2cta_tma),
     GEMM_B200_BF16_ENTRY("2cta_256x256x64_s6_tmastore_maskcommit", Bf16_2cta_tma_m),
-    GEMM_B200_BF16_ENTRY("2cta_256x512x64_s4_tmastore_maskcommit", Bf16_2cta_n512),
-    GEMM_B200_BF16_ENTRY("2cta_256x512x64_s4_direct_maskcommit", Bf16_2cta_n512_d),
     GEMM_B200_BF16_ENTRY("2cta_256x512x64_s3_tmastore2_maskcommit", Bf16_2cta_n512_s3),
     GEMM_B200_BF16_ENTRY("2cta_256x128x64_s7_tmastore_maskcommit", Bf16_2cta_n128),
     GEMM_B200_BF16_ENTRY("1cta_128x128x64_s6_tmastore", Bf16_1cta_n128),
+#ifdef GEMM_B200_TUNING
+    GEMM_B200_BF16_ENTRY("2cta_256x256x64_s6_direct", Bf16_2cta_direct),
+    GEMM_B200_BF16_ENTRY("2cta_256x256x64_s6_tmastore", Bf16_2cta_tma),
+    GEMM_B200_BF16_ENTRY("2cta_256x512x64_s4_tmastore_maskcommit", Bf16_2cta_n512),
+    GEMM_B200_BF16_ENTRY("2cta_256x512x64_s4_direct_maskcommit", Bf16_2cta_n512_d),
+#endif
 };
-constexpr int kNumBf16Configs = sizeof(kBf16Configs) / sizeof(kBf16Configs[0]);
-constexpr int kBf16Cfg1cta = 1;   // single CTA, 128x256 tiles, TMA store
-constexpr int kBf16Cfg256 = 4;    // CTA pair, 256x256 tiles, double-buffered accumulator
-constexpr int kBf16Cfg512 = 7;    // CTA pair, 256x512 tiles (A shared by two accumulators)
-constexpr int kBf16Cfg2ctaN128 = 8;   // CTA pair, 256x128 tiles: at most half a round of 256-wide tiles
-constexpr int kBf16Cfg1ctaN128 = 9;   // single CTA, 128x128 tiles: one row tile and few column tiles
+static_assert(sizeof(kBf16Configs) / sizeof(kBf16Configs[0]) == kNumBf16Configs, "table and enum out of step");
 
 // 256x512 tiles move 25 % fewer operand bytes per flop and measure ~4 % faster when both tile
 // shapes fill their rounds equally well; with few tiles the coarser grid wastes more of the last
@@ -524,7 +565,7 @@ static int bf16_entry(const void* A, const void* B, void* C, int64_t batch, int6
       if (ws) {
         if (log_enabled())
           fprintf(stderr, "[gemm_b200] gemm_bf16 %lldx%lldx%lld -> %s, %d K splits\n", (long long)M, (long long)K,
-                  (long long)N, kBf16Configs[0].name, splits);
+                  (long long)N, kBf16Configs[kBf16Cfg1ctaDirect].name, splits);
         return launch_bf16_splitk(args, b_layout, out_dtype, splits, ws);
       }
     }
@@ -705,27 +746,38 @@ struct MxConfigEntry {
   int (*launch[2])(const MxArgs&);   // [out_dtype]
 };
 using Mx_1cta = MxCfg<1, 4, false>;
-using Mx_2cta = MxCfg<2, 6, false>;
-using Mx_2cta_m = MxCfg<2, 6, true>;
 using Mx_2cta_m_tma = MxCfg<2, 5, true, 1>;
 using Mx_1cta_a32 = MxCfg<1, 5, false, 0, 32>;   // M <= 32: 4 KB of A per stage, 5 stages of B in flight
 using Mx_2cta_n128 = MxCfg<2, 7, true, 1, kBlockM, 128>;   // 256 x 128 tiles for one-round problems
 using Mx_1cta_n128 = MxCfg<1, 6, false, 0, kBlockM, 128>;   // 128 x 128 tiles: 32 < M <= 128 with few column tiles
+#ifdef GEMM_B200_TUNING
+using Mx_2cta = MxCfg<2, 6, false>;
+using Mx_2cta_m = MxCfg<2, 6, true>;
+#endif
+// index of every variant in kMxConfigs (the order of the table below)
+enum MxConfigId : int {
+  kSkinnyMxConfig = 0,   // single CTA, 128 x 256 tiles: 33..128 rows, and the split-K partial sums
+  kDefaultMxConfig,      // CTA pair, masked commit, TMA-store epilogue
+  kNarrowMxConfig,       // M <= 32: single CTA with 32-row A stages and a deeper B pipeline
+  kN128MxConfig,         // CTA pair, 256 x 128 tiles: at most half a round of 256-wide tiles
+  k1ctaN128MxConfig,     // single CTA, 128 x 128 tiles
+#ifdef GEMM_B200_TUNING
+  kMxTune2cta, kMxTune2ctaMask,
+#endif
+  kNumMxConfigs
+};
 static const MxConfigEntry kMxConfigs[] = {
     {"1cta_128x256x128_s4", {launch_mxfp8<Mx_1cta, 0>, launch_mxfp8<Mx_1cta, 1>}},
-    {"2cta_256x256x128_s6", {launch_mxfp8<Mx_2cta, 0>, launch_mxfp8<Mx_2cta, 1>}},
-    {"2cta_256x256x128_s6_maskcommit", {launch_mxfp8<Mx_2cta_m, 0>, launch_mxfp8<Mx_2cta_m, 1>}},
     {"2cta_256x256x128_s5_maskcommit_tmastore", {launch_mxfp8<Mx_2cta_m_tma, 0>, launch_mxfp8<Mx_2cta_m_tma, 1>}},
     {"1cta_32x256x128_s5_narrowA", {launch_mxfp8<Mx_1cta_a32, 0>, launch_mxfp8<Mx_1cta_a32, 1>}},
     {"2cta_256x128x128_s7_maskcommit_tmastore", {launch_mxfp8<Mx_2cta_n128, 0>, launch_mxfp8<Mx_2cta_n128, 1>}},
     {"1cta_128x128x128_s6", {launch_mxfp8<Mx_1cta_n128, 0>, launch_mxfp8<Mx_1cta_n128, 1>}},
+#ifdef GEMM_B200_TUNING
+    {"2cta_256x256x128_s6", {launch_mxfp8<Mx_2cta, 0>, launch_mxfp8<Mx_2cta, 1>}},
+    {"2cta_256x256x128_s6_maskcommit", {launch_mxfp8<Mx_2cta_m, 0>, launch_mxfp8<Mx_2cta_m, 1>}},
+#endif
 };
-constexpr int kNumMxConfigs = sizeof(kMxConfigs) / sizeof(kMxConfigs[0]);
-constexpr int kDefaultMxConfig = 3;      // CTA pair, masked commit, TMA-store epilogue
-constexpr int kSkinnyMxConfig = 0;       // M <= 128: single-CTA tiles give more independent column tiles
-constexpr int kNarrowMxConfig = 4;       // M <= 32: the same with 32-row A stages and a deeper B pipeline
-constexpr int kN128MxConfig = 5;         // CTA pair, 256 x 128 tiles: problems of at most half a round of 256-wide tiles
-constexpr int k1ctaN128MxConfig = 6;     // single CTA, 128 x 128 tiles
+static_assert(sizeof(kMxConfigs) / sizeof(kMxConfigs[0]) == kNumMxConfigs, "table and enum out of step");
 
 }  // namespace tc
 }  // namespace gemm_b200
@@ -960,14 +1012,24 @@ static __device__ __align__(256) float g_static_scratch[GEMM_B200_STATIC_SCRATCH
 static std::mutex g_static_mu;
 static float* g_static_ptr[64] = {nullptr};
 
+// First call on a device: besides the address look-up, load every kernel this entry point can
+// launch (the split-K GEMM, the unsplit single-CTA GEMM for k_splits == 1, both reduce kernels) and
+// opt them in to their shared-memory size, so that no later call on that device loads code,
+// whichever output type it asks for.
 static int static_scratch_for_current_device(float** out) {
-  int dev = 0;
-  GEMM_B200_CUDA_TRY(cudaGetDevice(&dev));
+  DeviceInfo di;
+  if (int rc = device_info(&di)) return rc;
   std::lock_guard<std::mutex> lk(g_static_mu);
-  const int slot = dev & 63;
+  const int slot = di.dev & 63;
   if (!g_static_ptr[slot]) {
     void* p = nullptr;
     GEMM_B200_CUDA_TRY(cudaGetSymbolAddress(&p, g_static_scratch));
+    int clusters = 0;
+    if (int rc = persistent_clusters(gemm_mxfp8_kernel<Mx_1cta, 0>, 1, kMxThreads, Mx_1cta::SMEM_BYTES, di, &clusters)) return rc;
+    if (int rc = persistent_clusters(gemm_mxfp8_kernel<Mx_1cta, 1>, 1, kMxThreads, Mx_1cta::SMEM_BYTES, di, &clusters)) return rc;
+    cudaFuncAttributes fa;
+    GEMM_B200_CUDA_TRY(cudaFuncGetAttributes(&fa, splitk_reduce_kernel<true>));
+    GEMM_B200_CUDA_TRY(cudaFuncGetAttributes(&fa, splitk_reduce_kernel<false>));
     g_static_ptr[slot] = static_cast<float*>(p);
   }
   *out = g_static_ptr[slot];
@@ -982,9 +1044,17 @@ extern "C" int gemm_b200_gemm_mxfp8_splitk_static(const void* Aq, const void* SF
                                                   int k_splits, void* stream) {
   using namespace gemm_b200;
   if (M < 0 || N < 0 || K < 0) return fail(GEMM_B200_ERR_INVALID_ARG, "gemm_mxfp8_splitk_static: negative size");
+  if (M > 0x7fffffff || N > 0x7fffffff || K > 0x7fffffff)
+    return fail(GEMM_B200_ERR_TOO_LARGE, "gemm_mxfp8_splitk_static: a dimension exceeds 2^31-1");
   if (k_splits > 64) return fail(GEMM_B200_ERR_INVALID_ARG, "gemm_mxfp8_splitk_static: k_splits %d above 64", k_splits);
-  if (k_splits <= 0) k_splits = gemm_b200_gemm_mxfp8_auto_splits(M, N, K);
-  const size_t need = gemm_b200_gemm_mxfp8_splitk_scratch_bytes(M, N, k_splits);
+  if (k_splits <= 0) {
+    // the library's own choice; the split path stores 8 columns at a time, other widths run unsplit
+    k_splits = (N % 8 == 0) ? gemm_b200_gemm_mxfp8_auto_splits(M, N, K) : 1;
+    // a choice that does not fit the built-in array is reduced until it does
+    while (k_splits > 1 && gemm_b200_gemm_mxfp8_splitk_scratch_bytes(M, N, k_splits) > (size_t)GEMM_B200_STATIC_SCRATCH_BYTES)
+      --k_splits;
+  }
+  const size_t need = gemm_b200_gemm_mxfp8_splitk_scratch_bytes(M, N, k_splits);   // M, N < 2^31, k_splits <= 64: no overflow
   if (need > (size_t)GEMM_B200_STATIC_SCRATCH_BYTES)
     return fail(GEMM_B200_ERR_TOO_LARGE,
                 "gemm_mxfp8_splitk_static: %d splits of a %lld x %lld result need %zu bytes of scratch, the built-in "
@@ -1022,94 +1092,6 @@ __global__ void __launch_bounds__(32) wait_timeout_selftest_kernel(unsigned long
 
 }  // namespace tc
 }  // namespace gemm_b200
-
-// ---------------------------------------------------------------------------------------
-// TMA streaming probe: the time a grid needs just to pull a [rows, cols] byte matrix through
-// TMA into shared memory, tiled the way the skinny GEMMs stream their B operand.  It is the
-// floor a bandwidth-bound GEMM call can be held against (same launch, same cold caches).
-// ---------------------------------------------------------------------------------------
-namespace gemm_b200 {
-namespace tc {
-
-// Every CTA streams `rows_per_cta` rows: in passes of ROWS rows, SEG adjacent 128-byte column
-// segments per stage.  One producer warp, one consumer warp that only frees the stage.
-template <int ROWS, int SEG, int STAGES>
-__global__ void __launch_bounds__(64, 1)
-tma_stream_probe_kernel(const __grid_constant__ CUtensorMap tm, int cols, int rows_per_cta) {
-  extern __shared__ uint8_t smem_raw[];
-  const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
-  constexpr int STAGE_BYTES = ROWS * 128 * SEG;
-  const uint32_t bar0 = base + STAGES * STAGE_BYTES;
-  auto full = [&](int s) { return bar0 + 8u * s; };
-  auto empty = [&](int s) { return bar0 + 8u * (STAGES + s); };
-  if (threadIdx.x == 0) {
-    for (int s = 0; s < STAGES; ++s) {
-      mbar_init(full(s), 1);
-      mbar_init(empty(s), 1);
-    }
-    fence_mbar_init();
-  }
-  __syncthreads();
-  const int row0 = blockIdx.x * rows_per_cta, passes = rows_per_cta / ROWS, ksteps = cols / (128 * SEG);
-  const bool issuer = elect_one();
-  uint32_t it = 0;
-  for (int p = 0; p < passes; ++p) {
-    for (int ks = 0; ks < ksteps; ++ks, ++it) {
-      const int s = it % STAGES;
-      const uint32_t ph = (it / STAGES) & 1u;
-      if (threadIdx.x < 32) {
-        if (!mbar_wait_warp(empty(s), ph ^ 1u, kRoleProducer, s)) return;
-        if (issuer) {
-          mbar_arrive_expect_tx(full(s), STAGE_BYTES);
-#pragma unroll
-          for (int g = 0; g < SEG; ++g)
-            tma_load_2d(base + s * STAGE_BYTES + g * ROWS * 128, &tm, (ks * SEG + g) * 128, row0 + p * ROWS, full(s));
-        }
-      } else {
-        if (!mbar_wait_warp(full(s), ph, kRoleMma, s)) return;
-        if (issuer) mbar_arrive(empty(s));
-      }
-      __syncwarp();
-    }
-  }
-}
-
-template <int ROWS, int SEG, int STAGES>
-static int launch_stream_probe(const void* X, int64_t rows, int64_t cols, int64_t rows_per_cta, cudaStream_t st) {
-  if (rows % rows_per_cta != 0 || rows_per_cta % ROWS != 0 || cols % (128 * SEG) != 0)
-    return fail(GEMM_B200_ERR_INVALID_ARG, "tma_stream_probe: rows %% rows_per_cta, rows_per_cta %% %d and cols %% %d must be 0",
-                ROWS, 128 * SEG);
-  CUtensorMap tm;
-  if (int rc = make_map_2d(&tm, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, X, rows, cols, cols, 128, ROWS, CU_TENSOR_MAP_SWIZZLE_128B))
-    return rc;
-  auto kern = tma_stream_probe_kernel<ROWS, SEG, STAGES>;
-  constexpr int smem = 1024 + STAGES * ROWS * 128 * SEG + 2 * STAGES * 8 + 64;
-  GEMM_B200_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-  kern<<<(unsigned)(rows / rows_per_cta), 64, smem, st>>>(tm, (int)cols, (int)rows_per_cta);
-  launch_counter().fetch_add(1, std::memory_order_relaxed);
-  GEMM_B200_CUDA_TRY(cudaGetLastError());
-  return GEMM_B200_OK;
-}
-
-}  // namespace tc
-}  // namespace gemm_b200
-
-extern "C" int gemm_b200_selftest_tma_stream(const void* X, int64_t rows, int64_t cols, int64_t rows_per_cta, int pattern,
-                                             void* stream) {
-  using namespace gemm_b200;
-  if (!X || rows <= 0 || cols <= 0 || rows_per_cta <= 0 || rows > 0x7fffffff || cols > 0x7fffffff)
-    return fail(GEMM_B200_ERR_INVALID_ARG, "tma_stream_probe: bad arguments");
-  if (reinterpret_cast<uintptr_t>(X) % 16 != 0 || cols % 16 != 0)
-    return fail(GEMM_B200_ERR_ALIGNMENT, "tma_stream_probe: X and cols must be 16-byte aligned");
-  cudaStream_t st = static_cast<cudaStream_t>(stream);
-  switch (pattern) {
-    case 0: return tc::launch_stream_probe<256, 1, 4>(X, rows, cols, rows_per_cta, st);
-    case 1: return tc::launch_stream_probe<256, 1, 6>(X, rows, cols, rows_per_cta, st);
-    case 2: return tc::launch_stream_probe<64, 4, 6>(X, rows, cols, rows_per_cta, st);
-    case 3: return tc::launch_stream_probe<32, 8, 6>(X, rows, cols, rows_per_cta, st);
-    default: return fail(GEMM_B200_ERR_INVALID_ARG, "tma_stream_probe: pattern %d (0..3)", pattern);
-  }
-}
 
 extern "C" int gemm_b200_selftest_wait_timeout(int64_t limit_us, int* device_flag, void* stream) {
   using namespace gemm_b200;

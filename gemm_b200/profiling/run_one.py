@@ -1,8 +1,8 @@
 """Runs one operator of the library a few times on seeded synthetic inputs:
 
-    python -m gemm_b200.run_one {f32|bf16|mxfp8} [--m M --k K --n N] [--config C] [--reps R]
+    python -m gemm_b200.profiling.run_one {f32|bf16|mxfp8} [--m M --k K --n N] [--config C] [--reps R]
 
-Meant as the target of a profiler (`ncu ... python -m gemm_b200.run_one bf16 --m 8192 ...`) or
+Meant as the target of a profiler (`ncu ... python -m gemm_b200.profiling.run_one bf16 --m 8192 ...`) or
 for a quick timing; prints the median device time and TFLOP/s of the launches."""
 from __future__ import annotations
 
@@ -12,7 +12,7 @@ import sys
 
 import torch
 
-from . import ops
+from .. import ops
 
 
 def main(argv=None) -> int:

@@ -1,6 +1,6 @@
 """Runs the MXFP8 quantiser a few times on a seeded synthetic matrix (profiler target / quick timing):
 
-    python -m gemm_b200.run_quant [--rows R --k K] [--transposed] [--reps N]
+    python -m gemm_b200.profiling.run_quant [--rows R --k K] [--transposed] [--reps N]
 """
 from __future__ import annotations
 
@@ -10,7 +10,7 @@ import sys
 
 import torch
 
-from . import ops
+from .. import ops
 
 
 def main(argv=None) -> int:

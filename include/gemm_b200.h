@@ -96,10 +96,14 @@ const char* gemm_b200_gemm_bf16_config_name(int config);
  * ([k_splits][M][N] floats, device memory, 16-byte aligned, at least
  * gemm_b200_gemm_bf16_splitk_scratch_bytes() bytes) and are then summed in ascending split order
  * into C by a second kernel.  k_splits == 1 runs the plain kernel and never splits.
- * gemm_b200_gemm_bf16() takes the split path by itself, on a library-owned scratch buffer, with
- * the count of gemm_b200_gemm_bf16_auto_splits() (1 = it does not split; it also stays unsplit
- * when the buffer would have to grow during stream capture).  N % 4 == 0.  The reference always
- * walks K inside one thread (naive/naive_1.cu:9-12); it has no counterpart. */
+ * gemm_b200_gemm_bf16() takes the split path by itself with the count of
+ * gemm_b200_gemm_bf16_auto_splits() (1 = it does not split), on scratch the library owns: one
+ * buffer per (device, stream), so calls on different streams may overlap and calls on one stream
+ * are ordered anyway.  The first split call on a stream, and a later one that needs a larger
+ * buffer, allocate (cudaMalloc; growing also frees, which waits for the device); during stream
+ * capture such a call runs unsplit instead.  The library keeps buffers for the 32 most recently
+ * used streams.  N % 4 == 0.  The reference always walks K inside one thread
+ * (naive/naive_1.cu:9-12); it has no counterpart. */
 int gemm_b200_gemm_bf16_splitk(const void* A, const void* B, void* C,
                                int64_t M, int64_t N, int64_t K,
                                int64_t lda, int64_t ldb, int64_t ldc,
@@ -163,8 +167,9 @@ int gemm_b200_gemm_mxfp8_quant_out(const void* Aq, const void* SFA, const void* 
  * ranges of K whose FP32 partial sums go to `scratch` ([k_splits][M][N] floats, device memory,
  * 16-byte aligned, at least gemm_b200_gemm_mxfp8_splitk_scratch_bytes() bytes) and are then
  * summed in ascending split order into C by a second kernel.  gemm_b200_gemm_mxfp8() takes this
- * path by itself for M <= 128, with a library-owned scratch buffer and the split count of
- * gemm_b200_gemm_mxfp8_auto_splits().  No counterpart in the reference. */
+ * path by itself for M <= 128 (and for a handful of tiles with K >= 16384) with the split count
+ * of gemm_b200_gemm_mxfp8_auto_splits(), on library-owned scratch kept per (device, stream) under
+ * the rules given for gemm_b200_gemm_bf16_splitk above.  No counterpart in the reference. */
 int gemm_b200_gemm_mxfp8_splitk(const void* Aq, const void* SFA, const void* Bq, const void* SFB,
                                 void* C, int64_t M, int64_t N, int64_t K, int64_t ldc, int out_dtype,
                                 int k_splits, void* scratch, size_t scratch_bytes, void* stream);
@@ -176,11 +181,14 @@ size_t gemm_b200_gemm_mxfp8_splitk_scratch_bytes(int64_t M, int64_t N, int k_spl
  * inside its execute callback.  It has no counterpart in the reference.
  *   - The FP32 partial sums go to a GEMM_B200_STATIC_SCRATCH_BYTES array built into the library's
  *     device image; every GPU that loads the library holds that much until the process exits.
- *   - Limit: k_splits * M * N * 4 bytes must fit (k_splits <= 0 picks the library's split count);
- *     larger problems get GEMM_B200_ERR_TOO_LARGE and should use gemm_b200_gemm_mxfp8_splitk.
+ *   - Limit: k_splits * M * N * 4 bytes must fit; larger problems get GEMM_B200_ERR_TOO_LARGE and
+ *     should use gemm_b200_gemm_mxfp8_splitk.  k_splits <= 0 picks the library's split count,
+ *     lowered as far as needed to fit (down to 1 = unsplit, which needs no scratch).
  *   - The call performs no cudaMalloc / cudaFree and calls no allocating library routine.
- *   - The first call on each device looks the array's device address up; make that first call
- *     before starting any stream capture on that device.
+ *   - The first call on each device does the one-time set-up: it looks the array's device address
+ *     up and loads every kernel the entry point can launch (both output types), so later calls on
+ *     that device load nothing.  Make that first call before starting any stream capture on that
+ *     device and outside the region where allocation is forbidden (loading code takes memory).
  *   - All calls on a device share the one array, which keeps whatever the last call left there
  *     (nothing in it has to start at zero: every value read is written by the same call first).
  *     Two calls whose kernels can overlap on the GPU (different streams) race on it; keep them on
@@ -212,18 +220,13 @@ int gemm_b200_release_workspace(void);
  * ------------------------------------------------------------------------- */
 /* Reads (and clears) the device-side status word that bounded waits write when
  * they give up.  Synchronises `stream`.  0 = clean, GEMM_B200_ERR_TIMEOUT
- * otherwise; `detail`, if not NULL, receives {code, block, role, stage}. */
+ * otherwise; `detail`, if not NULL, receives {code, block, role, stage}.
+ * The word is per device and sticky: once a wait has given up, every later
+ * tensor-core kernel on that device skips its work (its C is garbage) while the
+ * launching calls keep returning GEMM_B200_OK, until this function has been
+ * called.  Call it wherever a result is consumed.  The host-buffer entry points
+ * call it themselves before returning. */
 int gemm_b200_check_status(void* stream, int32_t detail[4]);
-/* Bandwidth probe: one launch that only streams the byte matrix X[rows, cols]
- * through TMA into shared memory (no tensor-core work, no output), every CTA
- * taking rows_per_cta rows.  pattern 0: 256-row x 128-byte boxes, 4 stages (the
- * skinny GEMMs' B stream); 1: the same with 6 stages; 2: 64 rows x 512 bytes;
- * 3: 32 rows x 1024 bytes.  Time it like a GEMM call to get the floor of a
- * bandwidth-bound call.  rows % rows_per_cta == 0, rows_per_cta a multiple of the
- * pattern's rows, cols a multiple of the pattern's bytes per row. */
-int gemm_b200_selftest_tma_stream(const void* X, int64_t rows, int64_t cols, int64_t rows_per_cta,
-                                  int pattern, void* stream);
-
 /* Self-test of the bounded-wait machinery: launches one warp that waits `limit_us` microseconds
  * (1 .. 100000) on a barrier nothing arrives on, then records the give-up in the status word and
  * returns normally (writing 1 to *device_flag, an int in device memory).  A following

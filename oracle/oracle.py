@@ -151,6 +151,18 @@ def reference_kernel(variant: str):
     return call
 
 
+def reference_launcher(variant: str):
+    """The same launcher without the synchronisation around it, for timing with events recorded on
+    the legacy default stream (where the reference launches, naive/naive_1.cu:23): f(A, B, C)."""
+    reference_kernel(variant)
+    fn = _REF_CACHE[variant]
+
+    def launch(A: torch.Tensor, B: torch.Tensor, Cout: torch.Tensor) -> None:
+        fn(A.data_ptr(), B.data_ptr(), Cout.data_ptr(), A.shape[0], B.shape[1], A.shape[1])   # (M, N, K)
+
+    return launch
+
+
 # --------------------------------------------------------------------------------------
 # error metrics
 # --------------------------------------------------------------------------------------

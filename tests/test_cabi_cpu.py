@@ -34,7 +34,7 @@ def test_version_and_config_tables():
     from gemm_b200 import _lib
     assert _lib.lib.gemm_b200_version() == 100
     import gemm_b200.ops as ops
-    assert len(ops.sgemm_f32_configs()) >= 4 and all(ops.sgemm_f32_configs())
+    assert len(ops.sgemm_f32_configs()) >= 3 and all(ops.sgemm_f32_configs())
     assert len(ops.gemm_bf16_configs()) >= 2
     assert len(ops.gemm_mxfp8_configs()) >= 2
     assert _lib.lib.gemm_b200_sgemm_f32_config_name(999) == b""

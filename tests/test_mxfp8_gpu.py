@@ -198,7 +198,7 @@ def test_quantising_epilogue_equals_gemm_then_quantise(ops, oracle, M, K, N):
     Aq = ops.quantize_mxfp8(A.cuda()); Bq = ops.quantize_mxfp8(B.cuda(), transposed_in=True)
     fused = ops.gemm_mxfp8_quant_out(Aq, Bq)
     ops.check_status()
-    C16 = ops.gemm_mxfp8(Aq, Bq, out_dtype=torch.bfloat16, config=(0 if M <= 128 else 2))
+    C16 = ops.gemm_mxfp8(Aq, Bq, out_dtype=torch.bfloat16, config=(0 if M <= 128 else ops.gemm_mxfp8_configs().index("2cta_256x256x128_s5_maskcommit_tmastore")))
     unfused = ops.quantize_mxfp8(C16)
     assert torch.equal(fused.data, unfused.data)
     assert torch.equal(fused.scales, unfused.scales)                    # packed buffers, padding included
@@ -233,7 +233,7 @@ def test_half_round_problems_take_the_128_column_tiles(ops, oracle, M, K, N):
     Aq = ops.quantize_mxfp8(A.cuda())
     Bq = ops.quantize_mxfp8(B.cuda(), transposed_in=True)
     auto = ops.gemm_mxfp8(Aq, Bq, out_dtype=torch.float32)
-    wide = ops.gemm_mxfp8(Aq, Bq, out_dtype=torch.float32, config=3)
+    wide = ops.gemm_mxfp8(Aq, Bq, out_dtype=torch.float32, config=ops.gemm_mxfp8_configs().index("2cta_256x256x128_s5_maskcommit_tmastore"))
     ops.check_status()
     assert torch.equal(auto, wide)
     _gemm_check(ops, oracle, M, K, N, config=ops.gemm_mxfp8_configs().index("2cta_256x128x128_s7_maskcommit_tmastore"), seed=1)
@@ -247,7 +247,7 @@ def test_handful_of_tiles_and_long_k_splits_by_itself(ops, oracle):
     Aq = ops.quantize_mxfp8(A.cuda())
     Bq = ops.quantize_mxfp8(B.cuda(), transposed_in=True)
     auto = ops.gemm_mxfp8(Aq, Bq, out_dtype=torch.float32)
-    unsplit = ops.gemm_mxfp8(Aq, Bq, out_dtype=torch.float32, config=3)
+    unsplit = ops.gemm_mxfp8(Aq, Bq, out_dtype=torch.float32, config=ops.gemm_mxfp8_configs().index("2cta_256x256x128_s5_maskcommit_tmastore"))
     ops.check_status()
     assert oracle.rel_frobenius(auto.cpu(), unsplit.cpu()) <= 1e-5
     qa, sa = oracle.mxfp8_quantize(A)

@@ -184,4 +184,4 @@ def test_log_and_forced_config_knobs(oracle):
     env = dict(os.environ, GEMM_B200_LOG="1", GEMM_B200_F32_CONFIG="0")
     r = subprocess.run([sys.executable, "-c", code], env=env, capture_output=True, text=True, cwd=str(__import__("pathlib").Path(__file__).resolve().parent.parent))
     assert r.returncode == 0, r.stderr
-    assert "[gemm_b200] sgemm_f32 256x64x256 -> 128x128x16_s3" in r.stderr
+    assert "[gemm_b200] sgemm_f32 256x64x256 -> 64x128x32_s3_f32x2" in r.stderr

@@ -36,14 +36,16 @@ def test_selftest_argument_checks():
     assert L.lib.gemm_b200_selftest_wait_timeout(100, None, None) == L.ERR_INVALID_ARG
 
 
-def test_tma_stream_probe_runs_and_validates(ops):
-    """The bandwidth probe streams a matrix through TMA and leaves the device status clean."""
-    import gemm_b200._lib as L
+def test_tma_stream_probe_runs_and_validates():
+    """The bandwidth probe (a library of its own under gemm_b200/profiling) streams a matrix through
+    TMA, leaves its status word clean and checks its arguments."""
+    from gemm_b200.profiling.run_stream import load_probe
+    P = load_probe()
     X = torch.ones(2048, 4096, device="cuda", dtype=torch.uint8)
     st = torch.cuda.current_stream().cuda_stream
     for pattern in range(4):
-        assert L.lib.gemm_b200_selftest_tma_stream(X.data_ptr(), 2048, 4096, 256, pattern, st) == L.OK
-    ops.check_status()
-    assert L.lib.gemm_b200_selftest_tma_stream(X.data_ptr(), 2048, 4096, 256, 9, st) == L.ERR_INVALID_ARG
-    assert L.lib.gemm_b200_selftest_tma_stream(X.data_ptr(), 2048, 4096, 100, 0, st) == L.ERR_INVALID_ARG
-    assert L.lib.gemm_b200_selftest_tma_stream(0, 2048, 4096, 256, 0, st) == L.ERR_INVALID_ARG
+        assert P.gemm_b200_probe_tma_stream(X.data_ptr(), 2048, 4096, 256, pattern, st) == 0
+    assert P.gemm_b200_probe_check_status(st) == 0
+    assert P.gemm_b200_probe_tma_stream(X.data_ptr(), 2048, 4096, 256, 9, st) == -1
+    assert P.gemm_b200_probe_tma_stream(X.data_ptr(), 2048, 4096, 100, 0, st) == -1
+    assert P.gemm_b200_probe_tma_stream(0, 2048, 4096, 256, 0, st) == -1

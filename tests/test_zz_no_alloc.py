@@ -79,3 +79,53 @@ def test_static_scratch_rejects_what_does_not_fit(ops):
     assert rc == L.ERR_TOO_LARGE
     assert "scratch" in L.last_error() and str(STATIC_BYTES) in L.last_error()
     assert L.lib.gemm_b200_gemm_mxfp8_splitk_scratch_bytes(M, N, 8) > STATIC_BYTES
+
+
+def test_static_scratch_second_output_type_loads_nothing(ops):
+    """The first call on a device sets up both output types: after a bf16 call, an f32 call (and an
+    unsplit one) must not take device memory either."""
+    import gemm_b200._lib as L
+    M, K, N = 32, 2048, 512
+    Aq, Bq = _operands(ops, M, K, N, seed=9)
+    out16 = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
+    out32 = torch.empty(M, N, device="cuda", dtype=torch.float32)
+    assert _call_static(L, Aq, Bq, out16, 4) == 0, L.last_error()
+    torch.cuda.synchronize()
+    free0, _ = torch.cuda.mem_get_info()
+    assert _call_static(L, Aq, Bq, out32, 4) == 0, L.last_error()
+    assert _call_static(L, Aq, Bq, out32, 1) == 0, L.last_error()
+    assert _call_static(L, Aq, Bq, out16, 1) == 0, L.last_error()
+    torch.cuda.synchronize()
+    free1, _ = torch.cuda.mem_get_info()
+    assert free1 == free0
+    ops.check_status()
+    assert torch.equal(out32, ops.gemm_mxfp8(Aq, Bq, out_dtype=torch.float32, config=0))
+
+
+def test_static_scratch_auto_splits_edge_cases(ops):
+    import gemm_b200._lib as L
+    # N % 8 != 0 with f32 output: the library's own choice falls back to the unsplit kernel
+    M, K, N = 16, 4096, 2052
+    Aq, Bq = _operands(ops, M, K, N, seed=4)
+    out = torch.empty(M, N, device="cuda", dtype=torch.float32)
+    assert _call_static(L, Aq, Bq, out, 0) == 0, L.last_error()
+    ops.check_status()
+    assert torch.equal(out, ops.gemm_mxfp8(Aq, Bq, out_dtype=torch.float32, config=0))
+    # dimensions beyond 2^31 - 1 are refused before any size arithmetic
+    rc = L.lib.gemm_b200_gemm_mxfp8_splitk_static(None, None, None, None, None, 1 << 40, 1 << 40, 32, 1 << 40, 0, 2, None)
+    assert rc == L.ERR_TOO_LARGE
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_static_scratch_on_a_second_device(ops):
+    """Every device has its own copy of the array; its address is looked up with that device current."""
+    import gemm_b200._lib as L
+    with torch.cuda.device(1):
+        M, K, N = 16, 4096, 1024
+        Aq, Bq = _operands(ops, M, K, N, seed=2)
+        want = ops.gemm_mxfp8_splitk(Aq, Bq, 4, out_dtype=torch.float32)
+        for _ in range(2):
+            out = torch.full((M, N), float("nan"), device="cuda", dtype=torch.float32)
+            assert _call_static(L, Aq, Bq, out, 4) == 0, L.last_error()
+            ops.check_status()
+            assert torch.equal(out, want)
