@@ -20,6 +20,7 @@ i64, i32, vp, sz = C.c_int64, C.c_int, C.c_void_p, C.c_size_t
 SIGNATURES = {
     "gemm_b200_sgemm_f32": (i32, [vp, vp, vp, i64, i64, i64, i64, i64, i64, vp]),
     "gemm_b200_sgemm_f32_cfg": (i32, [vp, vp, vp, i64, i64, i64, i64, i64, i64, i32, vp]),
+    "gemm_b200_sgemm_f32_batched": (i32, [vp, vp, vp, i64, i64, i64, i64, i64, i64, i64, i64, i64, i64, vp]),
     "gemm_b200_sgemm_f32_num_configs": (i32, []),
     "gemm_b200_sgemm_f32_config_name": (C.c_char_p, [i32]),
     "gemm_b200_gemm_bf16": (i32, [vp, vp, vp, i64, i64, i64, i64, i64, i64, i32, i32, vp]),

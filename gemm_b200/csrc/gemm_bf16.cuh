@@ -34,6 +34,72 @@ constexpr int kBlockK = 64;    // bf16 elements per 128-byte swizzled row
 constexpr int kUmmaK = 16;
 constexpr int kTmemCols = 512;
 
+// ---------------------------------------------------------------------------------------
+// Run-time hand-out of work units (used by the BF16 and the MXFP8 kernel).
+//
+// The producer warp of the leader CTA asks the hardware for the next unit one unit ahead
+// (clc_try_cancel) and, once the answer is in, publishes it to every CTA of the cluster through a
+// ring in shared memory: a 32-bit unit index (-1 = no work left) and an mbarrier per slot.  Every
+// other warp role walks the same ring.  Slot (n - 1) % kSchedSlots carries the n-th unit of the
+// cluster (n >= 1; unit 0 is the cluster's own blockIdx), in phase ((n - 1) / kSchedSlots) & 1 of
+// the slot's barriers.  No "slot free" signal is needed: the producer
+// runs at most STAGES K blocks ahead of the MMA issuer and the issuer at most two accumulators
+// ahead of the epilogue, so the slot written for unit n + 1 was last read STAGES + 3 units ago at
+// the latest, and the ring holds more slots than that.
+//   [0, 256)    kSchedSlots x 16 B  hardware answers           (used in the leader CTA)
+//   [256, 384)  kSchedSlots x 8 B   mbarriers of the answers   (used in the leader CTA)
+//   [384, 512)  kSchedSlots x 8 B   "unit published" mbarriers (every CTA)
+//   [512, 576)  kSchedSlots x 4 B   published unit index       (every CTA)
+// ---------------------------------------------------------------------------------------
+constexpr int kSchedSlots = 16;
+constexpr int kSchedBytes = 576;
+struct SchedRing {
+  uint32_t base;   // 16-byte aligned shared-memory address
+  __device__ __forceinline__ uint32_t resp(uint32_t s) const { return base + 16u * s; }
+  __device__ __forceinline__ uint32_t hw_bar(uint32_t s) const { return base + 256u + 8u * s; }
+  __device__ __forceinline__ uint32_t pub_bar(uint32_t s) const { return base + 384u + 8u * s; }
+  __device__ __forceinline__ uint32_t unit(uint32_t s) const { return base + 512u + 4u * s; }
+  __device__ __forceinline__ void init() const {   // one thread, before the CTA-wide barrier
+    for (uint32_t i = 0; i < (uint32_t)kSchedSlots; ++i) {
+      mbar_init(hw_bar(i), 1);
+      mbar_init(pub_bar(i), 1);
+    }
+  }
+  // leader CTA's producer warp, one lane: ask for the cluster's n-th unit
+  __device__ __forceinline__ void request(uint32_t n) const {
+    const uint32_t s = (n - 1) % kSchedSlots;
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // earlier reads of this slot before the new answer
+    mbar_arrive_expect_tx(hw_bar(s), 16);
+    clc_try_cancel(resp(s), hw_bar(s));
+  }
+  // leader CTA's producer warp, whole warp: wait for the answer to request(n) and hand the unit to
+  // every CTA of the cluster.  Returns the unit (-1: none left), -2 if the wait gave up.
+  template <int CG>
+  __device__ __forceinline__ int fetch_and_publish(uint32_t n, bool issuer) const {
+    const uint32_t s = (n - 1) % kSchedSlots;
+    if (!mbar_wait_warp(hw_bar(s), ((n - 1) / kSchedSlots) & 1u, kRoleProducer, 300)) return -2;
+    const int first = clc_first_cta(resp(s));
+    const int unit_idx = first < 0 ? -1 : first / CG;
+    if (issuer) {
+      st_shared_u32(unit(s), (uint32_t)unit_idx);
+      mbar_arrive(pub_bar(s));
+      if constexpr (CG == 2) {
+        st_shared_cluster_u32(map_to_cta(unit(s), 1), (uint32_t)unit_idx);
+        mbar_arrive_cluster(map_to_cta(pub_bar(s), 1));
+      }
+    }
+    __syncwarp();
+    return unit_idx;
+  }
+  // every other role: the cluster's n-th unit (n >= 1); -2 if the wait gave up
+  __device__ __forceinline__ int wait_unit(uint32_t n, int role) const {
+    const uint32_t s = (n - 1) % kSchedSlots;
+    const bool ok = mbar_wait_cluster(pub_bar(s), ((n - 1) / kSchedSlots) & 1u, role, 310);
+    if (!__all_sync(0xffffffffu, ok)) return -2;
+    return (int)ld_shared_u32(unit(s));
+  }
+};
+
 // EPI: 0 = direct global stores, 1 = swizzled smem staging + TMA store
 // COMMIT_MASK: CTA-pair commits use the masked form (one instruction for both CTAs) instead of two
 // NT: column tiles of kBlockN per work unit.
@@ -45,11 +111,15 @@ constexpr int kTmemCols = 512;
 //           is not overlapped; 8 epilogue warps keep that short.
 // BN: columns of C per MMA / accumulator (256, or 128 for problems whose 256-column tiles would
 //     leave most of the SMs without work).
+// DYN: work units are handed out at run time instead of the static unit = cluster + i * clusters:
+//     the grid has one cluster per unit, the clusters that get to run first keep running and adopt
+//     the units of clusters that have not started (cluster launch control), so the units in flight
+//     are always a contiguous window of the raster however far the clusters drift apart in time.
 template <int CG_, int STAGES_, int EPI_, bool COMMIT_MASK_, int NT_ = 1, int EPI_BUFS_ = (NT_ == 1 ? 2 : 1),
-          int BN_ = kBlockN>
+          int BN_ = kBlockN, bool DYN_ = false>
 struct Bf16Cfg {
   static constexpr int CG = CG_, STAGES = STAGES_, EPI = EPI_, NT = NT_, BN = BN_;
-  static constexpr bool COMMIT_MASK = COMMIT_MASK_;
+  static constexpr bool COMMIT_MASK = COMMIT_MASK_, DYN = DYN_;
   static constexpr int ACC_STAGES = (NT == 1) ? 2 : 1;
   static constexpr int EPI_WARPS = 4 * NT;
   static constexpr int THREADS = 64 + 32 * EPI_WARPS;
@@ -61,8 +131,9 @@ struct Bf16Cfg {
   static constexpr int STAGE_BYTES = A_BYTES + NT * B_BYTES;
   static constexpr int EPI_WARP_BUF = 32 * 128;                     // 32 rows x 128 bytes
   static constexpr int EPI_BYTES = EPI_WARPS * EPI_BUFS * EPI_WARP_BUF;
-  static constexpr int BAR_BYTES = (2 * STAGES + 4) * 8 + 16;
+  static constexpr int BAR_BYTES = (2 * STAGES + 4) * 8 + 16 + (DYN ? kSchedBytes : 0);
   static constexpr int SMEM_BYTES = 1024 + STAGES * STAGE_BYTES + EPI_BYTES + BAR_BYTES;
+  static_assert(STAGES + 5 <= kSchedSlots, "the unit ring must outlast the producer's lead over the epilogue");
   static_assert(NT == 1 || NT == 2, "column tiles per unit");
   static_assert(BN == 256 || (BN == 128 && NT == 1), "tile width");
   static_assert(SMEM_BYTES <= 232448, "shared memory budget");
@@ -85,6 +156,9 @@ struct GemmShape {
   // problems share one (batch stride 0).  c_batch_stride: elements between the C matrices.
   int batch, a_z, b_z;
   int64_t c_batch_stride;
+  // L2 eviction priority of the operand loads (BF16 kernel): bit 0 = A tiles evict-first, bit 1 = B
+  // tiles evict-last, bit 2 = A evict-last, bit 3 = B evict-first; 0 = no hint
+  int l2_hint;
 };
 
 __device__ __forceinline__ void tile_coord(int t, const GemmShape& sh, int& tm, int& tn) {
@@ -122,6 +196,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   auto tfull_bar = [&](int a) { return bar0 + 8u * (2 * STAGES + a); };
   auto tempty_bar = [&](int a) { return bar0 + 8u * (2 * STAGES + 2 + a); };
   const uint32_t tmem_slot = bar0 + 8u * (2 * STAGES + 4);
+  const SchedRing ring{bar0 + 8u * (2 * STAGES + 4) + 16u};   // only with Cfg::DYN
+  constexpr bool DYN = Cfg::DYN;
 
   const int warp = __shfl_sync(0xffffffffu, (int)(threadIdx.x >> 5), 0);
   const int lane = threadIdx.x & 31;
@@ -150,6 +226,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       mbar_init(tfull_bar(a), 1);
       mbar_init(tempty_bar(a), Cfg::EPI_WARPS * CG);   // one arrival per epilogue warp of every CTA of the pair
     }
+    if constexpr (DYN) ring.init();
     fence_mbar_init();
   }
   if (warp == 0 && lane == 0) {
@@ -180,18 +257,32 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     // The whole warp walks the schedule (coordinates and addresses stay warp-uniform); one
     // elected lane issues the copies.
     const bool issuer = elect_one();
-    auto load = [&](uint32_t dst, const CUtensorMap* map, int x, int y, int z, uint32_t bar) {
-      if constexpr (CG == 1) tma_load_3d(dst, map, x, y, z, bar);
-      else tma_load_3d_pair(dst, map, x, y, z, bar);
+    const uint64_t pol_a = (shape.l2_hint & 1) ? l2_policy_evict_first() : (shape.l2_hint & 4) ? l2_policy_evict_last() : 0ull;
+    const uint64_t pol_b = (shape.l2_hint & 2) ? l2_policy_evict_last() : (shape.l2_hint & 8) ? l2_policy_evict_first() : 0ull;
+    auto load_p = [&](uint32_t dst, const CUtensorMap* map, int x, int y, int z, uint32_t bar, uint64_t pol) {
+      if (pol != 0ull) {
+        if constexpr (CG == 1) tma_load_3d_hint(dst, map, x, y, z, bar, pol);
+        else tma_load_3d_pair_hint(dst, map, x, y, z, bar, pol);
+      } else {
+        if constexpr (CG == 1) tma_load_3d(dst, map, x, y, z, bar);
+        else tma_load_3d_pair(dst, map, x, y, z, bar);
+      }
     };
-    uint32_t it = 0;
-    for (int u = cluster_id; u < num_tiles && !failed; u += num_clusters) {
+    auto load = [&](uint32_t dst, const CUtensorMap* map, int x, int y, int z, uint32_t bar) {
+      load_p(dst, map, x, y, z, bar, pol_b);
+    };
+    uint32_t it = 0, n = 0;   // n: how many units this cluster has started
+    int u = cluster_id;
+    while (u >= 0 && u < num_tiles && !failed) {
       int t, split, kb0, kb1, tm, tn;
       unit_range(u, t, split, kb0, kb1);
       const int bi = t / tiles_per_matrix;
       tile_coord(t - bi * tiles_per_matrix, shape, tm, tn);
       const int az = bi * shape.a_z, bz = bi * shape.b_z;
       const int m0 = (tm * CG + (int)cta_rank) * kBlockM;
+      if constexpr (DYN) {
+        if (cta_rank == 0 && issuer) ring.request(n + 1);   // the answer arrives while this unit loads
+      }
       for (int kb = kb0; kb < kb1; ++kb, ++it) {
         const int s = it % STAGES;
         const uint32_t ph = (it / STAGES) & 1u;
@@ -201,7 +292,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         const uint32_t bar = (CG == 1) ? full_bar(s) : map_to_cta(full_bar(s), 0);
         if (issuer) {
           if (cta_rank == 0) mbar_arrive_expect_tx(full_bar(s), CG * Cfg::STAGE_BYTES);
-          load(a_dst, &tmA, kb * kBlockK, m0, az, bar);
+          load_p(a_dst, &tmA, kb * kBlockK, m0, az, bar, pol_a);
 #pragma unroll
           for (int nt = 0; nt < NT; ++nt) {
             const uint32_t b_dst = sB0 + (s * NT + nt) * Cfg::B_BYTES;
@@ -215,6 +306,14 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           }
         }
         __syncwarp();
+      }
+      if (failed) break;
+      ++n;
+      if constexpr (DYN) {
+        u = (cta_rank == 0) ? ring.template fetch_and_publish<CG>(n, issuer) : ring.wait_unit(n, kRoleProducer);
+        if (u == -2) failed = true;
+      } else {
+        u += num_clusters;
       }
     }
   } else if (warp == 1) {
@@ -239,7 +338,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         }
       };
       uint32_t it = 0, acc_it = 0;
-      for (int u = cluster_id; u < num_tiles && !failed; u += num_clusters, ++acc_it) {
+      int u = cluster_id;
+      while (u >= 0 && u < num_tiles && !failed) {
         int t, split, kb0, kb1;
         unit_range(u, t, split, kb0, kb1);
         const uint32_t acc = acc_it % ACC_STAGES, aph = (acc_it / ACC_STAGES) & 1u;
@@ -270,6 +370,13 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         if (failed) break;
         if (issuer) commit(tfull_bar(acc));   // accumulator complete -> epilogue warps of both CTAs
         __syncwarp();
+        ++acc_it;
+        if constexpr (DYN) {
+          u = ring.wait_unit(acc_it, kRoleMma);
+          if (u == -2) failed = true;
+        } else {
+          u += num_clusters;
+        }
       }
     }
   } else {
@@ -279,7 +386,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     const uint32_t lane_base = (uint32_t)(quad * 32) << 16;
     const uint32_t stage0 = sEpi0 + (uint32_t)(warp - 2) * (uint32_t)Cfg::EPI_BUFS * Cfg::EPI_WARP_BUF;
     uint32_t acc_it = 0, store_it = 0;
-    for (int u = cluster_id; u < num_tiles && !failed; u += num_clusters, ++acc_it) {
+    int u = cluster_id;
+    while (u >= 0 && u < num_tiles && !failed) {
       int t, split, kb0, kb1, tm, tn;
       unit_range(u, t, split, kb0, kb1);
       const int bi = t / tiles_per_matrix;
@@ -428,6 +536,13 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           if constexpr (CG == 1) mbar_arrive(tempty_bar(acc));
           else mbar_arrive_cluster(map_to_cta(tempty_bar(acc), 0));
         }
+      }
+      ++acc_it;
+      if constexpr (DYN) {
+        u = ring.wait_unit(acc_it, kRoleEpilogue);
+        if (u == -2) failed = true;
+      } else {
+        u += num_clusters;
       }
     }
     if (Cfg::EPI == 1 && lane == 0) tma_store_wait_all<0>();

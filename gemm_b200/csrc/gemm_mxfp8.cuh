@@ -46,10 +46,11 @@ constexpr int kMxSfbCol = 260;     // TMEM columns [260, 268): scales of B (256 
 //      are never stored, and the shared memory saved buys more stages of B in flight.
 // BN:  columns of C per tile (per CTA for CG = 1, per CTA pair for CG = 2): 256, or 128 for problems
 //      whose 256-column tiles would not fill one round of the persistent grid.
-template <int CG_, int STAGES_, bool COMMIT_MASK_, int EPI_ = 0, int A_ROWS_ = kBlockM, int BN_ = kBlockN>
+// DYN: work units handed out at run time (see SchedRing) instead of unit = cluster + i * clusters.
+template <int CG_, int STAGES_, bool COMMIT_MASK_, int EPI_ = 0, int A_ROWS_ = kBlockM, int BN_ = kBlockN, bool DYN_ = false>
 struct MxCfg {
   static constexpr int CG = CG_, STAGES = STAGES_, EPI = EPI_, A_ROWS = A_ROWS_, BN = BN_;
-  static constexpr bool COMMIT_MASK = COMMIT_MASK_;
+  static constexpr bool COMMIT_MASK = COMMIT_MASK_, DYN = DYN_;
   static constexpr int NCH = BN / 64;                       // 32-column accumulator chunks per epilogue warp
   static constexpr int BN_CTA = BN / CG;
   static constexpr int A_BYTES = A_ROWS * kMxBlockK;        // bytes a stage loads and the stage pitch (16 KB for 128 rows)
@@ -60,7 +61,8 @@ struct MxCfg {
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES + SFA_BYTES + SFB_BYTES;
   static constexpr int EPI_WARP_BUF = 32 * 128;             // 32 rows x 128 bytes per epilogue warp
   static constexpr int EPI_BYTES = EPI == 1 ? 8 * EPI_WARP_BUF : 0;
-  static constexpr int BAR_BYTES = (2 * STAGES + 2) * 8 + 16;
+  static constexpr int BAR_BYTES = (2 * STAGES + 2) * 8 + 16 + (DYN ? kSchedBytes : 0);
+  static_assert(STAGES + 5 <= kSchedSlots, "the unit ring must outlast the producer's lead over the epilogue");
   static constexpr int SMEM_BYTES = 1024 + A_RING_BYTES + STAGES * (B_BYTES + SFA_BYTES + SFB_BYTES) + EPI_BYTES + BAR_BYTES;
   static_assert(A_ROWS % 8 == 0 && A_ROWS >= 8 && A_ROWS <= kBlockM, "A rows per stage: whole 8-row swizzle atoms");
   static_assert(A_ROWS == kBlockM || CG == 1, "narrow A stages are a single-CTA variant");
@@ -93,6 +95,8 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
   const uint32_t tfull_bar = bar0 + 8u * (2 * STAGES);
   const uint32_t tempty_bar = bar0 + 8u * (2 * STAGES + 1);
   const uint32_t tmem_slot = bar0 + 8u * (2 * STAGES + 2);
+  const SchedRing ring{bar0 + 8u * (2 * STAGES + 2) + 16u};   // only with Cfg::DYN
+  constexpr bool DYN = Cfg::DYN;
 
   const int warp = __shfl_sync(0xffffffffu, (int)(threadIdx.x >> 5), 0);
   const int lane = threadIdx.x & 31;
@@ -116,6 +120,7 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
     }
     mbar_init(tfull_bar, 1);
     mbar_init(tempty_bar, 8 * CG);   // one arrival per epilogue warp of every CTA of the pair
+    if constexpr (DYN) ring.init();
     fence_mbar_init();
   }
   if (warp == 0 && lane == 0) {
@@ -147,14 +152,18 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
     // ------------------------------------------------------------------ TMA producer
     // The whole warp walks the schedule; one elected lane issues the copies.
     const bool issuer = elect_one();
-    uint32_t it = 0;
-    for (int u = cluster_id; u < num_units && !failed; u += num_clusters) {
+    uint32_t it = 0, n = 0;   // n: how many units this cluster has started
+    int u = cluster_id;
+    while (u >= 0 && u < num_units && !failed) {
       int t, split, kb0, kb1, tm, tn;
       unit_range(u, t, split, kb0, kb1);
       tile_coord(t, shape, tm, tn);
       const int mblk = tm * CG + (int)cta_rank;            // 128-row block of A / C
       const int m0 = mblk * kBlockM;
       const int n0 = tn * Cfg::BN + (int)cta_rank * Cfg::BN_CTA;
+      if constexpr (DYN) {
+        if (cta_rank == 0 && issuer) ring.request(n + 1);   // the answer arrives while this unit loads
+      }
       for (int kb = kb0; kb < kb1; ++kb, ++it) {
         const int s = it % STAGES;
         const uint32_t ph = (it / STAGES) & 1u;
@@ -182,6 +191,14 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
         }
         __syncwarp();
       }
+      if (failed) break;
+      ++n;
+      if constexpr (DYN) {
+        u = (cta_rank == 0) ? ring.template fetch_and_publish<CG>(n, issuer) : ring.wait_unit(n, kRoleProducer);
+        if (u == -2) failed = true;
+      } else {
+        u += num_clusters;
+      }
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer (leader CTA)
@@ -205,7 +222,8 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
       const uint32_t d_tmem = tmem_base;
       const uint32_t sfa_tmem = tmem_base + kMxSfaCol, sfb_tmem = tmem_base + kMxSfbCol;
       uint32_t it = 0, acc_it = 0;
-      for (int u = cluster_id; u < num_units && !failed; u += num_clusters, ++acc_it) {
+      int u = cluster_id;
+      while (u >= 0 && u < num_units && !failed) {
         int t, split, kb0, kb1;
         unit_range(u, t, split, kb0, kb1);
         if (!mbar_wait_warp(tempty_bar, (acc_it & 1u) ^ 1u, kRoleMma, 100)) { failed = true; break; }
@@ -239,6 +257,13 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
         if (failed) break;
         if (issuer) commit(tfull_bar);
         __syncwarp();
+        ++acc_it;
+        if constexpr (DYN) {
+          u = ring.wait_unit(acc_it, kRoleMma);
+          if (u == -2) failed = true;
+        } else {
+          u += num_clusters;
+        }
       }
     }
   } else {
@@ -248,7 +273,8 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
     const int half = (warp - 2) >> 2;      // columns [BN/2 half, BN/2 half + BN/2) of the tile
     const uint32_t t_addr = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(half * (Cfg::BN / 2));
     uint32_t acc_it = 0;
-    for (int u = cluster_id; u < num_units && !failed; u += num_clusters, ++acc_it) {
+    int u = cluster_id;
+    while (u >= 0 && u < num_units && !failed) {
       int t, split, kb0, kb1, tm, tn;
       unit_range(u, t, split, kb0, kb1);
       tile_coord(t, shape, tm, tn);
@@ -390,6 +416,13 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
             }
           }
         }
+      }
+      ++acc_it;
+      if constexpr (DYN) {
+        u = ring.wait_unit(acc_it, kRoleEpilogue);
+        if (u == -2) failed = true;
+      } else {
+        u += num_clusters;
       }
     }
     if (Cfg::EPI == 1 && lane == 0) tma_store_wait_all<0>();

@@ -46,8 +46,13 @@ __device__ __forceinline__ void cp_async_wait() {
   asm volatile("cp.async.wait_group %0;\n" ::"n"(N));
 }
 
-template <int BM_, int BN_, int BK_, int WMW_, int WNW_, int STAGES_, int MINB_, bool X2_, int AK_ = 2>
+// ADUP: every element of the A tile is stored twice in shared memory ({a, a}), so that one LDS.128
+//       delivers two ready-made operands of the packed multiply-add (which wants the A value in
+//       both halves of a 64-bit register pair) and the loop needs no register moves to build them.
+//       The tile is filled by 4-byte cp.async, two per element.
+template <int BM_, int BN_, int BK_, int WMW_, int WNW_, int STAGES_, int MINB_, bool X2_, int AK_ = 2, bool ADUP_ = false>
 struct Cfg {
+  static constexpr bool ADUP = ADUP_;
   static constexpr int AK = AK_;              // k-width of one A fragment load (2: LDS.64, 4: LDS.128)
   static constexpr int BM = BM_, BN = BN_, BK = BK_, WMW = WMW_, WNW = WNW_;
   static constexpr int STAGES = STAGES_, MINB = MINB_;
@@ -55,12 +60,13 @@ struct Cfg {
   static constexpr int THREADS = WMW * WNW * 32;
   static constexpr int TM = BM / (WMW * 4);   // rows per thread (interleaved by 4)
   static constexpr int TN = BN / (WNW * 8);   // columns per thread (float4 groups, 32 apart)
-  static constexpr int LDA_S = BK + 4;        // padded row of the A tile, in floats
+  static constexpr int LDA_S = (ADUP ? 2 * BK : BK) + 4;   // padded row of the A tile, in floats
   static constexpr int A_STAGE = BM * LDA_S;
   static constexpr int B_STAGE = BK * BN;
   static constexpr int SMEM_BYTES = STAGES * (A_STAGE + B_STAGE) * 4;
   static_assert(TM >= 1 && TN >= 4 && TN % 4 == 0, "thread tile");
   static_assert(BK % 4 == 0, "BK");
+  static_assert(!ADUP || (X2 && AK == 2), "duplicated A serves the packed multiply-add, two k per load");
   static_assert(((LDA_S / 4) & 1) == 1, "A row stride must be an odd number of 16-byte units");
 };
 
@@ -70,7 +76,12 @@ struct Cfg {
 template <class C, int VEC>
 __global__ void __launch_bounds__(C::THREADS, C::MINB)
 sgemm_kernel(const float* __restrict__ A, const float* __restrict__ B, float* __restrict__ Cm,
-             int M, int N, int K, int64_t lda, int64_t ldb, int64_t ldc, int tiles_m, int tiles_n) {
+             int M, int N, int K, int64_t lda, int64_t ldb, int64_t ldc, int tiles_m, int tiles_n,
+             int64_t batch_a, int64_t batch_b, int64_t batch_c) {
+  // blockIdx.y = problem of a strided batch (strides in elements; 0 shares the operand)
+  A += (int64_t)blockIdx.y * batch_a;
+  B += (int64_t)blockIdx.y * batch_b;
+  Cm += (int64_t)blockIdx.y * batch_c;
   constexpr int BM = C::BM, BN = C::BN, BK = C::BK, TM = C::TM, TN = C::TN, TNC = C::TN / 4;
   constexpr int STAGES = C::STAGES, THREADS = C::THREADS, LDA_S = C::LDA_S, AK = C::AK;
   extern __shared__ __align__(16) float smem[];
@@ -97,9 +108,10 @@ sgemm_kernel(const float* __restrict__ A, const float* __restrict__ B, float* __
   // Per-thread loader state for the 16-byte path: chunk `it` of a thread is RPI rows below chunk
   // `it - 1`, so one base pointer per operand (advanced by BK columns / BK rows per K tile) suffices.
   constexpr int KC = BK / 4, NC = BN / 4;
-  constexpr int A_IT = BM * KC / THREADS, A_RPI = THREADS / KC;   // A: rows per pass
-  constexpr int B_IT = BK * NC / THREADS, B_RPI = THREADS / NC;   // B: k rows per pass
-  static_assert(BM * KC % THREADS == 0 && THREADS % KC == 0, "A tile must split evenly over the threads");
+  constexpr int A_IT = (BM * KC + THREADS - 1) / THREADS, A_RPI = THREADS / KC;   // A: rows per pass
+  constexpr int B_IT = BK * NC / THREADS, B_RPI = THREADS / NC;                   // B: k rows per pass
+  constexpr bool A_EVEN = (BM * KC) % THREADS == 0;   // else the last pass is guarded (tile heights such as 28)
+  static_assert(THREADS % KC == 0, "a pass over the A tile must cover whole rows");
   static_assert(BK * NC % THREADS == 0 && THREADS % NC == 0, "B tile must split evenly over the threads");
   const int a_r = tid / KC, a_kc = (tid % KC) * 4;
   const int b_r = tid / NC, b_nc = (tid % NC) * 4;
@@ -111,13 +123,31 @@ sgemm_kernel(const float* __restrict__ A, const float* __restrict__ B, float* __
 
   auto load_tile = [&](int kt, int slot) {
     const int k0 = kt * BK;
+    if constexpr (C::ADUP) {
+      // one element per thread and pass, consecutive threads on consecutive k; stored twice
+      const uint32_t a_base = smem_u32(sA + slot * C::A_STAGE);
+#pragma unroll
+      for (int it = 0; it < (BM * BK + THREADS - 1) / THREADS; ++it) {
+        const int c = tid + it * THREADS;
+        if ((BM * BK) % THREADS != 0 && c >= BM * BK) break;
+        const int r = c / BK, kc = c % BK;
+        const bool ok = (row0 + r < M) && (k0 + kc < K);
+        const float* src = ok ? (A + (int64_t)(row0 + r) * lda + (k0 + kc)) : A;
+        const uint32_t dst = a_base + (r * LDA_S + 2 * kc) * 4;
+        cp_async4(dst, src, ok ? 4 : 0);
+        cp_async4(dst + 4, src, ok ? 4 : 0);
+      }
+    }
     if constexpr (VEC == 4) {
       const bool a_k_ok = (k0 + a_kc) < K;
+      if constexpr (!C::ADUP) {
 #pragma unroll
-      for (int it = 0; it < A_IT; ++it) {
-        const bool ok = a_k_ok && (row0 + a_r + it * A_RPI < M);
-        const float* src = a_src + (int64_t)(it * A_RPI) * lda + k0;
-        cp_async16(a_sdst + (slot * C::A_STAGE + it * A_RPI * LDA_S) * 4, ok ? src : A, ok ? 16 : 0);
+        for (int it = 0; it < A_IT; ++it) {
+          if (!A_EVEN && a_r + it * A_RPI >= BM) break;
+          const bool ok = a_k_ok && (row0 + a_r + it * A_RPI < M);
+          const float* src = a_src + (int64_t)(it * A_RPI) * lda + k0;
+          cp_async16(a_sdst + (slot * C::A_STAGE + it * A_RPI * LDA_S) * 4, ok ? src : A, ok ? 16 : 0);
+        }
       }
 #pragma unroll
       for (int it = 0; it < B_IT; ++it) {
@@ -128,14 +158,17 @@ sgemm_kernel(const float* __restrict__ A, const float* __restrict__ B, float* __
     } else {
       float* a_dst = sA + slot * C::A_STAGE;
       float* b_dst = sB + slot * C::B_STAGE;
+      if constexpr (!C::ADUP) {
 #pragma unroll 4
-      for (int it = 0; it < BM * BK / THREADS; ++it) {
-        const int c = tid + it * THREADS;
-        const int r = c / BK, kc = c % BK;
-        const int gr = row0 + r, gk = k0 + kc;
-        const bool ok = (gr < M) && (gk < K);
-        const float* src = ok ? (A + (int64_t)gr * lda + gk) : A;
-        cp_async4(smem_u32(a_dst + r * LDA_S + kc), src, ok ? 4 : 0);
+        for (int it = 0; it < (BM * BK + THREADS - 1) / THREADS; ++it) {
+          const int c = tid + it * THREADS;
+          if ((BM * BK) % THREADS != 0 && c >= BM * BK) break;
+          const int r = c / BK, kc = c % BK;
+          const int gr = row0 + r, gk = k0 + kc;
+          const bool ok = (gr < M) && (gk < K);
+          const float* src = ok ? (A + (int64_t)gr * lda + gk) : A;
+          cp_async4(smem_u32(a_dst + r * LDA_S + kc), src, ok ? 4 : 0);
+        }
       }
 #pragma unroll 4
       for (int it = 0; it < BK * BN / THREADS; ++it) {
@@ -180,9 +213,15 @@ sgemm_kernel(const float* __restrict__ A, const float* __restrict__ B, float* __
 #pragma unroll
     for (int kq = 0; kq < BK / AK; ++kq) {
       float af[TM][AK];
+      float2 af2[TM][AK];   // ADUP: the operand pairs as they come out of shared memory
 #pragma unroll
       for (int i = 0; i < TM; ++i) {
-        if constexpr (AK == 4) {
+        if constexpr (C::ADUP) {
+          const float4 v = *reinterpret_cast<const float4*>(a_s + (4 * i) * LDA_S + kq * 4);
+          af2[i][0] = make_float2(v.x, v.y);
+          af2[i][1] = make_float2(v.z, v.w);
+          af[i][0] = v.x; af[i][1] = v.z;
+        } else if constexpr (AK == 4) {
           const float4 v = *reinterpret_cast<const float4*>(a_s + (4 * i) * LDA_S + kq * 4);
           af[i][0] = v.x; af[i][1] = v.y; af[i][2] = v.z; af[i][3] = v.w;
         } else {
@@ -200,7 +239,7 @@ sgemm_kernel(const float* __restrict__ A, const float* __restrict__ B, float* __
         for (int i = 0; i < TM; ++i) {
           const float a = af[i][kk];
           if constexpr (C::X2) {
-            const float2 a2 = make_float2(a, a);
+            const float2 a2 = C::ADUP ? af2[i][kk] : make_float2(a, a);
 #pragma unroll
             for (int c = 0; c < TNC; ++c) {
               acc2[i][2 * c + 0] = __ffma2_rn(a2, make_float2(bf[c].x, bf[c].y), acc2[i][2 * c + 0]);
@@ -247,7 +286,7 @@ struct ConfigEntry {
   const char* name;
   int bm, bn;
   int (*launch)(const float*, const float*, float*, int, int, int, int64_t, int64_t, int64_t, bool,
-                cudaStream_t);
+                cudaStream_t, int, int64_t, int64_t, int64_t);
 };
 
 // Internal linkage on purpose: this source is compiled into several modules of one process (the
@@ -255,7 +294,8 @@ struct ConfigEntry {
 // "attribute already set" cache below must not be merged across them by the dynamic linker.
 template <class C>
 static int launch_cfg(const float* A, const float* B, float* Cm, int M, int N, int K, int64_t lda,
-                      int64_t ldb, int64_t ldc, bool vec, cudaStream_t stream) {
+                      int64_t ldb, int64_t ldc, bool vec, cudaStream_t stream, int batch, int64_t batch_a,
+                      int64_t batch_b, int64_t batch_c) {
   const int tiles_m = (M + C::BM - 1) / C::BM, tiles_n = (N + C::BN - 1) / C::BN;
   const int64_t tiles = (int64_t)tiles_m * tiles_n;
   if (tiles == 0) return GEMM_B200_OK;
@@ -276,9 +316,14 @@ static int launch_cfg(const float* A, const float* B, float* Cm, int M, int N, i
       done_fn[slot] = reinterpret_cast<const void*>(kern);
     }
   }
-  kern<<<(unsigned)tiles, C::THREADS, C::SMEM_BYTES, stream>>>(A, B, Cm, M, N, K, lda, ldb, ldc, tiles_m, tiles_n);
-  launch_counter().fetch_add(1, std::memory_order_relaxed);
-  GEMM_B200_CUDA_TRY(cudaGetLastError());
+  // at most 65535 problems per launch (grid.y)
+  for (int b0 = 0; b0 < batch; b0 += 65535) {
+    const int nb = batch - b0 < 65535 ? batch - b0 : 65535;
+    kern<<<dim3((unsigned)tiles, (unsigned)nb), C::THREADS, C::SMEM_BYTES, stream>>>(
+        A + b0 * batch_a, B + b0 * batch_b, Cm + b0 * batch_c, M, N, K, lda, ldb, ldc, tiles_m, tiles_n, batch_a, batch_b, batch_c);
+    launch_counter().fetch_add(1, std::memory_order_relaxed);
+    GEMM_B200_CUDA_TRY(cudaGetLastError());
+  }
   return GEMM_B200_OK;
 }
 
@@ -286,6 +331,25 @@ static int launch_cfg(const float* A, const float* B, float* Cm, int M, int N, i
 using C64x128k32p3     = Cfg<64, 128, 32, 2, 2, 3, 2, true>;
 using C64x64k32p       = Cfg<64, 64, 32, 2, 2, 4, 4, true>;
 using C32x64k32p       = Cfg<32, 64, 32, 2, 2, 4, 6, true>;
+// Tile heights of 28 and 56 rows: 148 SMs = 4 x 37, and 37 tiles of 28 rows cover 1024 rows (74 of
+// 28 or 37 of 56 cover 2048, ...), so power-of-two problems split into a whole number of tiles per
+// SM instead of leaving a third of the SMs one tile short.  7 rows x 8 (or 4) columns per thread.
+using C28x256k32p      = Cfg<28, 256, 32, 1, 4, 3, 1, true>;
+using C28x128k32p      = Cfg<28, 128, 32, 1, 4, 4, 2, true>;
+using C28x256k32pw8    = Cfg<28, 256, 32, 1, 8, 3, 1, true>;
+using C56x256k16p      = Cfg<56, 256, 16, 2, 4, 4, 2, true>;
+using C56x256k32p      = Cfg<56, 256, 32, 2, 4, 3, 1, true>;
+using C56x128k32p      = Cfg<56, 128, 32, 2, 2, 3, 3, true>;
+using C28x64k32p       = Cfg<28, 64, 32, 1, 2, 4, 4, true>;
+using C28x128k32pd     = Cfg<28, 128, 32, 1, 4, 4, 2, true, 2, true>;
+using C64x128k32pd     = Cfg<64, 128, 32, 2, 2, 3, 2, true, 2, true>;
+using C64x64k32pd      = Cfg<64, 64, 32, 2, 2, 4, 4, true, 2, true>;
+using C56x128k32pd     = Cfg<56, 128, 32, 2, 2, 3, 2, true, 2, true>;
+using C32x64k32pd      = Cfg<32, 64, 32, 2, 2, 4, 6, true, 2, true>;
+using C28x128k32ps3    = Cfg<28, 128, 32, 1, 4, 3, 2, true>;
+using C28x128k16ps6    = Cfg<28, 128, 16, 1, 4, 6, 2, true>;
+using C28x128k32pa4    = Cfg<28, 128, 32, 1, 4, 4, 2, true, 4>;
+using C28x128k32       = Cfg<28, 128, 32, 1, 4, 4, 2, false>;
 #ifdef GEMM_B200_TUNING
 // tile shapes the heuristic never picks; built only for tuning sweeps
 using C128x128k16      = Cfg<128, 128, 16, 4, 2, 3, 2, false>;
@@ -306,6 +370,22 @@ static const ConfigEntry kConfigs[] = {
     {"64x128x32_s3_f32x2", 64, 128, launch_cfg<C64x128k32p3>},
     {"64x64x32_s4_f32x2", 64, 64, launch_cfg<C64x64k32p>},
     {"32x64x32_s4_f32x2", 32, 64, launch_cfg<C32x64k32p>},
+    {"28x256x32_s3_f32x2", 28, 256, launch_cfg<C28x256k32p>},
+    {"28x128x32_s4_f32x2", 28, 128, launch_cfg<C28x128k32p>},
+    {"28x256x32_s3_f32x2_w8", 28, 256, launch_cfg<C28x256k32pw8>},
+    {"56x256x16_s4_f32x2", 56, 256, launch_cfg<C56x256k16p>},
+    {"56x256x32_s3_f32x2", 56, 256, launch_cfg<C56x256k32p>},
+    {"56x128x32_s3_f32x2", 56, 128, launch_cfg<C56x128k32p>},
+    {"28x64x32_s4_f32x2", 28, 64, launch_cfg<C28x64k32p>},
+    {"28x128x32_s4_f32x2_adup", 28, 128, launch_cfg<C28x128k32pd>},
+    {"64x128x32_s3_f32x2_adup", 64, 128, launch_cfg<C64x128k32pd>},
+    {"64x64x32_s4_f32x2_adup", 64, 64, launch_cfg<C64x64k32pd>},
+    {"56x128x32_s3_f32x2_adup", 56, 128, launch_cfg<C56x128k32pd>},
+    {"32x64x32_s4_f32x2_adup", 32, 64, launch_cfg<C32x64k32pd>},
+    {"28x128x32_s3_f32x2", 28, 128, launch_cfg<C28x128k32ps3>},
+    {"28x128x16_s6_f32x2", 28, 128, launch_cfg<C28x128k16ps6>},
+    {"28x128x32_s4_f32x2_a4", 28, 128, launch_cfg<C28x128k32pa4>},
+    {"28x128x32_s4", 28, 128, launch_cfg<C28x128k32>},
 #ifdef GEMM_B200_TUNING
     {"128x128x16_s3", 128, 128, launch_cfg<C128x128k16>},
     {"128x128x16_s3_f32x2", 128, 128, launch_cfg<C128x128k16p>},
@@ -334,12 +414,12 @@ inline int config_index(const char* name) {
 // 14 / 39 / 52 / 55 / 56;  32x64x32: 16 / 34 / 43 / 44 / 45.  So: 64x128x32 once it yields about
 // four tiles per SM, 64x64x32 while those tiles still fill the SMs, 32x64x32 below that.  Other
 // thread-tile shapes at 128x128x32 (4x16: 54.6, 16x4: 46.5 TFLOP/s at 4096) did not beat 8x8.
-inline int pick_config(int64_t M, int64_t N, int num_sms) {
+inline int pick_config(int64_t M, int64_t N, int num_sms, int64_t batch = 1) {
   static const int large = config_index("64x128x32_s3_f32x2"), medium = config_index("64x64x32_s4_f32x2"),
                    small = config_index("32x64x32_s4_f32x2");
-  const int64_t t_large = ceil_div64(M, 64) * ceil_div64(N, 128);
+  const int64_t t_large = batch * ceil_div64(M, 64) * ceil_div64(N, 128);
   if (t_large >= 4 * (int64_t)num_sms) return large;
-  const int64_t t64 = ceil_div64(M, 64) * ceil_div64(N, 64);
+  const int64_t t64 = batch * ceil_div64(M, 64) * ceil_div64(N, 64);
   if (t64 >= (int64_t)num_sms + num_sms / 2) return medium;
   return small;
 }
@@ -347,19 +427,31 @@ inline int pick_config(int64_t M, int64_t N, int num_sms) {
 }  // namespace f32
 }  // namespace gemm_b200
 
-extern "C" int gemm_b200_sgemm_f32_cfg(const float* A, const float* B, float* C, int64_t M, int64_t N,
-                                       int64_t K, int64_t lda, int64_t ldb, int64_t ldc, int config,
-                                       void* stream) {
-  using namespace gemm_b200;
-  if (M < 0 || N < 0 || K < 0) return fail(GEMM_B200_ERR_INVALID_ARG, "sgemm_f32: negative size");
-  if (M == 0 || N == 0) return GEMM_B200_OK;
+namespace gemm_b200 {
+namespace f32 {
+
+// Shared body of the plain and the strided-batched entry points (batch == 1, strides 0: plain).
+static int entry(const float* A, const float* B, float* C, int64_t batch, int64_t M, int64_t N, int64_t K, int64_t lda,
+                 int64_t ldb, int64_t ldc, int64_t stride_a, int64_t stride_b, int64_t stride_c, int config, void* stream) {
+  if (M < 0 || N < 0 || K < 0 || batch < 0) return fail(GEMM_B200_ERR_INVALID_ARG, "sgemm_f32: negative size");
+  if (M == 0 || N == 0 || batch == 0) return GEMM_B200_OK;
   if (!C || (K > 0 && (!A || !B))) return fail(GEMM_B200_ERR_INVALID_ARG, "sgemm_f32: null pointer");
   if (lda < K || ldb < N || ldc < N)
     return fail(GEMM_B200_ERR_INVALID_ARG, "sgemm_f32: leading dimension smaller than the row (lda=%lld ldb=%lld ldc=%lld)",
                 (long long)lda, (long long)ldb, (long long)ldc);
-  if (M > 0x7fffffff || N > 0x7fffffff || K > 0x7fffffff)
+  if (M > 0x7fffffff || N > 0x7fffffff || K > 0x7fffffff || batch > 0x7fffffff)
     return fail(GEMM_B200_ERR_TOO_LARGE, "sgemm_f32: a dimension exceeds 2^31-1");
-  if (config >= f32::kNumConfigs) return fail(GEMM_B200_ERR_INVALID_ARG, "sgemm_f32: config %d out of range", config);
+  if (batch > 1) {
+    // matrices of one operand must not interleave; 0 shares A or B between the problems
+    if (stride_a < 0 || stride_b < 0 || (stride_a != 0 && stride_a < (M - 1) * lda + K) ||
+        (stride_b != 0 && stride_b < (K - 1) * ldb + N) || stride_c < (M - 1) * ldc + N)
+      return fail(GEMM_B200_ERR_INVALID_ARG,
+                  "sgemm_f32_batched: a batch stride is smaller than its matrix (stride_a=%lld stride_b=%lld stride_c=%lld)",
+                  (long long)stride_a, (long long)stride_b, (long long)stride_c);
+  } else {
+    stride_a = stride_b = stride_c = 0;
+  }
+  if (config >= kNumConfigs) return fail(GEMM_B200_ERR_INVALID_ARG, "sgemm_f32: config %d out of range", config);
   if (config < 0) {
     static thread_local int cached_dev = -1, cached_sms = 148;
     int dev = 0;
@@ -369,21 +461,37 @@ extern "C" int gemm_b200_sgemm_f32_cfg(const float* A, const float* B, float* C,
       cached_dev = dev;
     }
     static const int forced = env_int("GEMM_B200_F32_CONFIG", -1);
-    config = (forced >= 0 && forced < f32::kNumConfigs) ? forced : f32::pick_config(M, N, cached_sms);
+    config = (forced >= 0 && forced < kNumConfigs) ? forced : pick_config(M, N, cached_sms, batch);
   }
   const bool vec = (lda % 4 == 0) && (ldb % 4 == 0) && (ldc % 4 == 0) && (K % 4 == 0) && (N % 4 == 0) &&
+                   (stride_a % 4 == 0) && (stride_b % 4 == 0) && (stride_c % 4 == 0) &&
                    ((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(B) |
                      reinterpret_cast<uintptr_t>(C)) % 16 == 0);
   if (log_enabled())
     fprintf(stderr, "[gemm_b200] sgemm_f32 %lldx%lldx%lld -> %s%s\n", (long long)M, (long long)K, (long long)N,
-            f32::kConfigs[config].name, vec ? "" : " (4-byte loads)");
-  return f32::kConfigs[config].launch(A, B, C, (int)M, (int)N, (int)K, lda, ldb, ldc, vec,
-                                      static_cast<cudaStream_t>(stream));
+            kConfigs[config].name, vec ? "" : " (4-byte loads)");
+  return kConfigs[config].launch(A, B, C, (int)M, (int)N, (int)K, lda, ldb, ldc, vec, static_cast<cudaStream_t>(stream),
+                                 (int)batch, stride_a, stride_b, stride_c);
+}
+
+}  // namespace f32
+}  // namespace gemm_b200
+
+extern "C" int gemm_b200_sgemm_f32_cfg(const float* A, const float* B, float* C, int64_t M, int64_t N,
+                                       int64_t K, int64_t lda, int64_t ldb, int64_t ldc, int config,
+                                       void* stream) {
+  return gemm_b200::f32::entry(A, B, C, 1, M, N, K, lda, ldb, ldc, 0, 0, 0, config, stream);
 }
 
 extern "C" int gemm_b200_sgemm_f32(const float* A, const float* B, float* C, int64_t M, int64_t N, int64_t K,
                                    int64_t lda, int64_t ldb, int64_t ldc, void* stream) {
-  return gemm_b200_sgemm_f32_cfg(A, B, C, M, N, K, lda, ldb, ldc, -1, stream);
+  return gemm_b200::f32::entry(A, B, C, 1, M, N, K, lda, ldb, ldc, 0, 0, 0, -1, stream);
+}
+
+extern "C" int gemm_b200_sgemm_f32_batched(const float* A, const float* B, float* C, int64_t batch, int64_t M, int64_t N,
+                                           int64_t K, int64_t lda, int64_t ldb, int64_t ldc, int64_t stride_a,
+                                           int64_t stride_b, int64_t stride_c, void* stream) {
+  return gemm_b200::f32::entry(A, B, C, batch, M, N, K, lda, ldb, ldc, stride_a, stride_b, stride_c, -1, stream);
 }
 
 extern "C" int gemm_b200_sgemm_f32_num_configs(void) { return gemm_b200::f32::kNumConfigs; }

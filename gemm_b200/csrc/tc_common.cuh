@@ -118,6 +118,78 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int rol
   }
 }
 
+// Wait on a barrier that a thread of ANOTHER CTA of the cluster arrives on (acquire at cluster
+// scope, so that CTA's shared::cluster stores before its arrive are visible afterwards).
+__device__ __forceinline__ bool mbar_try_wait_cluster(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n"
+      "selp.u32 %0, 1, 0, p;\n"
+      "}\n"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+__device__ __forceinline__ bool mbar_wait_cluster(uint32_t bar, uint32_t parity, int role, int stage,
+                                                  unsigned long long limit_ns = kWaitLimitNs) {
+  if (mbar_try_wait_cluster(bar, parity)) return true;
+  const unsigned long long t0 = globaltimer_ns();
+  uint32_t spins = 0;
+  while (true) {
+    if (mbar_try_wait_cluster(bar, parity)) return true;
+    if ((++spins & 255u) == 0) {
+      if (aborted()) return false;
+      if (globaltimer_ns() - t0 > limit_ns) {
+        record_timeout(role, stage);
+        return false;
+      }
+    }
+  }
+}
+__device__ __forceinline__ void st_shared_cluster_u32(uint32_t cluster_addr, uint32_t v) {
+  asm volatile("st.shared::cluster.u32 [%0], %1;" ::"r"(cluster_addr), "r"(v) : "memory");
+}
+__device__ __forceinline__ void st_shared_u32(uint32_t addr, uint32_t v) {
+  asm volatile("st.shared.u32 [%0], %1;" ::"r"(addr), "r"(v) : "memory");
+}
+__device__ __forceinline__ uint32_t ld_shared_u32(uint32_t addr) {
+  uint32_t v;
+  asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(addr) : "memory");
+  return v;
+}
+
+// ---------------------------------------------------------------------------------------
+// Cluster launch control: a running cluster takes over the work of a cluster of the same grid
+// that has not started yet.  try_cancel asks the hardware to cancel the launch of one pending
+// cluster; the 16-byte answer lands in this CTA's shared memory and completes 16 bytes on `bar`.
+// clc_first_cta returns blockIdx.x of the first CTA of the cancelled cluster, or -1 when no
+// cluster was left to cancel (after which the CTA must not ask again).
+// ---------------------------------------------------------------------------------------
+__device__ __forceinline__ void clc_try_cancel(uint32_t resp_smem, uint32_t bar) {
+  asm volatile("clusterlaunchcontrol.try_cancel.async.shared::cta.mbarrier::complete_tx::bytes.b128 [%0], [%1];"
+               ::"r"(resp_smem), "r"(bar) : "memory");
+}
+__device__ __forceinline__ int clc_first_cta(uint32_t resp_smem) {
+  uint32_t ok, x;
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      ".reg .b128 h;\n"
+      "ld.shared.b128 h, [%2];\n"
+      "clusterlaunchcontrol.query_cancel.is_canceled.pred.b128 p, h;\n"
+      "selp.u32 %0, 1, 0, p;\n"
+      "mov.u32 %1, 0;\n"
+      "@p clusterlaunchcontrol.query_cancel.get_first_ctaid::x.b32.b128 %1, h;\n"
+      "}\n"
+      : "=r"(ok), "=r"(x)
+      : "r"(resp_smem)
+      : "memory");
+  return ok ? (int)x : -1;
+}
+
 // Programmatic dependent launch: a kernel launched behind this one with the programmatic-
 // serialization attribute may be scheduled once every CTA here has called pdl_launch_dependents()
 // (or exited); it must call pdl_wait() before touching anything this grid wrote, which returns
@@ -184,6 +256,31 @@ __device__ __forceinline__ void tma_load_3d_pair(uint32_t dst, const CUtensorMap
       "cp.async.bulk.tensor.3d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
       ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(cluster_bar), "r"(x), "r"(y), "r"(z)
       : "memory");
+}
+// The same load with an L2 eviction-priority policy (from l2_policy_*()).
+__device__ __forceinline__ void tma_load_3d_hint(uint32_t dst, const CUtensorMap* map, int x, int y, int z, uint32_t bar,
+                                                 uint64_t policy) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1, {%3, %4, %5}], [%2], %6;"
+      ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(x), "r"(y), "r"(z), "l"(policy)
+      : "memory");
+}
+__device__ __forceinline__ void tma_load_3d_pair_hint(uint32_t dst, const CUtensorMap* map, int x, int y, int z,
+                                                      uint32_t cluster_bar, uint64_t policy) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1, {%3, %4, %5}], [%2], %6;"
+      ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(cluster_bar), "r"(x), "r"(y), "r"(z), "l"(policy)
+      : "memory");
+}
+__device__ __forceinline__ uint64_t l2_policy_evict_first() {
+  uint64_t p;
+  asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(p));
+  return p;
+}
+__device__ __forceinline__ uint64_t l2_policy_evict_last() {
+  uint64_t p;
+  asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(p));
+  return p;
 }
 __device__ __forceinline__ void tma_store_3d(const CUtensorMap* map, int x, int y, int z, uint32_t src) {
   asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%2, %3, %4}], [%1];"

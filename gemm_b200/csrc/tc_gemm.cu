@@ -374,9 +374,15 @@ static int launch_bf16(const Bf16Args& a) {
   shape.a_z = a.stride_a ? 1 : 0;
   shape.b_z = a.stride_b ? 1 : 0;
   shape.c_batch_stride = a.batch > 1 ? a.stride_c : 0;
+  static const int l2_hint = env_int("GEMM_B200_BF16_L2HINT", 0);   // tuning knob, see GemmShape::l2_hint
+  shape.l2_hint = l2_hint;
   const int64_t num_tiles = (int64_t)shape.tiles_m * shape.tiles_n * a.batch * shape.k_splits;
   if (num_tiles > 0x7fffffff) return fail(GEMM_B200_ERR_TOO_LARGE, "gemm_bf16: too many tiles");
-  const int clusters = (int)(num_tiles < max_clusters ? num_tiles : max_clusters);
+  // static schedule: one cluster per resident slot, each walks unit = cluster + i * clusters;
+  // run-time hand-out: one cluster per unit, the ones that run adopt the units of the others
+  const int clusters = Cfg::DYN ? (int)num_tiles : (int)(num_tiles < max_clusters ? num_tiles : max_clusters);
+  if (Cfg::DYN && shape.k_splits > 1)
+    return fail(GEMM_B200_ERR_INVALID_ARG, "gemm_bf16: K splits run on the static schedule");
 
   return launch_clusters(kern, clusters, CG, Cfg::THREADS, Cfg::SMEM_BYTES, a.stream, tmA, tmB, tmC, a.C, a.ldc, shape);
 }
@@ -401,6 +407,9 @@ using Bf16_2cta_tma_m  = Bf16Cfg<2, 6, 1, true>;
 using Bf16_2cta_n512_s3 = Bf16Cfg<2, 3, 1, true, 2, 2>;
 using Bf16_2cta_n128    = Bf16Cfg<2, 7, 1, true, 1, 2, 128>;
 using Bf16_1cta_n128    = Bf16Cfg<1, 6, 1, false, 1, 2, 128>;
+// the two multi-round shapes with units handed out at run time
+using Bf16_2cta_tma_m_dyn   = Bf16Cfg<2, 6, 1, true, 1, 2, kBlockN, true>;
+using Bf16_2cta_n512_s3_dyn = Bf16Cfg<2, 3, 1, true, 2, 2, kBlockN, true>;
 #ifdef GEMM_B200_TUNING
 // variants the heuristics never pick; built only for tuning sweeps
 using Bf16_2cta_direct = Bf16Cfg<2, 6, 0, false>;
@@ -417,6 +426,8 @@ enum Bf16ConfigId : int {
   kBf16Cfg512,              // CTA pair, 256x512 tiles (A shared by two accumulators)
   kBf16Cfg2ctaN128,         // CTA pair, 256x128 tiles: at most half a round of 256-wide tiles
   kBf16Cfg1ctaN128,         // single CTA, 128x128 tiles: one row tile and few column tiles
+  kBf16Cfg256Dyn,           // 256x256 tiles, units handed out at run time (problems of several rounds)
+  kBf16Cfg512Dyn,           // 256x512 tiles, units handed out at run time
 #ifdef GEMM_B200_TUNING
   kBf16Tune2ctaDirect, kBf16Tune2ctaTma, kBf16Tune512s4, kBf16Tune512Direct,
 #endif
@@ -430,6 +441,8 @@ static const Bf16ConfigEntry kBf16Configs[] = {
     GEMM_B200_BF16_ENTRY("2cta_256x512x64_s3_tmastore2_maskcommit", Bf16_2cta_n512_s3),
     GEMM_B200_BF16_ENTRY("2cta_256x128x64_s7_tmastore_maskcommit", Bf16_2cta_n128),
     GEMM_B200_BF16_ENTRY("1cta_128x128x64_s6_tmastore", Bf16_1cta_n128),
+    GEMM_B200_BF16_ENTRY("2cta_256x256x64_s6_tmastore_maskcommit_dynamic", Bf16_2cta_tma_m_dyn),
+    GEMM_B200_BF16_ENTRY("2cta_256x512x64_s3_tmastore2_maskcommit_dynamic", Bf16_2cta_n512_s3_dyn),
 #ifdef GEMM_B200_TUNING
     GEMM_B200_BF16_ENTRY("2cta_256x256x64_s6_direct", Bf16_2cta_direct),
     GEMM_B200_BF16_ENTRY("2cta_256x256x64_s6_tmastore", Bf16_2cta_tma),
@@ -456,7 +469,14 @@ static int pick_bf16_config(int64_t M, int64_t N, int64_t K, int sms, int64_t ba
   // the 512-wide tile's epilogue is not hidden under a main loop: it pays off from K ~ 4096 up
   // (8192^2 x K, TFLOP/s 256-wide / 512-wide: K=2048 1607 / 1570, 4096 1627 / 1662, 8192 1591 / 1660)
   const double gain = K >= 3072 ? 1.04 : 0.97;
-  return (gain * eff(2 * kBlockN) >= eff(kBlockN)) ? kBf16Cfg512 : kBf16Cfg256;
+  const bool wide = gain * eff(2 * kBlockN) >= eff(kBlockN);
+  // More than one round of units: hand them out at run time, so that clusters which fall behind
+  // do not end up alone on tiles whose operands the others streamed through the L2 long ago.
+  // GEMM_B200_BF16_DYNAMIC=0 keeps the static schedule (A/B comparisons).
+  static const bool dyn_ok = env_int("GEMM_B200_BF16_DYNAMIC", 1) != 0;
+  const int64_t units = batch * ceil_div64(M, 2 * kBlockM) * ceil_div64(N, wide ? 2 * kBlockN : kBlockN);
+  if (dyn_ok && units > clusters) return wide ? kBf16Cfg512Dyn : kBf16Cfg256Dyn;
+  return wide ? kBf16Cfg512 : kBf16Cfg256;
 }
 
 // Split-K BF16 GEMM: FP32 partial sums of every (tile, K range) unit go to `scratch`
@@ -719,12 +739,15 @@ static int launch_mxfp8(const MxArgs& a) {
   shape.batch = 1;
   shape.a_z = shape.b_z = 0;
   shape.c_batch_stride = 0;
+  shape.l2_hint = 0;
   shape.k_splits = (int)ceil_div64(num_kb, shape.kb_per_split);   // no empty split
   shape.split_stride = a.M * a.N;
   shape.raster_group = raster_group_for(shape.tiles_m, shape.tiles_n, (int64_t)Cfg::BN * a.K);
   const int64_t num_tiles = (int64_t)shape.tiles_m * shape.tiles_n * shape.k_splits;
   if (num_tiles > 0x7fffffff) return fail(GEMM_B200_ERR_TOO_LARGE, "gemm_mxfp8: too many tiles");
-  const int clusters = (int)(num_tiles < max_clusters ? num_tiles : max_clusters);
+  const int clusters = Cfg::DYN ? (int)num_tiles : (int)(num_tiles < max_clusters ? num_tiles : max_clusters);
+  if (Cfg::DYN && shape.k_splits > 1)
+    return fail(GEMM_B200_ERR_INVALID_ARG, "gemm_mxfp8: K splits run on the static schedule");
   return launch_clusters(kern, clusters, CG, kMxThreads, Cfg::SMEM_BYTES, a.stream, tmA, tmB, tmSFA, tmSFB, tmC, a.C, a.ldc, a.SFC, shape);
 }
 
@@ -750,6 +773,7 @@ using Mx_2cta_m_tma = MxCfg<2, 5, true, 1>;
 using Mx_1cta_a32 = MxCfg<1, 5, false, 0, 32>;   // M <= 32: 4 KB of A per stage, 5 stages of B in flight
 using Mx_2cta_n128 = MxCfg<2, 7, true, 1, kBlockM, 128>;   // 256 x 128 tiles for one-round problems
 using Mx_1cta_n128 = MxCfg<1, 6, false, 0, kBlockM, 128>;   // 128 x 128 tiles: 32 < M <= 128 with few column tiles
+using Mx_2cta_m_tma_dyn = MxCfg<2, 5, true, 1, kBlockM, kBlockN, true>;   // units handed out at run time
 #ifdef GEMM_B200_TUNING
 using Mx_2cta = MxCfg<2, 6, false>;
 using Mx_2cta_m = MxCfg<2, 6, true>;
@@ -761,6 +785,7 @@ enum MxConfigId : int {
   kNarrowMxConfig,       // M <= 32: single CTA with 32-row A stages and a deeper B pipeline
   kN128MxConfig,         // CTA pair, 256 x 128 tiles: at most half a round of 256-wide tiles
   k1ctaN128MxConfig,     // single CTA, 128 x 128 tiles
+  kDynMxConfig,          // the default tile with units handed out at run time (problems of several rounds)
 #ifdef GEMM_B200_TUNING
   kMxTune2cta, kMxTune2ctaMask,
 #endif
@@ -772,6 +797,7 @@ static const MxConfigEntry kMxConfigs[] = {
     {"1cta_32x256x128_s5_narrowA", {launch_mxfp8<Mx_1cta_a32, 0>, launch_mxfp8<Mx_1cta_a32, 1>}},
     {"2cta_256x128x128_s7_maskcommit_tmastore", {launch_mxfp8<Mx_2cta_n128, 0>, launch_mxfp8<Mx_2cta_n128, 1>}},
     {"1cta_128x128x128_s6", {launch_mxfp8<Mx_1cta_n128, 0>, launch_mxfp8<Mx_1cta_n128, 1>}},
+    {"2cta_256x256x128_s5_maskcommit_tmastore_dynamic", {launch_mxfp8<Mx_2cta_m_tma_dyn, 0>, launch_mxfp8<Mx_2cta_m_tma_dyn, 1>}},
 #ifdef GEMM_B200_TUNING
     {"2cta_256x256x128_s6", {launch_mxfp8<Mx_2cta, 0>, launch_mxfp8<Mx_2cta, 1>}},
     {"2cta_256x256x128_s6_maskcommit", {launch_mxfp8<Mx_2cta_m, 0>, launch_mxfp8<Mx_2cta_m, 1>}},
@@ -890,6 +916,9 @@ extern "C" int gemm_b200_gemm_mxfp8_cfg(const void* Aq, const void* SFA, const v
       // 64 tiles of 256 columns up the wider tile wins again)
       const int64_t units256 = ceil_div64(M, 2 * tc::kBlockM) * ceil_div64(N, tc::kBlockN);
       config = (4 * units256 <= (int64_t)di.sms) ? tc::kN128MxConfig : tc::kDefaultMxConfig;
+      // several rounds of units: hand them out at run time (GEMM_B200_MXFP8_DYNAMIC=0: static schedule)
+      static const bool dyn_ok = env_int("GEMM_B200_MXFP8_DYNAMIC", 1) != 0;
+      if (dyn_ok && config == tc::kDefaultMxConfig && 2 * units256 > (int64_t)di.sms) config = tc::kDynMxConfig;
       // a handful of tiles and a very long K (e.g. 256 x 65536 x 256): only K splits put the GPU to work
       const int64_t tiles_1cta = ceil_div64(M, tc::kBlockM) * ceil_div64(N, tc::kBlockN);
       if (8 * tiles_1cta <= (int64_t)di.sms && K >= 16384 && N % 4 == 0) {

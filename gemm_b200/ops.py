@@ -14,7 +14,7 @@ from . import _lib
 from ._lib import lib, check
 
 __all__ = [
-    "sgemm_f32", "gemm_bf16", "check_status", "sgemm_f32_host", "gemm_bf16_host",
+    "sgemm_f32", "sgemm_f32_batched", "gemm_bf16", "gemm_bf16_batched", "check_status", "sgemm_f32_host", "gemm_bf16_host",
     "sgemm_f32_configs", "gemm_bf16_configs", "launch_count",
     "quantize_mxfp8", "gemm_mxfp8", "gemm_mxfp8_configs", "MxFp8Tensor", "gemm_mxfp8_splitk", "gemm_mxfp8_auto_splits", "gemm_mxfp8_quant_out",
 ]
@@ -148,6 +148,33 @@ def gemm_bf16_batched(A: torch.Tensor, B: torch.Tensor, out: torch.Tensor | None
             A.data_ptr(), B.data_ptr(), out.data_ptr(), batch, M, N, K, lda, ldb, ldc, sa, sb, sc,
             _lib.B_ROW_MAJOR_NK if b_is_nk else _lib.B_ROW_MAJOR_KN,
             _lib.OUT_F32 if out_dtype == torch.float32 else _lib.OUT_BF16, _stream(A)))
+    return out
+
+
+def sgemm_f32_batched(A: torch.Tensor, B: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
+    """``out[i] = A[i] @ B[i]`` for a batch of equally shaped FP32 problems in one launch, each
+    bit-identical to ``sgemm_f32``.  ``A`` is ``[batch, M, K]``; ``B`` is ``[batch, K, N]`` or a
+    single 2-D matrix shared by every problem."""
+    _require(A.is_cuda and B.is_cuda, "A and B must be CUDA tensors")
+    _require(A.dtype == torch.float32 and B.dtype == torch.float32, "expected float32")
+    _require(A.dim() == 3 and B.dim() in (2, 3), "A must be 3-D and B 2-D or 3-D")
+    batch, M, K = (int(x) for x in A.shape)
+    N = int(B.shape[-1])
+    _require(B.shape[-2] == K and (B.dim() == 2 or B.shape[0] == batch), f"A is {tuple(A.shape)} but B is {tuple(B.shape)}")
+    lda, sa = _batch_layout(A)
+    if B.dim() == 3:
+        ldb, sb = _batch_layout(B)
+        if batch > 1:
+            _require(sb != 0, "pass a shared B as a 2-D tensor")
+    else:
+        ldb, sb = _row_major_ld(B), 0
+    if out is None:
+        out = torch.empty((batch, M, N), device=A.device, dtype=torch.float32)
+    _require(out.is_cuda and out.dtype == torch.float32 and tuple(out.shape) == (batch, M, N), "bad out tensor")
+    ldc, sc = _batch_layout(out)
+    with _OnDevice(A.device):
+        check(lib.gemm_b200_sgemm_f32_batched(A.data_ptr(), B.data_ptr(), out.data_ptr(), batch, M, N, K, lda, ldb, ldc,
+                                              sa, sb, sc, _stream(A)))
     return out
 
 

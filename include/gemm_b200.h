@@ -66,6 +66,16 @@ int gemm_b200_sgemm_f32_cfg(const float* A, const float* B, float* C,
                             int64_t M, int64_t N, int64_t K,
                             int64_t lda, int64_t ldb, int64_t ldc,
                             int config, void* stream);
+/* Strided-batched form: `batch` independent problems of one shape,
+ *   C_i[M,N] = A_i[M,K] @ B_i[K,N],   X_i = X + i * stride_x (strides in elements),
+ * each with the arithmetic of gemm_b200_sgemm_f32 (bit-identical to one call per problem).
+ * The reference multiplies one pair of matrices per call (naive/naive.cpp:6-22); this is the
+ * loop a caller would write around it, as one launch.  stride_a == 0 or stride_b == 0 shares
+ * that operand between the problems; the C matrices must not overlap. */
+int gemm_b200_sgemm_f32_batched(const float* A, const float* B, float* C, int64_t batch,
+                                int64_t M, int64_t N, int64_t K,
+                                int64_t lda, int64_t ldb, int64_t ldc,
+                                int64_t stride_a, int64_t stride_b, int64_t stride_c, void* stream);
 int gemm_b200_sgemm_f32_num_configs(void);
 const char* gemm_b200_sgemm_f32_config_name(int config);
 

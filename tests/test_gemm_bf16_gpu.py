@@ -149,3 +149,22 @@ def test_splitk_rejects_a_small_scratch(ops):
     rc = L.lib.gemm_b200_gemm_bf16_splitk(A.data_ptr(), B.data_ptr(), C.data_ptr(), 128, 256, 1024, 1024, 256, 256,
                                           L.B_ROW_MAJOR_KN, L.OUT_BF16, 4, scratch.data_ptr(), 1024, 0)
     assert rc == L.ERR_INVALID_ARG and b"scratch" in L.lib.gemm_b200_last_error()
+
+
+@pytest.mark.parametrize("name", ["2cta_256x256x64_s6_tmastore_maskcommit", "2cta_256x512x64_s3_tmastore2_maskcommit"])
+def test_runtime_unit_handout_matches_the_static_schedule(ops, oracle, name):
+    """Many short units per cluster (2048 of 256 x 256, K = 128: about 28 per cluster), so the ring
+    that carries the adopted unit indices wraps; every unit must be computed exactly once."""
+    M, K, N = 16384, 128, 8192
+    g = torch.Generator(device="cuda").manual_seed(4)
+    A = torch.randn(M, K, device="cuda", generator=g).bfloat16()
+    B = torch.randn(K, N, device="cuda", generator=g).bfloat16()
+    names = ops.gemm_bf16_configs()
+    static = ops.gemm_bf16(A, B, config=names.index(name))
+    for _ in range(3):
+        dyn = torch.full((M, N), float("nan"), device="cuda", dtype=torch.bfloat16)
+        ops.gemm_bf16(A, B, dyn, config=names.index(name + "_dynamic"))
+        ops.check_status()
+        assert torch.equal(dyn, static)
+    rows = torch.tensor([0, 255, 256, 8191, M - 1])
+    torch.testing.assert_close(static[rows].float().cpu(), oracle.bf16_matmul_oracle(A[rows], B), rtol=2e-2, atol=2e-2)

@@ -185,3 +185,30 @@ def test_log_and_forced_config_knobs(oracle):
     r = subprocess.run([sys.executable, "-c", code], env=env, capture_output=True, text=True, cwd=str(__import__("pathlib").Path(__file__).resolve().parent.parent))
     assert r.returncode == 0, r.stderr
     assert "[gemm_b200] sgemm_f32 256x64x256 -> 64x128x32_s3_f32x2" in r.stderr
+
+
+@pytest.mark.parametrize("batch,M,K,N", [(3, 70, 52, 44), (5, 128, 64, 256), (2, 1, 9, 3), (7, 200, 33, 130)])
+def test_strided_batched_equals_one_call_per_problem(ops, oracle, batch, M, K, N):
+    g = torch.Generator().manual_seed(batch * 100 + M)
+    A = torch.rand(batch, M, K, generator=g) * 2 - 1
+    B = torch.rand(batch, K, N, generator=g) * 2 - 1
+    got = ops.sgemm_f32_batched(A.cuda(), B.cuda()).cpu()
+    for i in range(batch):
+        assert torch.equal(got[i], oracle.sgemm_seq(A[i], B[i]))
+    shared = ops.sgemm_f32_batched(A.cuda(), B[0].cuda()).cpu()         # one B for every problem
+    for i in range(batch):
+        assert torch.equal(shared[i], oracle.sgemm_seq(A[i], B[0]))
+    # padded pitches and batch strides; bytes between the matrices stay untouched
+    Cbig = torch.full((batch, M + 3, N + 5), -7.0, device="cuda")
+    ops.sgemm_f32_batched(A.cuda(), B.cuda(), Cbig[:, 1:M + 1, 2:N + 2])
+    assert torch.equal(Cbig[:, 1:M + 1, 2:N + 2].cpu(), got)
+    mask = torch.ones_like(Cbig, dtype=torch.bool); mask[:, 1:M + 1, 2:N + 2] = False
+    assert bool((Cbig[mask] == -7.0).all())
+
+
+def test_strided_batched_argument_errors(ops):
+    import gemm_b200._lib as L
+    A = torch.zeros(2, 4, 4, device="cuda")
+    rc = L.lib.gemm_b200_sgemm_f32_batched(A.data_ptr(), A.data_ptr(), A.data_ptr(), 2, 4, 4, 4, 4, 4, 4, 8, 16, 16, None)
+    assert rc == L.ERR_INVALID_ARG and "stride" in L.last_error()
+    assert L.lib.gemm_b200_sgemm_f32_batched(None, None, None, 0, 4, 4, 4, 4, 4, 4, 16, 16, 16, None) == L.OK

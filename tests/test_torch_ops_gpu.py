@@ -21,6 +21,20 @@ def test_custom_ops_match_direct_calls(ops, oracle):
     assert torch.equal(c3, ops.gemm_bf16_batched(A3, Bb.cuda())) and c3.shape == (3, 256, 264)
 
 
+def test_mxfp8_custom_ops_match_direct_calls(ops, oracle):
+    import gemm_b200.torch_ops  # noqa: F401
+    Ab, Bb = oracle.gen_randn_bf16(256, 512, 384, seed=3)
+    aq, asf = torch.ops.gemm_b200.quantize_mxfp8(Ab.cuda())
+    bq, bsf = torch.ops.gemm_b200.quantize_mxfp8(Bb.cuda(), True)
+    A = ops.quantize_mxfp8(Ab.cuda()); B = ops.quantize_mxfp8(Bb.cuda(), transposed_in=True)
+    assert torch.equal(aq, A.data) and torch.equal(asf, A.scales) and torch.equal(bq, B.data) and torch.equal(bsf, B.scales)
+    got = torch.ops.gemm_b200.gemm_mxfp8(aq, asf, bq, bsf, True)
+    ops.check_status()
+    assert torch.equal(got, ops.gemm_mxfp8(A, B, out_dtype=torch.float32))
+    qa, sa = oracle.mxfp8_quantize(Ab); qb, sb = oracle.mxfp8_quantize(Bb.t().contiguous())
+    assert oracle.rel_frobenius(got.cpu(), oracle.mxfp8_matmul_oracle(qa, sa, qb, sb)) <= 1e-3
+
+
 def test_fake_tensor_shapes():
     import gemm_b200.torch_ops  # noqa: F401
     from torch._subclasses.fake_tensor import FakeTensorMode
@@ -32,3 +46,7 @@ def test_fake_tensor_shapes():
         assert out.shape == (64, 48) and out.dtype == torch.float32
         A3 = torch.empty(5, 64, 32, device="cuda", dtype=torch.bfloat16)
         assert torch.ops.gemm_b200.gemm_bf16_batched(A3, Bt, True, False).shape == (5, 64, 48)
+        aq, asf = torch.ops.gemm_b200.quantize_mxfp8(Ab)
+        bq, bsf = torch.ops.gemm_b200.quantize_mxfp8(Bt)
+        assert aq.shape == (64, 32) and asf.shape == (512,) and bq.shape == (48, 32)
+        assert torch.ops.gemm_b200.gemm_mxfp8(aq, asf, bq, bsf).shape == (64, 48)

@@ -66,17 +66,28 @@ def test_current_stream_is_honoured():
     assert torch.equal(D, f(A, B, torch.zeros(512, 512, device="cuda")) * 2)
 
 
-def test_reference_style_two_file_jit_build(tmp_path, monkeypatch, oracle):
+# variant -> (module name, sources, exported function) exactly as the reference's scripts pass them to load()
+# (naive/test.py:5-11, shared/test.py:5-11, blocktile_1d/test.py:5-11)
+JIT = {
+    "naive": ("naive_gemm_cuda", ["naive.cpp", "naive_1.cu"], "naive_gemm"),
+    "shared": ("shared_gemm", ["shared.cpp", "shared_2.cu"], "gemm_cuda"),
+    "blocktile_1d": ("blocktile_1d", ["blocktile_1d.cpp", "blocktile_1d.cu"], "gemm_cuda"),
+}
+
+
+@pytest.mark.parametrize("variant", ["naive", "shared", "blocktile_1d"])
+def test_reference_style_two_file_jit_build(tmp_path, monkeypatch, oracle, variant):
     """The reference's scripts build their module with a two-file load() from the variant's
-    directory (naive/test.py:5-11).  The same call, unchanged, must work from ours."""
+    directory.  The same call, unchanged, must work from ours, for every variant."""
     from pathlib import Path
     from torch.utils.cpp_extension import load
     import gemm_b200
+    name, sources, fn = JIT[variant]
     monkeypatch.setenv("TORCH_EXTENSIONS_DIR", str(tmp_path))
-    monkeypatch.chdir(Path(gemm_b200.__file__).parent / "variants" / "shared")
+    monkeypatch.chdir(Path(gemm_b200.__file__).parent / "variants" / variant)
     custom_gemm = load(
-        name='shared_gemm',
-        sources=['shared.cpp', 'shared_2.cu'],
+        name=name,
+        sources=sources,
         extra_cuda_cflags=['-O3', '--use_fast_math'],
         extra_cflags=['-O3'],
         verbose=False
@@ -85,7 +96,7 @@ def test_reference_style_two_file_jit_build(tmp_path, monkeypatch, oracle):
     A = torch.randn(512, 512, device='cuda', dtype=torch.float32)
     B = torch.randn(512, 512, device='cuda', dtype=torch.float32)
     C = torch.zeros(512, 512, device='cuda', dtype=torch.float32)
-    result = custom_gemm.gemm_cuda(A, B, C)
+    result = getattr(custom_gemm, fn)(A, B, C)
     expected = torch.matmul(A, B)
     assert oracle.rel_frobenius(result, expected) <= 1e-5
     assert torch.equal(result.cpu(), oracle.sgemm_seq(A.cpu(), B.cpu()))
