@@ -156,9 +156,10 @@ struct GemmShape {
   // problems share one (batch stride 0).  c_batch_stride: elements between the C matrices.
   int batch, a_z, b_z;
   int64_t c_batch_stride;
-  // L2 eviction priority of the operand loads (BF16 kernel): bit 0 = A tiles evict-first, bit 1 = B
-  // tiles evict-last, bit 2 = A evict-last, bit 3 = B evict-first; 0 = no hint
-  int l2_hint;
+  // BF16 kernel: load A tiles with L2 priority evict-first and B tiles evict-last.  Set for
+  // problems whose raster band lasts many rounds of units: there the band's B panel is re-read
+  // every round while an A tile is needed only by the clusters of one round.
+  int l2_stream_a_keep_b;
 };
 
 __device__ __forceinline__ void tile_coord(int t, const GemmShape& sh, int& tm, int& tn) {
@@ -257,10 +258,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     // The whole warp walks the schedule (coordinates and addresses stay warp-uniform); one
     // elected lane issues the copies.
     const bool issuer = elect_one();
-    const uint64_t pol_a = (shape.l2_hint & 1) ? l2_policy_evict_first() : (shape.l2_hint & 4) ? l2_policy_evict_last() : 0ull;
-    const uint64_t pol_b = (shape.l2_hint & 2) ? l2_policy_evict_last() : (shape.l2_hint & 8) ? l2_policy_evict_first() : 0ull;
+    const bool hinted = shape.l2_stream_a_keep_b != 0;
+    const uint64_t pol_a = hinted ? l2_policy_evict_first() : 0ull, pol_b = hinted ? l2_policy_evict_last() : 0ull;
     auto load_p = [&](uint32_t dst, const CUtensorMap* map, int x, int y, int z, uint32_t bar, uint64_t pol) {
-      if (pol != 0ull) {
+      if (hinted) {
         if constexpr (CG == 1) tma_load_3d_hint(dst, map, x, y, z, bar, pol);
         else tma_load_3d_pair_hint(dst, map, x, y, z, bar, pol);
       } else {

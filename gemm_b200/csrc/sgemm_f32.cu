@@ -46,13 +46,8 @@ __device__ __forceinline__ void cp_async_wait() {
   asm volatile("cp.async.wait_group %0;\n" ::"n"(N));
 }
 
-// ADUP: every element of the A tile is stored twice in shared memory ({a, a}), so that one LDS.128
-//       delivers two ready-made operands of the packed multiply-add (which wants the A value in
-//       both halves of a 64-bit register pair) and the loop needs no register moves to build them.
-//       The tile is filled by 4-byte cp.async, two per element.
-template <int BM_, int BN_, int BK_, int WMW_, int WNW_, int STAGES_, int MINB_, bool X2_, int AK_ = 2, bool ADUP_ = false>
+template <int BM_, int BN_, int BK_, int WMW_, int WNW_, int STAGES_, int MINB_, bool X2_, int AK_ = 2>
 struct Cfg {
-  static constexpr bool ADUP = ADUP_;
   static constexpr int AK = AK_;              // k-width of one A fragment load (2: LDS.64, 4: LDS.128)
   static constexpr int BM = BM_, BN = BN_, BK = BK_, WMW = WMW_, WNW = WNW_;
   static constexpr int STAGES = STAGES_, MINB = MINB_;
@@ -60,13 +55,12 @@ struct Cfg {
   static constexpr int THREADS = WMW * WNW * 32;
   static constexpr int TM = BM / (WMW * 4);   // rows per thread (interleaved by 4)
   static constexpr int TN = BN / (WNW * 8);   // columns per thread (float4 groups, 32 apart)
-  static constexpr int LDA_S = (ADUP ? 2 * BK : BK) + 4;   // padded row of the A tile, in floats
+  static constexpr int LDA_S = BK + 4;        // padded row of the A tile, in floats
   static constexpr int A_STAGE = BM * LDA_S;
   static constexpr int B_STAGE = BK * BN;
   static constexpr int SMEM_BYTES = STAGES * (A_STAGE + B_STAGE) * 4;
   static_assert(TM >= 1 && TN >= 4 && TN % 4 == 0, "thread tile");
   static_assert(BK % 4 == 0, "BK");
-  static_assert(!ADUP || (X2 && AK == 2), "duplicated A serves the packed multiply-add, two k per load");
   static_assert(((LDA_S / 4) & 1) == 1, "A row stride must be an odd number of 16-byte units");
 };
 
@@ -123,31 +117,14 @@ sgemm_kernel(const float* __restrict__ A, const float* __restrict__ B, float* __
 
   auto load_tile = [&](int kt, int slot) {
     const int k0 = kt * BK;
-    if constexpr (C::ADUP) {
-      // one element per thread and pass, consecutive threads on consecutive k; stored twice
-      const uint32_t a_base = smem_u32(sA + slot * C::A_STAGE);
-#pragma unroll
-      for (int it = 0; it < (BM * BK + THREADS - 1) / THREADS; ++it) {
-        const int c = tid + it * THREADS;
-        if ((BM * BK) % THREADS != 0 && c >= BM * BK) break;
-        const int r = c / BK, kc = c % BK;
-        const bool ok = (row0 + r < M) && (k0 + kc < K);
-        const float* src = ok ? (A + (int64_t)(row0 + r) * lda + (k0 + kc)) : A;
-        const uint32_t dst = a_base + (r * LDA_S + 2 * kc) * 4;
-        cp_async4(dst, src, ok ? 4 : 0);
-        cp_async4(dst + 4, src, ok ? 4 : 0);
-      }
-    }
     if constexpr (VEC == 4) {
       const bool a_k_ok = (k0 + a_kc) < K;
-      if constexpr (!C::ADUP) {
 #pragma unroll
-        for (int it = 0; it < A_IT; ++it) {
-          if (!A_EVEN && a_r + it * A_RPI >= BM) break;
-          const bool ok = a_k_ok && (row0 + a_r + it * A_RPI < M);
-          const float* src = a_src + (int64_t)(it * A_RPI) * lda + k0;
-          cp_async16(a_sdst + (slot * C::A_STAGE + it * A_RPI * LDA_S) * 4, ok ? src : A, ok ? 16 : 0);
-        }
+      for (int it = 0; it < A_IT; ++it) {
+        if (!A_EVEN && a_r + it * A_RPI >= BM) break;
+        const bool ok = a_k_ok && (row0 + a_r + it * A_RPI < M);
+        const float* src = a_src + (int64_t)(it * A_RPI) * lda + k0;
+        cp_async16(a_sdst + (slot * C::A_STAGE + it * A_RPI * LDA_S) * 4, ok ? src : A, ok ? 16 : 0);
       }
 #pragma unroll
       for (int it = 0; it < B_IT; ++it) {
@@ -158,17 +135,15 @@ sgemm_kernel(const float* __restrict__ A, const float* __restrict__ B, float* __
     } else {
       float* a_dst = sA + slot * C::A_STAGE;
       float* b_dst = sB + slot * C::B_STAGE;
-      if constexpr (!C::ADUP) {
 #pragma unroll 4
-        for (int it = 0; it < (BM * BK + THREADS - 1) / THREADS; ++it) {
-          const int c = tid + it * THREADS;
-          if ((BM * BK) % THREADS != 0 && c >= BM * BK) break;
-          const int r = c / BK, kc = c % BK;
-          const int gr = row0 + r, gk = k0 + kc;
-          const bool ok = (gr < M) && (gk < K);
-          const float* src = ok ? (A + (int64_t)gr * lda + gk) : A;
-          cp_async4(smem_u32(a_dst + r * LDA_S + kc), src, ok ? 4 : 0);
-        }
+      for (int it = 0; it < (BM * BK + THREADS - 1) / THREADS; ++it) {
+        const int c = tid + it * THREADS;
+        if ((BM * BK) % THREADS != 0 && c >= BM * BK) break;
+        const int r = c / BK, kc = c % BK;
+        const int gr = row0 + r, gk = k0 + kc;
+        const bool ok = (gr < M) && (gk < K);
+        const float* src = ok ? (A + (int64_t)gr * lda + gk) : A;
+        cp_async4(smem_u32(a_dst + r * LDA_S + kc), src, ok ? 4 : 0);
       }
 #pragma unroll 4
       for (int it = 0; it < BK * BN / THREADS; ++it) {
@@ -213,15 +188,9 @@ sgemm_kernel(const float* __restrict__ A, const float* __restrict__ B, float* __
 #pragma unroll
     for (int kq = 0; kq < BK / AK; ++kq) {
       float af[TM][AK];
-      float2 af2[TM][AK];   // ADUP: the operand pairs as they come out of shared memory
 #pragma unroll
       for (int i = 0; i < TM; ++i) {
-        if constexpr (C::ADUP) {
-          const float4 v = *reinterpret_cast<const float4*>(a_s + (4 * i) * LDA_S + kq * 4);
-          af2[i][0] = make_float2(v.x, v.y);
-          af2[i][1] = make_float2(v.z, v.w);
-          af[i][0] = v.x; af[i][1] = v.z;
-        } else if constexpr (AK == 4) {
+        if constexpr (AK == 4) {
           const float4 v = *reinterpret_cast<const float4*>(a_s + (4 * i) * LDA_S + kq * 4);
           af[i][0] = v.x; af[i][1] = v.y; af[i][2] = v.z; af[i][3] = v.w;
         } else {
@@ -239,7 +208,7 @@ sgemm_kernel(const float* __restrict__ A, const float* __restrict__ B, float* __
         for (int i = 0; i < TM; ++i) {
           const float a = af[i][kk];
           if constexpr (C::X2) {
-            const float2 a2 = C::ADUP ? af2[i][kk] : make_float2(a, a);
+            const float2 a2 = make_float2(a, a);
 #pragma unroll
             for (int c = 0; c < TNC; ++c) {
               acc2[i][2 * c + 0] = __ffma2_rn(a2, make_float2(bf[c].x, bf[c].y), acc2[i][2 * c + 0]);
@@ -334,22 +303,8 @@ using C32x64k32p       = Cfg<32, 64, 32, 2, 2, 4, 6, true>;
 // Tile heights of 28 and 56 rows: 148 SMs = 4 x 37, and 37 tiles of 28 rows cover 1024 rows (74 of
 // 28 or 37 of 56 cover 2048, ...), so power-of-two problems split into a whole number of tiles per
 // SM instead of leaving a third of the SMs one tile short.  7 rows x 8 (or 4) columns per thread.
-using C28x256k32p      = Cfg<28, 256, 32, 1, 4, 3, 1, true>;
 using C28x128k32p      = Cfg<28, 128, 32, 1, 4, 4, 2, true>;
-using C28x256k32pw8    = Cfg<28, 256, 32, 1, 8, 3, 1, true>;
-using C56x256k16p      = Cfg<56, 256, 16, 2, 4, 4, 2, true>;
-using C56x256k32p      = Cfg<56, 256, 32, 2, 4, 3, 1, true>;
 using C56x128k32p      = Cfg<56, 128, 32, 2, 2, 3, 3, true>;
-using C28x64k32p       = Cfg<28, 64, 32, 1, 2, 4, 4, true>;
-using C28x128k32pd     = Cfg<28, 128, 32, 1, 4, 4, 2, true, 2, true>;
-using C64x128k32pd     = Cfg<64, 128, 32, 2, 2, 3, 2, true, 2, true>;
-using C64x64k32pd      = Cfg<64, 64, 32, 2, 2, 4, 4, true, 2, true>;
-using C56x128k32pd     = Cfg<56, 128, 32, 2, 2, 3, 2, true, 2, true>;
-using C32x64k32pd      = Cfg<32, 64, 32, 2, 2, 4, 6, true, 2, true>;
-using C28x128k32ps3    = Cfg<28, 128, 32, 1, 4, 3, 2, true>;
-using C28x128k16ps6    = Cfg<28, 128, 16, 1, 4, 6, 2, true>;
-using C28x128k32pa4    = Cfg<28, 128, 32, 1, 4, 4, 2, true, 4>;
-using C28x128k32       = Cfg<28, 128, 32, 1, 4, 4, 2, false>;
 #ifdef GEMM_B200_TUNING
 // tile shapes the heuristic never picks; built only for tuning sweeps
 using C128x128k16      = Cfg<128, 128, 16, 4, 2, 3, 2, false>;
@@ -364,28 +319,23 @@ using C64x64k16p       = Cfg<64, 64, 16, 2, 2, 4, 4, true>;
 using C64x64k16        = Cfg<64, 64, 16, 2, 2, 4, 4, false>;
 using C32x64k16p       = Cfg<32, 64, 16, 2, 2, 4, 6, true>;
 using C128x128k32      = Cfg<128, 128, 32, 4, 2, 3, 2, false>;
+using C28x256k32p      = Cfg<28, 256, 32, 1, 4, 3, 1, true>;
+using C28x256k32pw8    = Cfg<28, 256, 32, 1, 8, 3, 1, true>;
+using C56x256k16p      = Cfg<56, 256, 16, 2, 4, 4, 2, true>;
+using C56x256k32p      = Cfg<56, 256, 32, 2, 4, 3, 1, true>;
+using C28x64k32p       = Cfg<28, 64, 32, 1, 2, 4, 4, true>;
+using C28x128k32ps3    = Cfg<28, 128, 32, 1, 4, 3, 2, true>;
+using C28x128k16ps6    = Cfg<28, 128, 16, 1, 4, 6, 2, true>;
+using C28x128k32pa4    = Cfg<28, 128, 32, 1, 4, 4, 2, true, 4>;
+using C28x128k32       = Cfg<28, 128, 32, 1, 4, 4, 2, false>;
 #endif
 
 static const ConfigEntry kConfigs[] = {
     {"64x128x32_s3_f32x2", 64, 128, launch_cfg<C64x128k32p3>},
     {"64x64x32_s4_f32x2", 64, 64, launch_cfg<C64x64k32p>},
     {"32x64x32_s4_f32x2", 32, 64, launch_cfg<C32x64k32p>},
-    {"28x256x32_s3_f32x2", 28, 256, launch_cfg<C28x256k32p>},
     {"28x128x32_s4_f32x2", 28, 128, launch_cfg<C28x128k32p>},
-    {"28x256x32_s3_f32x2_w8", 28, 256, launch_cfg<C28x256k32pw8>},
-    {"56x256x16_s4_f32x2", 56, 256, launch_cfg<C56x256k16p>},
-    {"56x256x32_s3_f32x2", 56, 256, launch_cfg<C56x256k32p>},
     {"56x128x32_s3_f32x2", 56, 128, launch_cfg<C56x128k32p>},
-    {"28x64x32_s4_f32x2", 28, 64, launch_cfg<C28x64k32p>},
-    {"28x128x32_s4_f32x2_adup", 28, 128, launch_cfg<C28x128k32pd>},
-    {"64x128x32_s3_f32x2_adup", 64, 128, launch_cfg<C64x128k32pd>},
-    {"64x64x32_s4_f32x2_adup", 64, 64, launch_cfg<C64x64k32pd>},
-    {"56x128x32_s3_f32x2_adup", 56, 128, launch_cfg<C56x128k32pd>},
-    {"32x64x32_s4_f32x2_adup", 32, 64, launch_cfg<C32x64k32pd>},
-    {"28x128x32_s3_f32x2", 28, 128, launch_cfg<C28x128k32ps3>},
-    {"28x128x16_s6_f32x2", 28, 128, launch_cfg<C28x128k16ps6>},
-    {"28x128x32_s4_f32x2_a4", 28, 128, launch_cfg<C28x128k32pa4>},
-    {"28x128x32_s4", 28, 128, launch_cfg<C28x128k32>},
 #ifdef GEMM_B200_TUNING
     {"128x128x16_s3", 128, 128, launch_cfg<C128x128k16>},
     {"128x128x16_s3_f32x2", 128, 128, launch_cfg<C128x128k16p>},
@@ -399,6 +349,15 @@ static const ConfigEntry kConfigs[] = {
     {"64x64x16_s4", 64, 64, launch_cfg<C64x64k16>},
     {"32x64x16_s4_f32x2", 32, 64, launch_cfg<C32x64k16p>},
     {"128x128x32_s3", 128, 128, launch_cfg<C128x128k32>},
+    {"28x256x32_s3_f32x2", 28, 256, launch_cfg<C28x256k32p>},
+    {"28x256x32_s3_f32x2_w8", 28, 256, launch_cfg<C28x256k32pw8>},
+    {"56x256x16_s4_f32x2", 56, 256, launch_cfg<C56x256k16p>},
+    {"56x256x32_s3_f32x2", 56, 256, launch_cfg<C56x256k32p>},
+    {"28x64x32_s4_f32x2", 28, 64, launch_cfg<C28x64k32p>},
+    {"28x128x32_s3_f32x2", 28, 128, launch_cfg<C28x128k32ps3>},
+    {"28x128x16_s6_f32x2", 28, 128, launch_cfg<C28x128k16ps6>},
+    {"28x128x32_s4_f32x2_a4", 28, 128, launch_cfg<C28x128k32pa4>},
+    {"28x128x32_s4", 28, 128, launch_cfg<C28x128k32>},
 #endif
 };
 constexpr int kNumConfigs = sizeof(kConfigs) / sizeof(kConfigs[0]);
@@ -409,19 +368,28 @@ inline int config_index(const char* name) {
   return 0;
 }
 
-// Heuristic from sweeps of square problems on a B200 (TFLOP/s at n = 512 / 1024 / 2048 / 4096 /
-// 8192): 64x128x32: - / 40 / 48 / 56.5 / 57;  128x128x32: 5 / 22 / 47 / 55.6 / 56;  64x64x32:
-// 14 / 39 / 52 / 55 / 56;  32x64x32: 16 / 34 / 43 / 44 / 45.  So: 64x128x32 once it yields about
-// four tiles per SM, 64x64x32 while those tiles still fill the SMs, 32x64x32 below that.  Other
-// thread-tile shapes at 128x128x32 (4x16: 54.6, 16x4: 46.5 TFLOP/s at 4096) did not beat 8x8.
+// Tile choice: the CTAs of a launch spread evenly over the SMs, so the launch takes
+//   ceil(tiles / SMs) x (time of one tile),   time of one tile ~ BM x BN / (rate of that tile shape),
+// with the rates measured at 8192^3 on a B200 (TFLOP/s): 64x128 57.3, 56x128 56.5, 64x64 55.5,
+// 28x128 51.5, 32x64 44.5.  The estimate ranks the five shapes as the measurements do at 512^3 ...
+// 8192^3 (n = 1024: 28x128 53 us, 64x128 / 64x64 59, 32x64 68, 56x128 90; n = 2048: 56x128 329 us,
+// 64x64 339, 28x128 356, 64x128 363, 32x64 410).  28- and 56-row tiles exist because 148 SMs =
+// 4 x 37 and 37 x 28 covers 1024 rows: power-of-two problems then split into whole tiles per SM.
 inline int pick_config(int64_t M, int64_t N, int num_sms, int64_t batch = 1) {
-  static const int large = config_index("64x128x32_s3_f32x2"), medium = config_index("64x64x32_s4_f32x2"),
-                   small = config_index("32x64x32_s4_f32x2");
-  const int64_t t_large = batch * ceil_div64(M, 64) * ceil_div64(N, 128);
-  if (t_large >= 4 * (int64_t)num_sms) return large;
-  const int64_t t64 = batch * ceil_div64(M, 64) * ceil_div64(N, 64);
-  if (t64 >= (int64_t)num_sms + num_sms / 2) return medium;
-  return small;
+  struct Cand { const char* name; int bm, bn; double rate; };
+  static const Cand cands[] = {{"64x128x32_s3_f32x2", 64, 128, 57.3}, {"56x128x32_s3_f32x2", 56, 128, 56.5},
+                               {"64x64x32_s4_f32x2", 64, 64, 55.5},  {"28x128x32_s4_f32x2", 28, 128, 51.5},
+                               {"32x64x32_s4_f32x2", 32, 64, 44.5}};
+  static const int index[5] = {config_index(cands[0].name), config_index(cands[1].name), config_index(cands[2].name),
+                               config_index(cands[3].name), config_index(cands[4].name)};
+  int best = 0;
+  double best_t = 0.0;
+  for (int i = 0; i < 5; ++i) {
+    const int64_t tiles = batch * ceil_div64(M, cands[i].bm) * ceil_div64(N, cands[i].bn);
+    const double t = (double)ceil_div64(tiles, num_sms) * cands[i].bm * cands[i].bn / cands[i].rate;
+    if (i == 0 || t < best_t * 0.999) { best = i; best_t = t; }
+  }
+  return index[best];
 }
 
 }  // namespace f32

@@ -257,7 +257,7 @@ __device__ __forceinline__ void tma_load_3d_pair(uint32_t dst, const CUtensorMap
       ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(cluster_bar), "r"(x), "r"(y), "r"(z)
       : "memory");
 }
-// The same load with an L2 eviction-priority policy (from l2_policy_*()).
+// The same loads with an L2 eviction-priority policy (l2_policy_evict_first / _last).
 __device__ __forceinline__ void tma_load_3d_hint(uint32_t dst, const CUtensorMap* map, int x, int y, int z, uint32_t bar,
                                                  uint64_t policy) {
   asm volatile(

@@ -112,25 +112,29 @@ static int make_map_3d(CUtensorMap* map, CUtensorMapDataType dt, int elem_bytes,
   return GEMM_B200_OK;
 }
 
-// Band width of the tile raster.  GEMM_B200_RASTER_GROUP overrides it (tuning knob): n > 0 =
-// bands of n row tiles, n < 0 = bands of -n column tiles.
-static int raster_group_for(int tiles_m, int tiles_n, int64_t col_tile_bytes = 0) {
+// Band width of the tile raster: bands of column tiles, walked column-fastest (on B200 1-5 %
+// faster and 10-20 % less DRAM traffic than bands of row tiles).  The band's B panel
+// (`col_tile_bytes` per column tile) is sized near 32 MB so that it survives in the L2 from one
+// round of units to the next, but a band is never narrower than `min_cols` columns of C.
+// Measured with units handed out at run time, BF16, TFLOP/s in a loop:
+//   131072 x 8192 x 8192, 512-wide tiles: bands of 4 / 6 / 8 / 16 tiles 1420 / 1414 / 1386 / 1277
+//   (DRAM 13.6 / - / 14.7 / - GB per launch); 32768 x 4096 x 4096: 4 / 8 / 16 tiles 1576 / 1591 /
+//   1611; 256-wide tiles, K = 8192: 2 / 4 / 8 tiles 1431 / 1511 / 1544.
+// MXFP8 16384 x 8192 x 28672 (256-wide tiles): bands of 14-16 tiles 2940-2957, of 8: 2917, of 28: 2807.
+// GEMM_B200_RASTER_GROUP overrides it (tuning knob): n > 0 = bands of n row tiles, n < 0 = bands
+// of -n column tiles.
+static int raster_group_for(int64_t col_tile_bytes, int tile_cols, int min_cols) {
   static const int forced = [] {
     const char* e = getenv("GEMM_B200_RASTER_GROUP");
     return e ? atoi(e) : 0;
   }();
   if (forced != 0) return forced;
-  (void)tiles_m;
-  (void)tiles_n;
-  // bands of column tiles, walked column-fastest: on B200 this measured 1-5 % faster and
-  // 10-20 % less DRAM traffic than bands of 8 row tiles (8192^3 and 131072 x 8192 x 8192, bf16)
-  if (col_tile_bytes > 0) {
-    // keep the band's B panel near 32 MB of the L2 (MXFP8 16384 x 8192 x 28672: bands of 14-16
-    // column tiles 2940-2957 TFLOP/s, of 8: 2917, of 28: 2807)
-    const int64_t g = (32ll << 20) / col_tile_bytes;
-    return -(int)(g < 4 ? 4 : g > 32 ? 32 : g);
-  }
-  return -8;
+  int64_t g = (32ll << 20) / (col_tile_bytes > 0 ? col_tile_bytes : 1);
+  const int64_t g_min = (min_cols + tile_cols - 1) / tile_cols;
+  if (g < g_min) g = g_min;
+  if (g < 4) g = 4;
+  if (g > 32) g = 32;
+  return -(int)g;
 }
 
 struct DeviceInfo {
@@ -369,13 +373,21 @@ static int launch_bf16(const Bf16Args& a) {
   shape.kb_per_split = (int)ceil_div64(num_kb, a.k_splits);
   shape.k_splits = (int)ceil_div64(num_kb, shape.kb_per_split);   // no empty split
   shape.split_stride = a.M * a.ldc;
-  shape.raster_group = raster_group_for(shape.tiles_m, shape.tiles_n);
+  shape.raster_group = raster_group_for((int64_t)Cfg::TILE_N * a.K * 2, Cfg::TILE_N, 2048);
   shape.batch = (int)a.batch;
   shape.a_z = a.stride_a ? 1 : 0;
   shape.b_z = a.stride_b ? 1 : 0;
   shape.c_batch_stride = a.batch > 1 ? a.stride_c : 0;
-  static const int l2_hint = env_int("GEMM_B200_BF16_L2HINT", 0);   // tuning knob, see GemmShape::l2_hint
-  shape.l2_hint = l2_hint;
+  // L2 priorities (A evict-first, B evict-last) when a raster band lasts at least three rounds of
+  // units.  Run-time hand-out only: on the static schedule clusters drift apart and an
+  // evict-first A tile is gone before the last of them asks for it.  Measured (TFLOP/s in a
+  // loop, without / with): 131072 x 8192 x 8192 (28 rounds per band) 1420 / 1428 with DRAM
+  // 14.8 -> 13.6 GB per launch; 32768 x 4096 x 4096 (14) 1591 / 1610; 16384 x 8192 x 8192 (3.5)
+  // 1609 / 1617; 8192^3 (1.7) 1600 / 1603; 8192 x 16384 x 4096 (1.7) 1521 / 1498.
+  {
+    const int64_t band = shape.raster_group < 0 ? (-shape.raster_group < shape.tiles_n ? -shape.raster_group : shape.tiles_n) : 0;
+    shape.l2_stream_a_keep_b = (Cfg::DYN && a.batch == 1 && band > 0 && (int64_t)shape.tiles_m * band >= 3 * (int64_t)max_clusters) ? 1 : 0;
+  }
   const int64_t num_tiles = (int64_t)shape.tiles_m * shape.tiles_n * a.batch * shape.k_splits;
   if (num_tiles > 0x7fffffff) return fail(GEMM_B200_ERR_TOO_LARGE, "gemm_bf16: too many tiles");
   // static schedule: one cluster per resident slot, each walks unit = cluster + i * clusters;
@@ -739,10 +751,10 @@ static int launch_mxfp8(const MxArgs& a) {
   shape.batch = 1;
   shape.a_z = shape.b_z = 0;
   shape.c_batch_stride = 0;
-  shape.l2_hint = 0;
+  shape.l2_stream_a_keep_b = 0;
   shape.k_splits = (int)ceil_div64(num_kb, shape.kb_per_split);   // no empty split
   shape.split_stride = a.M * a.N;
-  shape.raster_group = raster_group_for(shape.tiles_m, shape.tiles_n, (int64_t)Cfg::BN * a.K);
+  shape.raster_group = raster_group_for((int64_t)Cfg::BN * a.K, Cfg::BN, 0);
   const int64_t num_tiles = (int64_t)shape.tiles_m * shape.tiles_n * shape.k_splits;
   if (num_tiles > 0x7fffffff) return fail(GEMM_B200_ERR_TOO_LARGE, "gemm_mxfp8: too many tiles");
   const int clusters = Cfg::DYN ? (int)num_tiles : (int)(num_tiles < max_clusters ? num_tiles : max_clusters);

@@ -168,3 +168,27 @@ def test_runtime_unit_handout_matches_the_static_schedule(ops, oracle, name):
         assert torch.equal(dyn, static)
     rows = torch.tensor([0, 255, 256, 8191, M - 1])
     torch.testing.assert_close(static[rows].float().cpu(), oracle.bf16_matmul_oracle(A[rows], B), rtol=2e-2, atol=2e-2)
+
+
+@pytest.mark.parametrize("M,K,N", [(768, 640, 1280), (2048, 4096, 4096), (8192, 8192, 8192)])
+def test_against_an_independent_bf16_gemm(ops, M, K, N):
+    """Independent pin: cuBLAS (torch.matmul on the GPU, a checker here, never on the product path)
+    on the same bf16 operands.  Both accumulate in FP32 and round once to bf16, so the results can
+    differ only where the order of the FP32 additions moves a sum across a rounding boundary: FP32
+    outputs within 2e-6 relative, bf16 outputs one bf16 step apart in at most 1 element in 100."""
+    g = torch.Generator(device="cuda").manual_seed(M + K)
+    A = torch.randn(M, K, device="cuda", generator=g).bfloat16()
+    B = torch.randn(K, N, device="cuda", generator=g).bfloat16()
+    got32 = ops.gemm_bf16(A, B, out_dtype=torch.float32)
+    ops.check_status()
+    want32 = torch.matmul(A.float(), B.float())            # FP32 SGEMM of the same values (TF32 is off by default)
+    rel = float((got32.double() - want32.double()).norm() / want32.double().norm())
+    assert rel <= 2e-6
+    got16 = ops.gemm_bf16(A, B)
+    want16 = torch.matmul(A, B)
+    ops.check_status()
+    diff = got16 != want16
+    assert float(diff.float().mean()) <= 1e-2
+    a, b = got16[diff].float(), want16[diff].float()
+    # one bf16 step; sums that nearly cancel (|c| << sqrt(K)) get an absolute allowance instead
+    assert bool(((a - b).abs() <= 2.0 ** -7 * torch.maximum(a.abs(), b.abs()) + 1e-3).all())
