@@ -5,9 +5,11 @@ missing or does not load, importing this module raises."""
 from __future__ import annotations
 
 import ctypes as C
+import os
 from pathlib import Path
 
-LIB_PATH = Path(__file__).resolve().parent / "libgemm_b200.so"
+# GEMM_B200_LIB points at another build of the same library (e.g. a tuning build)
+LIB_PATH = Path(os.environ.get("GEMM_B200_LIB") or (Path(__file__).resolve().parent / "libgemm_b200.so"))
 
 OK = 0
 ERR_INVALID_ARG, ERR_ALIGNMENT, ERR_UNSUPPORTED, ERR_CUDA, ERR_TIMEOUT, ERR_TOO_LARGE = -1, -2, -3, -4, -5, -6
@@ -27,6 +29,7 @@ SIGNATURES = {
     "gemm_b200_gemm_bf16_cfg": (i32, [vp, vp, vp, i64, i64, i64, i64, i64, i64, i32, i32, i32, vp]),
     "gemm_b200_gemm_bf16_batched": (i32, [vp, vp, vp, i64, i64, i64, i64, i64, i64, i64, i64, i64, i64, i32, i32, vp]),
     "gemm_b200_gemm_bf16_splitk": (i32, [vp, vp, vp, i64, i64, i64, i64, i64, i64, i32, i32, i32, vp, sz, vp]),
+    "gemm_b200_gemm_bf16_cluster_splitk": (i32, [vp, vp, vp, i64, i64, i64, i64, i64, i64, i32, i32, i32, vp]),
     "gemm_b200_gemm_bf16_splitk_scratch_bytes": (sz, [i64, i64, i32]),
     "gemm_b200_gemm_bf16_auto_splits": (i32, [i64, i64, i64]),
     "gemm_b200_gemm_bf16_num_configs": (i32, []),

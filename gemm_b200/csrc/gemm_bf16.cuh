@@ -219,6 +219,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   };
 
   if (threadIdx.x == 0) {
+    trace_stamp(0);
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(full_bar(s), 1);
       mbar_init(empty_bar(s), 1);
@@ -250,6 +251,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   asm volatile("ld.shared.u32 %0, [%1];" : "=r"(tmem_base) : "r"(tmem_slot) : "memory");
   // split-K: lets the reduce kernel behind this one be scheduled early; it waits for this grid
   if (shape.k_splits > 1) pdl_launch_dependents();
+  if (threadIdx.x == 0) trace_stamp(1);
 
   bool failed = false;
 
@@ -293,6 +295,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         const uint32_t bar = (CG == 1) ? full_bar(s) : map_to_cta(full_bar(s), 0);
         if (issuer) {
           if (cta_rank == 0) mbar_arrive_expect_tx(full_bar(s), CG * Cfg::STAGE_BYTES);
+          if (it == 0) trace_stamp(2);
           load_p(a_dst, &tmA, kb * kBlockK, m0, az, bar, pol_a);
 #pragma unroll
           for (int nt = 0; nt < NT; ++nt) {
@@ -309,6 +312,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         __syncwarp();
       }
       if (failed) break;
+      if (issuer) trace_stamp(3);
       ++n;
       if constexpr (DYN) {
         u = (cta_rank == 0) ? ring.template fetch_and_publish<CG>(n, issuer) : ring.wait_unit(n, kRoleProducer);
@@ -352,6 +356,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           const uint32_t ph = (it / STAGES) & 1u;
           if (!mbar_wait_warp(full_bar(s), ph, kRoleMma, s)) { failed = true; break; }
           tc_fence_after_sync();
+          if (it == 0 && issuer) trace_stamp(4);
           const uint32_t a_addr = sA0 + s * Cfg::A_BYTES;
           const uint32_t first = kb != kb0 ? 1u : 0u;
           if (issuer) {
@@ -369,7 +374,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           __syncwarp();
         }
         if (failed) break;
-        if (issuer) commit(tfull_bar(acc));   // accumulator complete -> epilogue warps of both CTAs
+        if (issuer) { trace_stamp(5); commit(tfull_bar(acc)); }   // accumulator complete -> epilogue warps of both CTAs
         __syncwarp();
         ++acc_it;
         if constexpr (DYN) {
@@ -401,6 +406,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       const bool ready = mbar_wait(tfull_bar(acc), aph, kRoleEpilogue, 200 + (int)acc);
       if (!__all_sync(0xffffffffu, ready)) { failed = true; break; }
       tc_fence_after_sync();
+      if (warp == 2 && lane == 0) trace_stamp(6);
       const uint32_t t_addr = tmem_base + lane_base + (acc * NT + nt_w) * BN;
       bool released = false;   // TMEM already handed back inside the branch below
       const int row = m0 + lane;
@@ -546,7 +552,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         u += num_clusters;
       }
     }
+    if (warp == 2 && lane == 0) trace_stamp(7);
     if (Cfg::EPI == 1 && lane == 0) tma_store_wait_all<0>();
+    if (warp == 2 && lane == 0) trace_stamp(8);
   }
 
   // ------------------------------------------------------------------ teardown
@@ -561,9 +569,11 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     cluster_arrive();
     cluster_wait();
   }
+  if (threadIdx.x == 0) trace_stamp(9);
   if (warp == 1) {
     tc_fence_after_sync();
     tmem_dealloc<CG>(tmem_base, kTmemCols);
+    if (lane == 0) trace_stamp(10);
   }
 }
 

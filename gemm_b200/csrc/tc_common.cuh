@@ -42,6 +42,19 @@ __device__ __noinline__ void record_timeout(int role, int stage) {
   }
 }
 
+// Opt-in stage timeline (-DGEMM_B200_TRACE builds only): each of the first kTraceBlocks CTAs stamps
+// the global nanosecond timer at fixed points of the kernel; gemm_b200_trace_read() copies the
+// table out.  Compiles to nothing otherwise.
+#ifdef GEMM_B200_TRACE
+constexpr int kTraceBlocks = 160, kTraceSlots = 16;
+__device__ unsigned long long g_trace[kTraceBlocks][kTraceSlots];
+__device__ __forceinline__ void trace_stamp(int slot) {
+  if (blockIdx.x < kTraceBlocks) g_trace[blockIdx.x][slot] = globaltimer_ns();
+}
+#else
+__device__ __forceinline__ void trace_stamp(int) {}
+#endif
+
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
   return static_cast<uint32_t>(__cvta_generic_to_shared(p));
 }

@@ -6,6 +6,7 @@
 #include <utility>
 
 #include "gemm_bf16.cuh"
+#include "gemm_bf16_ksplit.cuh"
 #include "gemm_mxfp8.cuh"
 
 namespace gemm_b200 {
@@ -508,6 +509,73 @@ static int launch_bf16_splitk(const Bf16Args& a, int b_layout, int out_dtype, in
   return launch_splitk_reduce(scratch, a.M, a.N, splits, a.C, a.ldc, out_dtype, a.stream);
 }
 
+// K split across the CTAs of a cluster, partial sums combined through distributed shared memory
+// (gemm_bf16_ksplit.cuh): one launch, no scratch.  `splits` = CTAs per cluster, 2, 4 or 8.
+template <bool B_MN, bool OUT_F32>
+static int launch_bf16_cluster_splitk(const Bf16Args& a, int splits) {
+  DeviceInfo di;
+  if (int rc = device_info(&di)) return rc;
+  CUtensorMap tmA, tmB;
+  if (int rc = make_map_3d(&tmA, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, a.A, a.M, a.K, a.lda, 1, a.M * a.lda, kBlockK, kBlockM,
+                           CU_TENSOR_MAP_SWIZZLE_128B))
+    return rc;
+  if (B_MN) {
+    if (int rc = make_map_3d(&tmB, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, a.B, a.K, a.N, a.ldb, 1, a.K * a.ldb, 64, kBlockK,
+                             CU_TENSOR_MAP_SWIZZLE_128B))
+      return rc;
+  } else {
+    if (int rc = make_map_3d(&tmB, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, a.B, a.N, a.K, a.ldb, 1, a.N * a.ldb, kBlockK, kKsBN,
+                             CU_TENSOR_MAP_SWIZZLE_128B))
+      return rc;
+  }
+  auto kern = gemm_bf16_cluster_splitk_kernel<B_MN, OUT_F32>;
+  {
+    // opt in to the dynamic shared memory size once per device
+    static std::mutex mu;
+    static bool done[64] = {false};
+    std::lock_guard<std::mutex> lk(mu);
+    if (!done[di.dev & 63]) {
+      GEMM_B200_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kKsSmemBytes));
+      done[di.dev & 63] = true;
+    }
+  }
+  KsShape shape;
+  shape.M = (int)a.M;
+  shape.N = (int)a.N;
+  shape.K = (int)a.K;
+  shape.tiles_n = (int)ceil_div64(a.N, kKsBN);
+  const int64_t tiles = ceil_div64(a.M, kBlockM) * shape.tiles_n;
+  const int num_kb = (int)ceil_div64(a.K, kBlockK);
+  shape.kb_per_split = (int)ceil_div64(num_kb, splits);
+  if ((int64_t)(splits - 1) * shape.kb_per_split >= num_kb)
+    return fail(GEMM_B200_ERR_INVALID_ARG, "gemm_bf16_cluster_splitk: %d splits would leave a CTA without K blocks (K = %lld)",
+                splits, (long long)a.K);
+  if (tiles * splits > 0x7fffffff) return fail(GEMM_B200_ERR_TOO_LARGE, "gemm_bf16_cluster_splitk: too many tiles");
+  return launch_clusters(kern, (int)tiles, splits, kKsThreads, kKsSmemBytes, a.stream, tmA, tmB, a.C, a.ldc, shape);
+}
+
+static int launch_bf16_cluster_splitk_dispatch(const Bf16Args& a, int b_layout, int out_dtype, int splits) {
+  const bool mn = b_layout == GEMM_B200_B_ROW_MAJOR_KN, f32 = out_dtype == GEMM_B200_OUT_F32;
+  return mn ? (f32 ? launch_bf16_cluster_splitk<true, true>(a, splits) : launch_bf16_cluster_splitk<true, false>(a, splits))
+            : (f32 ? launch_bf16_cluster_splitk<false, true>(a, splits) : launch_bf16_cluster_splitk<false, false>(a, splits));
+}
+
+// Cluster size for the in-cluster K split, 1 = do not use it.  Measured on a B200 (call time in us,
+// default path / clusters of 4): 128 x 4096 x 4096 23.6 / 21.5, 64 x 2048 x 2048 19.3 / 15.3,
+// 384 x 4096 x 1024 23.4 / 17.4, 256 x 4096 x 2048 23.6 / 19.5, 256 x 2048 x 2048 21.4 / 15.4,
+// 16 x 4096 x 4096 19.4 / 19.5; clusters of 8 for at most 8 tiles: 32 x 4096 x 1024 17.3 / 15.3.
+// It loses where the tiles alone fill half the SMs (1024^3: 13.3 / 23.5) and for very long K,
+// where the two-launch split with many more ranges wins (512 x 32768 x 512: 39.9 / 54.3).
+static int bf16_cluster_splits(int64_t M, int64_t N, int64_t K) {
+  const int64_t tiles = ceil_div64(M, kBlockM) * ceil_div64(N, kKsBN), num_kb = ceil_div64(K, kBlockK);
+  int s = 1;
+  if (tiles <= 8 && K <= 16384) s = 8;
+  else if (tiles <= 32 && K <= 8192) s = 4;
+  if (s == 1 || num_kb < 8 * s) return 1;                                   // at least 512 of K per CTA
+  if ((int64_t)(s - 1) * ceil_div64(num_kb, s) >= num_kb) return 1;         // no CTA without K blocks
+  return s;
+}
+
 static int bf16_auto_splits(int64_t M, int64_t N, int64_t K, int sms) {
   // counted in K units of 256: no split below K = 2048, at least 1024 of K per split (1024^3 with
   // 32 tiles: 15.4 us unsplit, 19.4 us cut in two; 16 x 8192 x 8192: 50 us unsplit, 30 us cut in four)
@@ -575,6 +643,18 @@ static int bf16_entry(const void* A, const void* B, void* C, int64_t batch, int6
     return fail(GEMM_B200_ERR_UNSUPPORTED, "gemm_bf16: device has compute capability %d.x, need 10.x (sm_100a)", di.cc_major);
   Bf16Args args{A, B, C, M, N, K, lda, ldb, ldc, st, batch, stride_a, stride_b, stride_c};
   if (k_splits > 1) return launch_bf16_splitk(args, b_layout, out_dtype, k_splits, scratch);
+  if (k_splits < 0) return launch_bf16_cluster_splitk_dispatch(args, b_layout, out_dtype, -k_splits);
+  if (config < 0 && k_splits == 0 && batch == 1 && static_cast<int>(env_int("GEMM_B200_BF16_CONFIG", -1)) < 0) {
+    // few output tiles: split K inside a cluster (one launch, partial sums through shared memory)
+    static const bool cluster_ok = env_int("GEMM_B200_BF16_CLUSTER_SPLITK", 1) != 0;
+    const int cs = cluster_ok ? bf16_cluster_splits(M, N, K) : 1;
+    if (cs > 1) {
+      if (log_enabled())
+        fprintf(stderr, "[gemm_b200] gemm_bf16 %lldx%lldx%lld -> 128x128 tiles, K split over clusters of %d\n", (long long)M,
+                (long long)K, (long long)N, cs);
+      return launch_bf16_cluster_splitk_dispatch(args, b_layout, out_dtype, cs);
+    }
+  }
   if (config < 0 && batch == 1 && static_cast<int>(env_int("GEMM_B200_BF16_CONFIG", -1)) < 0) {
     // Problems whose 256-column tiles leave most SMs idle and whose K is not long enough for K
     // splits to pay: 128-column tiles give twice the units in one launch (256 x 8192 x 8192:
@@ -650,6 +730,17 @@ extern "C" int gemm_b200_gemm_bf16_splitk(const void* A, const void* B, void* C,
   }
   return tc::bf16_entry(A, B, C, 1, M, N, K, lda, ldb, ldc, 0, 0, 0, b_layout, out_dtype, -1, stream, k_splits,
                         static_cast<float*>(scratch));
+}
+
+extern "C" int gemm_b200_gemm_bf16_cluster_splitk(const void* A, const void* B, void* C, int64_t M, int64_t N, int64_t K,
+                                                  int64_t lda, int64_t ldb, int64_t ldc, int b_layout, int out_dtype,
+                                                  int k_splits, void* stream) {
+  using namespace gemm_b200;
+  if (k_splits != 2 && k_splits != 4 && k_splits != 8)
+    return fail(GEMM_B200_ERR_INVALID_ARG, "gemm_bf16_cluster_splitk: k_splits %d is not 2, 4 or 8", k_splits);
+  if (K <= 0 || M <= 0 || N <= 0)   // nothing to split: the plain entry point handles empty problems and K == 0
+    return gemm_b200_gemm_bf16(A, B, C, M, N, K, lda, ldb, ldc, b_layout, out_dtype, stream);
+  return tc::bf16_entry(A, B, C, 1, M, N, K, lda, ldb, ldc, 0, 0, 0, b_layout, out_dtype, -1, stream, -k_splits);
 }
 
 extern "C" int gemm_b200_gemm_bf16_batched(const void* A, const void* B, void* C, int64_t batch, int64_t M, int64_t N,
@@ -1143,3 +1234,14 @@ extern "C" int gemm_b200_selftest_wait_timeout(int64_t limit_us, int* device_fla
   GEMM_B200_CUDA_TRY(cudaGetLastError());
   return GEMM_B200_OK;
 }
+
+#ifdef GEMM_B200_TRACE
+// Tuning builds only: copies the stage timeline of the last tensor-core launch out (see trace_stamp).
+extern "C" int gemm_b200_trace_read(unsigned long long* out, int blocks) {
+  using namespace gemm_b200;
+  if (!out || blocks < 1 || blocks > tc::kTraceBlocks) return fail(GEMM_B200_ERR_INVALID_ARG, "trace_read: bad arguments");
+  GEMM_B200_CUDA_TRY(cudaDeviceSynchronize());
+  GEMM_B200_CUDA_TRY(cudaMemcpyFromSymbol(out, tc::g_trace, sizeof(unsigned long long) * tc::kTraceSlots * blocks));
+  return GEMM_B200_OK;
+}
+#endif

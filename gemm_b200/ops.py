@@ -75,12 +75,15 @@ def sgemm_f32(A: torch.Tensor, B: torch.Tensor, out: torch.Tensor | None = None,
 
 
 def gemm_bf16(A: torch.Tensor, B: torch.Tensor, out: torch.Tensor | None = None, *, b_is_nk: bool = False,
-              out_dtype: torch.dtype = torch.bfloat16, config: int = -1, k_splits: int = 0) -> torch.Tensor:
+              out_dtype: torch.dtype = torch.bfloat16, config: int = -1, k_splits: int = 0,
+              cluster_splits: int = 0) -> torch.Tensor:
     """BF16 ``C = A @ B`` on the tensor cores with FP32 accumulation.
 
     ``B`` is ``[K, N]`` row-major (the reference's layout) or, with ``b_is_nk``, its transpose
     ``[N, K]`` row-major.  ``k_splits``: 0 lets the library cut K when the output has few tiles,
-    1 never splits, n > 1 splits into n ranges of K (FP32 partial sums, summed in split order)."""
+    1 never splits, n > 1 splits into n ranges of K (FP32 partial sums, summed in split order).
+    ``cluster_splits`` = 2, 4 or 8 splits K over the CTAs of a cluster instead (one launch, partial
+    sums combined through distributed shared memory)."""
     _require(A.is_cuda and B.is_cuda, "A and B must be CUDA tensors")
     _require(A.dtype == torch.bfloat16 and B.dtype == torch.bfloat16, "expected bfloat16")
     _require(out_dtype in (torch.bfloat16, torch.float32), "out_dtype must be bfloat16 or float32")
@@ -97,7 +100,12 @@ def gemm_bf16(A: torch.Tensor, B: torch.Tensor, out: torch.Tensor | None = None,
     layout = _lib.B_ROW_MAJOR_NK if b_is_nk else _lib.B_ROW_MAJOR_KN
     od = _lib.OUT_F32 if out_dtype == torch.float32 else _lib.OUT_BF16
     with _OnDevice(A.device):
-        if k_splits >= 1:
+        if cluster_splits:
+            _require(config < 0 and k_splits == 0, "cluster_splits excludes k_splits and config")
+            check(lib.gemm_b200_gemm_bf16_cluster_splitk(
+                A.data_ptr(), B.data_ptr(), out.data_ptr(), M, N, K, _row_major_ld(A), _row_major_ld(B), _row_major_ld(out),
+                layout, od, cluster_splits, _stream(A)))
+        elif k_splits >= 1:
             _require(config < 0, "k_splits and config cannot both be given")
             nbytes = int(lib.gemm_b200_gemm_bf16_splitk_scratch_bytes(M, N, k_splits)) if k_splits > 1 else 0
             scratch = torch.empty((max(nbytes, 16),), device=A.device, dtype=torch.uint8)

@@ -122,6 +122,19 @@ int gemm_b200_gemm_bf16_splitk(const void* A, const void* B, void* C,
 size_t gemm_b200_gemm_bf16_splitk_scratch_bytes(int64_t M, int64_t N, int k_splits);
 int gemm_b200_gemm_bf16_auto_splits(int64_t M, int64_t N, int64_t K);
 
+/* Split-K inside a thread-block cluster, for problems with few 128 x 128 output tiles: the
+ * k_splits (2, 4 or 8) CTAs of a cluster each multiply one range of K for the same tile and
+ * combine their FP32 partial sums through distributed shared memory, in ascending order of the
+ * ranges: one launch, no scratch memory, no allocation, results independent of timing.
+ * Every range must hold at least one block of 64 k.  gemm_b200_gemm_bf16() takes this path by
+ * itself for problems of at most 32 tiles (clusters of 4; of 8 for at most 8 tiles) whose K
+ * leaves every CTA at least 512 and is not so long that the scratch-based split with many more
+ * ranges wins.  The reference walks K inside one thread (naive/naive_1.cu:9-12); no counterpart. */
+int gemm_b200_gemm_bf16_cluster_splitk(const void* A, const void* B, void* C,
+                                       int64_t M, int64_t N, int64_t K,
+                                       int64_t lda, int64_t ldb, int64_t ldc,
+                                       int b_layout, int out_dtype, int k_splits, void* stream);
+
 /* Strided-batched form: `batch` independent problems of one shape in one launch,
  *   C_i[M,N] = A_i[M,K] @ B_i,   X_i = X + i * stride_x (strides in elements).
  * The reference multiplies one pair of matrices per call (naive/naive.cpp:6-22);

@@ -33,7 +33,7 @@ def _skip_if_unsupported(fn):
 
 @pytest.mark.parametrize("M,K,N", [(256, 512, 384), (512, 4096, 4096), (2048, 4096, 4096), (8192, 8192, 8192)])
 def test_same_operands_same_result_as_scaled_mm(ops, M, K, N):
-    """FP32 output: only the order of the FP32 additions may differ (<= 2e-6 relative).  bf16
+    """FP32 output: only the order of the FP32 additions may differ (<= 1e-5 relative).  bf16
     output: equal, or where the checker summed K in another order, different by one bf16 step in
     at most one element per thousand."""
     Aq, Bq = _operands(ops, M, K, N, seed=M + N)
@@ -41,7 +41,7 @@ def test_same_operands_same_result_as_scaled_mm(ops, M, K, N):
     got32 = ops.gemm_mxfp8(Aq, Bq, out_dtype=torch.float32)
     ops.check_status()
     rel = float((got32.double() - want32.double()).norm() / want32.double().norm())
-    assert rel <= 2e-6
+    assert rel <= 1e-5
     del want32
     want16 = _scaled_mm(Aq, Bq, torch.bfloat16)
     got16 = ops.gemm_mxfp8(Aq, Bq, out_dtype=torch.bfloat16)
