@@ -241,16 +241,20 @@ def _flush_buffer():
     return _FLUSH
 
 
-def time_alone(fn, reps: int = 10, warmup: int = 3, both: bool = False):
-    """Device time (s) of single launches, L2 flushed (a 252 MB write) before each: the median, or
-    (median, best) with `both`."""
+def time_alone(fn, reps: int = 10, warmup: int = 3, both: bool = False, flush: str = "write"):
+    """Device time (s) of single launches, L2 flushed before each (by writing 252 MB, or with
+    flush="read" by reading them, which leaves no dirty lines behind): the median, or (median,
+    best) with `both`."""
     import torch
-    flush = _flush_buffer()
+    buf = _flush_buffer()
     for _ in range(warmup):
         fn()
     ts = []
     for _ in range(reps):
-        flush.zero_()
+        if flush == "read":
+            buf.sum()
+        else:
+            buf.zero_()
         e0 = torch.cuda.Event(enable_timing=True)
         e1 = torch.cuda.Event(enable_timing=True)
         e0.record()
@@ -402,6 +406,16 @@ def per_dtype_table(peaks: dict) -> dict:
                    "frac_of_measured_hbm": round(bytes_ / t / 1e9 / hbm, 4)}
             out[f"mxfp8_{M}x{K}x{N}"] = row
             if M < 1024:
+                # The HBM-bound decode shape.  `gbps` above is one call after the usual 252 MB WRITE
+                # flush; that flush leaves the L2 full of dirty lines whose write-back competes with
+                # this kernel's reads (a pure TMA stream of the same matrix: 55 us after the write
+                # flush, 43 us after a read flush).  Per call with the L2 evicted by READING:
+                t_c = time_alone(lambda: ops.gemm_mxfp8(Aq, Bq, C), flush="read")
+                row["gbps_clean_l2"] = round(bytes_ / t_c / 1e9, 1)
+                row["frac_of_measured_hbm_clean_l2"] = round(bytes_ / t_c / 1e9 / hbm, 4)
+                row["protocol"] = ("gbps: per call after a 252 MB write flush; gbps_clean_l2: per call after a 252 MB read "
+                                   "flush (no dirty lines); gbps_cuda_graph: write flush, call replayed from a CUDA graph; "
+                                   "gbps_back_to_back: no flush kernel, four copies of B in turn")
                 # A ~45 us HBM-bound kernel.  Two more views of the same call:
                 #  * replayed from a CUDA graph (no Python / ctypes between the events);
                 #  * back to back over four separate copies of B (4 x 235 MB, L2 = 126 MB) with no

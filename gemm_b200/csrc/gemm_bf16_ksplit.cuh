@@ -99,6 +99,7 @@ gemm_bf16_cluster_splitk_kernel(const __grid_constant__ CUtensorMap tmA, const _
   const uint32_t land_pitch = (uint32_t)(W + 4) * 4u;   // bytes per padded row of a landed piece
 
   if (threadIdx.x == 0) {
+    trace_stamp(0);
     for (int s = 0; s < kKsStages; ++s) {
       mbar_init(full_bar(s), 1);
       mbar_init(empty_bar(s), 1);
@@ -123,6 +124,7 @@ gemm_bf16_cluster_splitk_kernel(const __grid_constant__ CUtensorMap tmA, const _
   cluster_wait();
   tc_fence_after_sync();
   const uint32_t tmem_base = ld_shared_u32(tmem_slot);
+  if (threadIdx.x == 0) trace_stamp(1);
 
   bool failed = false;
 
@@ -135,6 +137,7 @@ gemm_bf16_cluster_splitk_kernel(const __grid_constant__ CUtensorMap tmA, const _
       const uint32_t ph = (it / kKsStages) & 1u;
       if (!mbar_wait_warp(empty_bar(s), ph ^ 1u, kRoleProducer, s)) { failed = true; break; }
       if (issuer) {
+        if (it == 0) trace_stamp(2);
         mbar_arrive_expect_tx(full_bar(s), kKsStageBytes);
         tma_load_3d(sA0 + s * kKsABytes, &tmA, kb * kBlockK, m0, 0, full_bar(s));
         const uint32_t b_dst = sB0 + s * kKsBBytes;
@@ -147,6 +150,7 @@ gemm_bf16_cluster_splitk_kernel(const __grid_constant__ CUtensorMap tmA, const _
       }
       __syncwarp();
     }
+    if (issuer) trace_stamp(3);
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer
     const bool issuer = elect_one();
@@ -160,6 +164,7 @@ gemm_bf16_cluster_splitk_kernel(const __grid_constant__ CUtensorMap tmA, const _
       const uint32_t ph = (it / kKsStages) & 1u;
       if (!mbar_wait_warp(full_bar(s), ph, kRoleMma, s)) { failed = true; break; }
       tc_fence_after_sync();
+      if (it == 0 && issuer) trace_stamp(4);
       const uint32_t a_addr = sA0 + s * kKsABytes, b_addr = sB0 + s * kKsBBytes;
       if (issuer) {
 #pragma unroll
@@ -171,7 +176,7 @@ gemm_bf16_cluster_splitk_kernel(const __grid_constant__ CUtensorMap tmA, const _
       __syncwarp();
     }
     if (!failed) {
-      if (issuer) mma_commit_local(tfull_bar);
+      if (issuer) { trace_stamp(5); mma_commit_local(tfull_bar); }
       __syncwarp();
     }
   } else {
@@ -184,6 +189,7 @@ gemm_bf16_cluster_splitk_kernel(const __grid_constant__ CUtensorMap tmA, const _
       failed = true;
     } else {
       tc_fence_after_sync();
+      if (warp == 2 && lane == 0) trace_stamp(6);
       // 1. hand every other CTA its columns of this CTA's partial sums: staged in the operand ring
       //    (every MMA that read it has completed: the accumulator barrier says so), then one bulk
       //    copy of this warp's 32 padded rows per destination
@@ -210,7 +216,9 @@ gemm_bf16_cluster_splitk_kernel(const __grid_constant__ CUtensorMap tmA, const _
         }
       }
       // 2. finish this CTA's own columns
+      if (warp == 2 && lane == 0) trace_stamp(7);
       const bool landed = mbar_wait_cluster(landed_bar, 0, kRoleEpilogue, 210);
+      if (warp == 2 && lane == 0) trace_stamp(8);
       if (!__all_sync(0xffffffffu, landed)) {
         failed = true;
       } else {
@@ -276,6 +284,7 @@ gemm_bf16_cluster_splitk_kernel(const __grid_constant__ CUtensorMap tmA, const _
     const unsigned long long t0 = globaltimer_ns();
     while (globaltimer_ns() - t0 < 200000ull) __nanosleep(1000);
   }
+  if (threadIdx.x == 64) trace_stamp(9);
   tc_fence_before_sync();
   __syncthreads();
   cluster_arrive();      // nobody leaves while a peer may still be writing into its landing zone
@@ -283,6 +292,7 @@ gemm_bf16_cluster_splitk_kernel(const __grid_constant__ CUtensorMap tmA, const _
   if (warp == 1) {
     tc_fence_after_sync();
     tmem_dealloc<1>(tmem_base, kKsBN);
+    if (lane == 0) trace_stamp(10);
   }
 }
 

@@ -114,6 +114,7 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
   };
 
   if (threadIdx.x == 0) {
+    trace_stamp(0);
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(full_bar(s), 1);
       mbar_init(empty_bar(s), 1);
@@ -145,6 +146,7 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
   asm volatile("ld.shared.u32 %0, [%1];" : "=r"(tmem_base) : "r"(tmem_slot) : "memory");
   // split-K: lets the reduce kernel behind this one be scheduled early; it waits for this grid
   if (shape.k_splits > 1) pdl_launch_dependents();
+  if (threadIdx.x == 0) trace_stamp(1);
 
   bool failed = false;
 
@@ -170,6 +172,7 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
         if (!mbar_wait_warp(empty_bar(s), ph ^ 1u, kRoleProducer, s)) { failed = true; break; }
         const uint32_t a_dst = sA0 + s * Cfg::A_BYTES, b_dst = sB0 + s * Cfg::B_BYTES;
         const uint32_t sfa_dst = sSFA0 + s * Cfg::SFA_BYTES, sfb_dst = sSFB0 + s * Cfg::SFB_BYTES;
+        if (it == 0 && issuer) trace_stamp(2);
         // scale maps: 32-bit elements, row = 128-row block, 128 elements (512 bytes) per K chunk
         if constexpr (CG == 1) {
           if (issuer) {
@@ -192,6 +195,7 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
         __syncwarp();
       }
       if (failed) break;
+      if (issuer) trace_stamp(3);
       ++n;
       if constexpr (DYN) {
         u = (cta_rank == 0) ? ring.template fetch_and_publish<CG>(n, issuer) : ring.wait_unit(n, kRoleProducer);
@@ -233,6 +237,7 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
           const uint32_t ph = (it / STAGES) & 1u;
           if (!mbar_wait_warp(full_bar(s), ph, kRoleMma, s)) { failed = true; break; }
           tc_fence_after_sync();
+          if (it == 0 && issuer) trace_stamp(4);
           const uint32_t a_addr = sA0 + s * Cfg::A_BYTES, b_addr = sB0 + s * Cfg::B_BYTES;
           const uint32_t sfa_addr = sSFA0 + s * Cfg::SFA_BYTES, sfb_addr = sSFB0 + s * Cfg::SFB_BYTES;
           const uint32_t first = (kb != kb0) ? 1u : 0u;
@@ -255,7 +260,7 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
           __syncwarp();
         }
         if (failed) break;
-        if (issuer) commit(tfull_bar);
+        if (issuer) { trace_stamp(5); commit(tfull_bar); }
         __syncwarp();
         ++acc_it;
         if constexpr (DYN) {
@@ -283,6 +288,7 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
       const bool ready = mbar_wait(tfull_bar, acc_it & 1u, kRoleEpilogue, 200);
       if (!__all_sync(0xffffffffu, ready)) { failed = true; break; }
       tc_fence_after_sync();
+      if (warp == 2 && lane == 0) trace_stamp(6);
       uint32_t v[NCH][32];
 #pragma unroll
       for (int c = 0; c < NCH; ++c) tmem_ld_32x32b_x32(t_addr + c * 32, v[c]);
@@ -425,7 +431,9 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
         u += num_clusters;
       }
     }
+    if (warp == 2 && lane == 0) trace_stamp(7);
     if (Cfg::EPI == 1 && lane == 0) tma_store_wait_all<0>();
+    if (warp == 2 && lane == 0) trace_stamp(8);
   }
 
   // ------------------------------------------------------------------ teardown
@@ -439,9 +447,11 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
     cluster_arrive();
     cluster_wait();
   }
+  if (threadIdx.x == 0) trace_stamp(9);
   if (warp == 1) {
     tc_fence_after_sync();
     tmem_dealloc<CG>(tmem_base, kTmemCols);
+    if (lane == 0) trace_stamp(10);
   }
 }
 

@@ -42,9 +42,13 @@ __device__ __noinline__ void record_timeout(int role, int stage) {
   }
 }
 
-// Opt-in stage timeline (-DGEMM_B200_TRACE builds only): each of the first kTraceBlocks CTAs stamps
-// the global nanosecond timer at fixed points of the kernel; gemm_b200_trace_read() copies the
-// table out.  Compiles to nothing otherwise.
+// Opt-in stage timeline (-DGEMM_B200_TRACE builds only, `python -m gemm_b200.build --trace`): each
+// of the first kTraceBlocks CTAs stamps the global nanosecond timer at fixed points of a
+// tensor-core kernel; gemm_b200_trace_read() copies the table out.  Compiles to nothing otherwise.
+// Slots: 0 kernel entry, 1 set-up done (barriers, TMEM, cluster sync), 2 first TMA issued, 3 last
+// load of the CTA issued, 4 first operand stage arrived, 5 last MMA issued, 6 epilogue sees the
+// accumulator, 7 stores issued (cluster split: partial sums sent), 8 stores complete (cluster
+// split: all pieces landed), 9 before the teardown barrier, 10 TMEM freed.
 #ifdef GEMM_B200_TRACE
 constexpr int kTraceBlocks = 160, kTraceSlots = 16;
 __device__ unsigned long long g_trace[kTraceBlocks][kTraceSlots];

@@ -8,6 +8,7 @@
 #include "gemm_bf16.cuh"
 #include "gemm_bf16_ksplit.cuh"
 #include "gemm_mxfp8.cuh"
+#include "gemm_mxfp8_ksplit.cuh"
 
 namespace gemm_b200 {
 namespace tc {
@@ -867,6 +868,60 @@ static int launch_mxfp8_splitk(const MxArgs& a, int out_dtype) {
   return launch_splitk_reduce(a.scratch, a.M, a.N, splits, a.C, a.ldc, out_dtype, a.stream);
 }
 
+// K split across the CTAs of a cluster (gemm_mxfp8_ksplit.cuh): one launch, no scratch.
+template <bool OUT_F32>
+static int launch_mxfp8_cluster_splitk(const MxArgs& a, int splits) {
+  DeviceInfo di;
+  if (int rc = device_info(&di)) return rc;
+  CUtensorMap tmA, tmB, tmSFA, tmSFB;
+  if (int rc = make_map_2d(&tmA, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, a.Aq, a.M, a.K, a.K, kMxBlockK, kBlockM, CU_TENSOR_MAP_SWIZZLE_128B))
+    return rc;
+  if (int rc = make_map_2d(&tmB, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, a.Bq, a.N, a.K, a.K, kMxBlockK, kKsBN, CU_TENSOR_MAP_SWIZZLE_128B))
+    return rc;
+  if (int rc = make_scale_map(&tmSFA, a.SFA, a.M, a.K, 1)) return rc;
+  if (int rc = make_scale_map(&tmSFB, a.SFB, a.N, a.K, 1)) return rc;
+  auto kern = gemm_mxfp8_cluster_splitk_kernel<OUT_F32>;
+  {
+    static std::mutex mu;
+    static bool done[64] = {false};
+    std::lock_guard<std::mutex> lk(mu);
+    if (!done[di.dev & 63]) {
+      GEMM_B200_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kMxKsSmemBytes));
+      done[di.dev & 63] = true;
+    }
+  }
+  KsShape shape;
+  shape.M = (int)a.M;
+  shape.N = (int)a.N;
+  shape.K = (int)a.K;
+  shape.tiles_n = (int)ceil_div64(a.N, kKsBN);
+  const int64_t tiles = ceil_div64(a.M, kBlockM) * shape.tiles_n;
+  const int num_kb = (int)ceil_div64(a.K, kMxBlockK);
+  shape.kb_per_split = (int)ceil_div64(num_kb, splits);
+  if ((int64_t)(splits - 1) * shape.kb_per_split >= num_kb)
+    return fail(GEMM_B200_ERR_INVALID_ARG, "gemm_mxfp8_cluster_splitk: %d splits would leave a CTA without K blocks (K = %lld)",
+                splits, (long long)a.K);
+  if (tiles * splits > 0x7fffffff) return fail(GEMM_B200_ERR_TOO_LARGE, "gemm_mxfp8_cluster_splitk: too many tiles");
+  return launch_clusters(kern, (int)tiles, splits, kKsThreads, kMxKsSmemBytes, a.stream, tmA, tmB, tmSFA, tmSFB, a.C, a.ldc, shape);
+}
+
+// Cluster size for the in-cluster K split of the MXFP8 GEMM, 1 = do not use it.  Measured on a B200
+// (call time in us, default path / clusters of 4; torch._scaled_mm beside it): 128 x 4096 x 4096
+// 18.4 / 16.4 (17.2), 64 x 2048 x 2048 15.1 / 13.2 (13.1), 384 x 4096 x 1024 17.2 / 15.2 (15.4),
+// 128 x 8192 x 2048 21.5 / 18.4 (21.5), 256 x 8192 x 2048 22.5 / 18.5 (21.5).  Up to 32 rows the
+// narrow-A kernel with the scratch-based split stays ahead (16 x 8192 x 4096: 19.2 / 20.5,
+// 16 x 16384 x 1024: 17.4 / 18.4 with clusters of 8), so those keep it.
+static int mxfp8_cluster_splits(int64_t M, int64_t N, int64_t K) {
+  if (M <= 32) return 1;
+  const int64_t tiles = ceil_div64(M, kBlockM) * ceil_div64(N, kKsBN), num_kb = ceil_div64(K, kMxBlockK);
+  int s = 1;
+  if (tiles <= 8 && K <= 16384) s = 8;
+  else if (tiles <= 32 && K <= 8192) s = 4;
+  if (s == 1 || num_kb < 4 * s) return 1;                                   // at least 512 of K per CTA
+  if ((int64_t)(s - 1) * ceil_div64(num_kb, s) >= num_kb) return 1;         // no CTA without K blocks
+  return s;
+}
+
 struct MxConfigEntry {
   const char* name;
   int (*launch[2])(const MxArgs&);   // [out_dtype]
@@ -982,9 +1037,25 @@ extern "C" int gemm_b200_gemm_mxfp8_cfg(const void* Aq, const void* SFA, const v
   if (di.cc_major != 10)
     return fail(GEMM_B200_ERR_UNSUPPORTED, "gemm_mxfp8: device has compute capability %d.x, need 10.x (sm_100a)", di.cc_major);
   tc::MxArgs args{Aq, SFA, Bq, SFB, C, M, N, K, ldc, st};
+  if (config <= -4) {   // explicit in-cluster K split (gemm_b200_gemm_mxfp8_cluster_splitk): -2 - splits
+    return out_dtype == GEMM_B200_OUT_F32 ? tc::launch_mxfp8_cluster_splitk<true>(args, -2 - config)
+                                          : tc::launch_mxfp8_cluster_splitk<false>(args, -2 - config);
+  }
   if (config < 0) {
     static const int forced = env_int("GEMM_B200_MXFP8_CONFIG", -1);
     if (forced >= 0 && forced < tc::kNumMxConfigs) config = forced;
+  }
+  if (config < 0) {
+    // few output tiles: split K inside a cluster (one launch, partial sums through shared memory)
+    static const bool cluster_ok = env_int("GEMM_B200_MXFP8_CLUSTER_SPLITK", 1) != 0;
+    const int cs = cluster_ok ? tc::mxfp8_cluster_splits(M, N, K) : 1;
+    if (cs > 1) {
+      if (log_enabled())
+        fprintf(stderr, "[gemm_b200] gemm_mxfp8 %lldx%lldx%lld -> 128x128 tiles, K split over clusters of %d\n", (long long)M,
+                (long long)K, (long long)N, cs);
+      return out_dtype == GEMM_B200_OUT_F32 ? tc::launch_mxfp8_cluster_splitk<true>(args, cs)
+                                            : tc::launch_mxfp8_cluster_splitk<false>(args, cs);
+    }
   }
   if (config < 0) {
     if (M <= 128) {
@@ -1113,6 +1184,18 @@ extern "C" int gemm_b200_gemm_mxfp8_splitk(const void* Aq, const void* SFA, cons
   args.scratch = static_cast<float*>(scratch);
   return tc::launch_mxfp8_splitk<tc::Mx_1cta>(args, out_dtype);
 }
+extern "C" int gemm_b200_gemm_mxfp8_cluster_splitk(const void* Aq, const void* SFA, const void* Bq, const void* SFB, void* C,
+                                                   int64_t M, int64_t N, int64_t K, int64_t ldc, int out_dtype, int k_splits,
+                                                   void* stream) {
+  using namespace gemm_b200;
+  if (k_splits != 2 && k_splits != 4 && k_splits != 8)
+    return fail(GEMM_B200_ERR_INVALID_ARG, "gemm_mxfp8_cluster_splitk: k_splits %d is not 2, 4 or 8", k_splits);
+  if (M <= 0 || N <= 0 || K <= 0)   // nothing to split: the plain entry point handles empty problems and K == 0
+    return gemm_b200_gemm_mxfp8(Aq, SFA, Bq, SFB, C, M, N, K, ldc, out_dtype, stream);
+  // the argument checks of the plain entry point, then the split (config -2 - k_splits selects it)
+  return gemm_b200_gemm_mxfp8_cfg(Aq, SFA, Bq, SFB, C, M, N, K, ldc, out_dtype, -2 - k_splits, stream);
+}
+
 extern "C" int gemm_b200_gemm_mxfp8(const void* Aq, const void* SFA, const void* Bq, const void* SFB, void* C, int64_t M,
                                     int64_t N, int64_t K, int64_t ldc, int out_dtype, void* stream) {
   return gemm_b200_gemm_mxfp8_cfg(Aq, SFA, Bq, SFB, C, M, N, K, ldc, out_dtype, -1, stream);

@@ -270,19 +270,25 @@ def quantize_mxfp8(X: torch.Tensor, transposed_in: bool = False) -> MxFp8Tensor:
 
 
 def gemm_mxfp8(A: MxFp8Tensor, B: MxFp8Tensor, out: torch.Tensor | None = None, *,
-               out_dtype: torch.dtype = torch.bfloat16, config: int = -1) -> torch.Tensor:
-    """C[M, N] = dequant(A)[M, K] @ dequant(B)[N, K]^T on the block-scaled tensor cores."""
+               out_dtype: torch.dtype = torch.bfloat16, config: int = -1, cluster_splits: int = 0) -> torch.Tensor:
+    """C[M, N] = dequant(A)[M, K] @ dequant(B)[N, K]^T on the block-scaled tensor cores.
+    ``cluster_splits`` = 2, 4 or 8 splits K over the CTAs of a cluster (few-tile problems)."""
     _require(A.K == B.K, f"K mismatch: {A.K} vs {B.K}")
     _require(out_dtype in (torch.bfloat16, torch.float32), "out_dtype must be bfloat16 or float32")
     M, N, K = A.rows, B.rows, A.K
     if out is None:
         out = torch.empty((M, N), device=A.data.device, dtype=out_dtype)
     _require(out.is_cuda and out.dtype == out_dtype and tuple(out.shape) == (M, N), "bad out tensor")
+    od = _lib.OUT_F32 if out_dtype == torch.float32 else _lib.OUT_BF16
     with _OnDevice(A.data.device):
-        check(lib.gemm_b200_gemm_mxfp8_cfg(A.data.data_ptr(), A.scales.data_ptr(), B.data.data_ptr(), B.scales.data_ptr(),
-                                           out.data_ptr(), M, N, K, _row_major_ld(out),
-                                           _lib.OUT_F32 if out_dtype == torch.float32 else _lib.OUT_BF16, config,
-                                           _stream(A.data)))
+        if cluster_splits:
+            _require(config < 0, "cluster_splits and config cannot both be given")
+            check(lib.gemm_b200_gemm_mxfp8_cluster_splitk(A.data.data_ptr(), A.scales.data_ptr(), B.data.data_ptr(),
+                                                          B.scales.data_ptr(), out.data_ptr(), M, N, K, _row_major_ld(out), od,
+                                                          cluster_splits, _stream(A.data)))
+        else:
+            check(lib.gemm_b200_gemm_mxfp8_cfg(A.data.data_ptr(), A.scales.data_ptr(), B.data.data_ptr(), B.scales.data_ptr(),
+                                               out.data_ptr(), M, N, K, _row_major_ld(out), od, config, _stream(A.data)))
     return out
 
 

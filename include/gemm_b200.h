@@ -198,6 +198,14 @@ int gemm_b200_gemm_mxfp8_splitk(const void* Aq, const void* SFA, const void* Bq,
                                 int k_splits, void* scratch, size_t scratch_bytes, void* stream);
 size_t gemm_b200_gemm_mxfp8_splitk_scratch_bytes(int64_t M, int64_t N, int k_splits);
 
+/* Split-K inside a thread-block cluster (see gemm_b200_gemm_bf16_cluster_splitk): k_splits = 2, 4
+ * or 8 CTAs per 128 x 128 tile, partial sums combined through distributed shared memory, one
+ * launch, no scratch.  Every range must hold at least one block of 128 k.  gemm_b200_gemm_mxfp8()
+ * takes this path by itself for problems of at most 32 tiles.  No counterpart in the reference. */
+int gemm_b200_gemm_mxfp8_cluster_splitk(const void* Aq, const void* SFA, const void* Bq, const void* SFB,
+                                        void* C, int64_t M, int64_t N, int64_t K, int64_t ldc, int out_dtype,
+                                        int k_splits, void* stream);
+
 /* The same split-K GEMM for callers that cannot allocate device memory where they call it: a
  * serving loop that gave all of HBM to its own pool at start-up (cudaMalloc would fail there, and
  * it synchronises the device even when it succeeds), or a plugin host that forbids allocation

@@ -47,3 +47,22 @@ def test_host_entry_argument_errors(ops):
     with pytest.raises(ValueError):
         ops.sgemm_f32_host(torch.zeros(4, 4, device="cuda"), torch.zeros(4, 4, device="cuda"))
     assert L.lib.gemm_b200_release_workspace() == L.OK
+
+
+def test_host_entry_error_leaves_nothing_in_flight(ops, oracle):
+    """A launch the device entry point refuses (K not a multiple of 8 for BF16) comes back as that
+    error with every queued copy finished: the caller may overwrite or free its buffers at once,
+    and the next call works on the same workspace."""
+    import gemm_b200._lib as L
+    M, K, N = 24576, 1028, 1024                      # several slabs; K % 8 != 0 -> GEMM_B200_ERR_ALIGNMENT
+    A = torch.ones(M, K, dtype=torch.bfloat16).pin_memory()
+    B = torch.ones(K, N, dtype=torch.bfloat16).pin_memory()
+    C = torch.full((M, N), 7.0, dtype=torch.bfloat16).pin_memory()
+    rc = L.lib.gemm_b200_gemm_bf16_host(A.data_ptr(), B.data_ptr(), C.data_ptr(), M, N, K, L.B_ROW_MAJOR_KN, L.OUT_BF16)
+    assert rc == L.ERR_ALIGNMENT
+    A.fill_(3.0); B.fill_(3.0)                        # nothing reads them any more
+    assert bool((C == 7.0).all())                     # and nothing was written
+    M, K, N = 4096, 1024, 512
+    A2, B2 = oracle.gen_randn_bf16(M, K, N, seed=8)
+    got = ops.gemm_bf16_host(A2.pin_memory(), B2.pin_memory())
+    assert torch.equal(got, ops.gemm_bf16(A2.cuda(), B2.cuda()).cpu())

@@ -269,3 +269,40 @@ def test_runtime_unit_handout_matches_the_static_schedule(ops, oracle):
         ops.gemm_mxfp8(Aq, Bq, dyn, config=names.index("2cta_256x256x128_s5_maskcommit_tmastore_dynamic"))
         ops.check_status()
         assert torch.equal(dyn, static)
+
+
+@pytest.mark.parametrize("splits", [2, 4, 8])
+@pytest.mark.parametrize("M,K,N", [(128, 4096, 2048), (16, 8192, 1024), (300, 2048, 520), (100, 3040, 136), (1, 1024, 8)])
+def test_cluster_splitk_matches_the_oracle(ops, oracle, M, K, N, splits):
+    """K split over the CTAs of a cluster, partial sums combined through distributed shared memory."""
+    A, B = oracle.gen_randn_bf16(M, K, N, seed=M + splits)
+    A = (A.float() * torch.exp(torch.randn(M, 1, generator=torch.Generator().manual_seed(M)) * 2)).bfloat16()
+    Aq = ops.quantize_mxfp8(A.cuda()); Bq = ops.quantize_mxfp8(B.cuda(), transposed_in=True)
+    qa, sa = oracle.mxfp8_quantize(A); qb, sb = oracle.mxfp8_quantize(B.t().contiguous())
+    want = oracle.mxfp8_matmul_oracle(qa, sa, qb, sb)
+    C32 = torch.full((M, N), float("nan"), device="cuda")
+    ops.gemm_mxfp8(Aq, Bq, C32, out_dtype=torch.float32, cluster_splits=splits)
+    ops.check_status()
+    assert oracle.rel_frobenius(C32.cpu(), want) <= REL_TOL
+    unsplit = ops.gemm_mxfp8(Aq, Bq, out_dtype=torch.float32, config=0)
+    assert oracle.rel_frobenius(C32.cpu(), unsplit.cpu()) <= 1e-5     # only the summation order differs
+    C16 = ops.gemm_mxfp8(Aq, Bq, out_dtype=torch.bfloat16, cluster_splits=splits)
+    ops.check_status()
+    assert torch.equal(C16, C32.bfloat16())
+    assert torch.equal(ops.gemm_mxfp8(Aq, Bq, out_dtype=torch.float32, cluster_splits=splits), C32)   # fixed order: same bits again
+
+
+def test_cluster_splitk_is_taken_by_itself(ops, oracle):
+    import gemm_b200._lib as L
+    M, K, N = 64, 4096, 2048                        # 16 tiles of 128 x 128: clusters of 4
+    A, B = oracle.gen_randn_bf16(M, K, N, seed=2)
+    Aq = ops.quantize_mxfp8(A.cuda()); Bq = ops.quantize_mxfp8(B.cuda(), transposed_in=True)
+    auto = ops.gemm_mxfp8(Aq, Bq, out_dtype=torch.float32)
+    ops.check_status()
+    assert torch.equal(auto, ops.gemm_mxfp8(Aq, Bq, out_dtype=torch.float32, cluster_splits=4))
+    rc = L.lib.gemm_b200_gemm_mxfp8_cluster_splitk(Aq.data.data_ptr(), Aq.scales.data_ptr(), Bq.data.data_ptr(), Bq.scales.data_ptr(),
+                                                   auto.data_ptr(), M, N, K, N, 1, 3, None)
+    assert rc == L.ERR_INVALID_ARG and "2, 4 or 8" in L.last_error()
+    rc = L.lib.gemm_b200_gemm_mxfp8_cluster_splitk(Aq.data.data_ptr(), Aq.scales.data_ptr(), Bq.data.data_ptr(), Bq.scales.data_ptr(),
+                                                   auto.data_ptr(), M, N, 256, N, 1, 8, None)
+    assert rc == L.ERR_INVALID_ARG and "without K blocks" in L.last_error()
