@@ -162,6 +162,16 @@ struct GemmShape {
   int l2_stream_a_keep_b;
 };
 
+// Grouped (ragged) problems: group g multiplies rows [row_start[g], row_start[g + 1]) of one tall A
+// by its own B_g into the same rows of one tall C.  tile_start[g] = index of the group's first
+// work unit; units of a group are ordered row tile by row tile.  count == 0: not a grouped launch.
+constexpr int kMaxGroups = 64;
+struct GroupTable {
+  int count;
+  int tile_start[kMaxGroups + 1];
+  int row_start[kMaxGroups + 1];
+};
+
 __device__ __forceinline__ void tile_coord(int t, const GemmShape& sh, int& tm, int& tn) {
   if (sh.raster_group > 0) {
     const int group = sh.raster_group;
@@ -184,7 +194,7 @@ template <class Cfg, bool B_MN, bool OUT_F32>
 __global__ void __launch_bounds__(Cfg::THREADS, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                  const __grid_constant__ CUtensorMap tmC, void* __restrict__ Cptr, int64_t ldc,
-                 const GemmShape shape) {
+                 const GemmShape shape, const __grid_constant__ GroupTable groups) {
   constexpr int CG = Cfg::CG, STAGES = Cfg::STAGES, NT = Cfg::NT, ACC_STAGES = Cfg::ACC_STAGES, BN = Cfg::BN;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -210,7 +220,30 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   // work units: (matrix, tile, K split); consecutive units share the tile.  k_splits > 1 only with
   // the direct-store FP32 epilogue: unit (tile, split) writes its partial sums to slice `split`
   // of the scratch buffer Cptr ([k_splits][M][ldc] floats).
-  const int num_tiles = tiles_per_matrix * shape.batch * shape.k_splits;
+  const bool grouped = groups.count > 0;
+  const int num_tiles = grouped ? groups.tile_start[groups.count] : tiles_per_matrix * shape.batch * shape.k_splits;
+  // tile index -> (matrix or group, row tile, column tile) and the rows [row_base, row_end) of A / C it
+  // may touch (row tiles count from row_base)
+  auto decode = [&](int t, int& bi, int& tm, int& tn, int& row_base, int& row_end) {
+    if (grouped) {
+      int lo = 0, hi = groups.count - 1;          // the last group whose first unit is <= t
+      while (lo < hi) {
+        const int mid = (lo + hi + 1) >> 1;
+        if (groups.tile_start[mid] <= t) lo = mid; else hi = mid - 1;
+      }
+      const int local = t - groups.tile_start[lo];
+      tm = local / shape.tiles_n;
+      tn = local - tm * shape.tiles_n;
+      bi = lo;
+      row_base = groups.row_start[lo];
+      row_end = groups.row_start[lo + 1];
+    } else {
+      bi = t / tiles_per_matrix;
+      tile_coord(t - bi * tiles_per_matrix, shape, tm, tn);
+      row_base = 0;
+      row_end = shape.M;
+    }
+  };
   auto unit_range = [&](int u, int& tile, int& split, int& kb0, int& kb1) {
     tile = u / shape.k_splits;
     split = u - tile * shape.k_splits;
@@ -277,12 +310,11 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     uint32_t it = 0, n = 0;   // n: how many units this cluster has started
     int u = cluster_id;
     while (u >= 0 && u < num_tiles && !failed) {
-      int t, split, kb0, kb1, tm, tn;
+      int t, split, kb0, kb1, tm, tn, bi, row_base, row_end;
       unit_range(u, t, split, kb0, kb1);
-      const int bi = t / tiles_per_matrix;
-      tile_coord(t - bi * tiles_per_matrix, shape, tm, tn);
-      const int az = bi * shape.a_z, bz = bi * shape.b_z;
-      const int m0 = (tm * CG + (int)cta_rank) * kBlockM;
+      decode(t, bi, tm, tn, row_base, row_end);
+      const int az = grouped ? 0 : bi * shape.a_z, bz = grouped ? bi : bi * shape.b_z;   // a group has its own B, A is one matrix
+      const int m0 = row_base + (tm * CG + (int)cta_rank) * kBlockM;
       if constexpr (DYN) {
         if (cta_rank == 0 && issuer) ring.request(n + 1);   // the answer arrives while this unit loads
       }
@@ -394,11 +426,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     uint32_t acc_it = 0, store_it = 0;
     int u = cluster_id;
     while (u >= 0 && u < num_tiles && !failed) {
-      int t, split, kb0, kb1, tm, tn;
+      int t, split, kb0, kb1, tm, tn, bi, row_base, row_end;
       unit_range(u, t, split, kb0, kb1);
-      const int bi = t / tiles_per_matrix;
-      tile_coord(t - bi * tiles_per_matrix, shape, tm, tn);
-      const int m0 = (tm * CG + (int)cta_rank) * kBlockM + quad * 32;   // first row of this warp
+      decode(t, bi, tm, tn, row_base, row_end);
+      const int m0 = row_base + (tm * CG + (int)cta_rank) * kBlockM + quad * 32;   // first row of this warp
       const int n0 = (tn * NT + nt_w) * BN;
       const uint32_t acc = acc_it % ACC_STAGES, aph = (acc_it / ACC_STAGES) & 1u;
       // every lane waits, and the warp moves on only if every lane saw the phase complete: the
@@ -418,7 +449,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           tmem_ld_32x32b_x32(t_addr + c * 32, v);
           tmem_ld_wait();
           const int col = n0 + c * 32;
-          if (row < shape.M) {
+          if (row < row_end) {
             if constexpr (OUT_F32) {
               float* dst = reinterpret_cast<float*>(Cptr) + bi * shape.c_batch_stride + split * shape.split_stride + (int64_t)row * ldc + col;
 #pragma unroll

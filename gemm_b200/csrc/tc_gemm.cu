@@ -398,7 +398,67 @@ static int launch_bf16(const Bf16Args& a) {
   if (Cfg::DYN && shape.k_splits > 1)
     return fail(GEMM_B200_ERR_INVALID_ARG, "gemm_bf16: K splits run on the static schedule");
 
-  return launch_clusters(kern, clusters, CG, Cfg::THREADS, Cfg::SMEM_BYTES, a.stream, tmA, tmB, tmC, a.C, a.ldc, shape);
+  static const GroupTable no_groups = {};   // count == 0
+  return launch_clusters(kern, clusters, CG, Cfg::THREADS, Cfg::SMEM_BYTES, a.stream, tmA, tmB, tmC, a.C, a.ldc, shape, no_groups);
+}
+
+// Grouped (ragged) BF16 GEMM, at most kMaxGroups groups per launch: single-CTA 128 x 256 tiles with
+// the direct-store epilogue, whose row guard stops at the end of the group (a TMA store would
+// write the first rows of the next group).  Units are handed out statically.
+template <bool B_MN, bool OUT_F32>
+static int launch_bf16_grouped(const void* A, const void* B, void* C, int groups, const int64_t* m_sizes, int64_t N, int64_t K,
+                               int64_t lda, int64_t ldb, int64_t stride_b, int64_t ldc, cudaStream_t stream) {
+  using Cfg = Bf16Cfg<1, 4, 0, false>;
+  DeviceInfo di;
+  if (int rc = device_info(&di)) return rc;
+  GroupTable table;
+  table.count = groups;
+  int64_t rows = 0, tiles = 0;
+  const int tiles_n = (int)ceil_div64(N, Cfg::TILE_N);
+  for (int g = 0; g < groups; ++g) {
+    table.tile_start[g] = (int)tiles;
+    table.row_start[g] = (int)rows;
+    rows += m_sizes[g];
+    tiles += ceil_div64(m_sizes[g], kBlockM) * tiles_n;
+    if (rows > 0x7fffffff || tiles > 0x7fffffff) return fail(GEMM_B200_ERR_TOO_LARGE, "gemm_bf16_grouped: too many rows or tiles");
+  }
+  for (int g = groups; g <= kMaxGroups; ++g) {
+    table.tile_start[g] = (int)tiles;
+    table.row_start[g] = (int)rows;
+  }
+  if (tiles == 0) return GEMM_B200_OK;
+  CUtensorMap tmA, tmB;
+  if (int rc = make_map_3d(&tmA, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, A, rows, K, lda, 1, rows * lda, kBlockK, kBlockM,
+                           CU_TENSOR_MAP_SWIZZLE_128B))
+    return rc;
+  if (B_MN) {
+    if (int rc = make_map_3d(&tmB, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, B, K, N, ldb, groups, stride_b, 64, kBlockK,
+                             CU_TENSOR_MAP_SWIZZLE_128B))
+      return rc;
+  } else {
+    if (int rc = make_map_3d(&tmB, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, B, N, K, ldb, groups, stride_b, kBlockK, Cfg::BN_CTA,
+                             CU_TENSOR_MAP_SWIZZLE_128B))
+      return rc;
+  }
+  auto kern = gemm_bf16_kernel<Cfg, B_MN, OUT_F32>;
+  int max_clusters = 0;
+  if (int rc = persistent_clusters(kern, 1, Cfg::THREADS, Cfg::SMEM_BYTES, di, &max_clusters)) return rc;
+  GemmShape shape;
+  shape.M = (int)rows;
+  shape.N = (int)N;
+  shape.K = (int)K;
+  shape.tiles_m = 0;                  // unused: the table says where every group's tiles start
+  shape.tiles_n = tiles_n;
+  shape.k_splits = 1;
+  shape.kb_per_split = (int)ceil_div64(K, kBlockK);
+  shape.split_stride = 0;
+  shape.raster_group = 1;
+  shape.batch = 1;
+  shape.a_z = shape.b_z = 0;
+  shape.c_batch_stride = 0;
+  shape.l2_stream_a_keep_b = 0;
+  const int clusters = (int)(tiles < max_clusters ? tiles : max_clusters);
+  return launch_clusters(kern, clusters, 1, Cfg::THREADS, Cfg::SMEM_BYTES, stream, tmA, tmB, tmA, C, ldc, shape, table);
 }
 
 struct Bf16ConfigEntry {
@@ -742,6 +802,62 @@ extern "C" int gemm_b200_gemm_bf16_cluster_splitk(const void* A, const void* B, 
   if (K <= 0 || M <= 0 || N <= 0)   // nothing to split: the plain entry point handles empty problems and K == 0
     return gemm_b200_gemm_bf16(A, B, C, M, N, K, lda, ldb, ldc, b_layout, out_dtype, stream);
   return tc::bf16_entry(A, B, C, 1, M, N, K, lda, ldb, ldc, 0, 0, 0, b_layout, out_dtype, -1, stream, -k_splits);
+}
+
+extern "C" int gemm_b200_gemm_bf16_grouped(const void* A, const void* B, void* C, int64_t groups, const int64_t* m_sizes,
+                                           int64_t N, int64_t K, int64_t lda, int64_t ldb, int64_t stride_b, int64_t ldc,
+                                           int b_layout, int out_dtype, void* stream) {
+  using namespace gemm_b200;
+  if (groups < 0 || N < 0 || K < 0) return fail(GEMM_B200_ERR_INVALID_ARG, "gemm_bf16_grouped: negative size");
+  if (b_layout != GEMM_B200_B_ROW_MAJOR_KN && b_layout != GEMM_B200_B_ROW_MAJOR_NK)
+    return fail(GEMM_B200_ERR_INVALID_ARG, "gemm_bf16_grouped: b_layout %d", b_layout);
+  if (out_dtype != GEMM_B200_OUT_BF16 && out_dtype != GEMM_B200_OUT_F32)
+    return fail(GEMM_B200_ERR_INVALID_ARG, "gemm_bf16_grouped: out_dtype %d", out_dtype);
+  if (groups == 0 || N == 0) return GEMM_B200_OK;
+  if (!m_sizes) return fail(GEMM_B200_ERR_INVALID_ARG, "gemm_bf16_grouped: null m_sizes");
+  int64_t rows = 0;
+  for (int64_t g = 0; g < groups; ++g) {
+    if (m_sizes[g] < 0) return fail(GEMM_B200_ERR_INVALID_ARG, "gemm_bf16_grouped: negative group size");
+    rows += m_sizes[g];
+    if (rows > 0x7fffffff) return fail(GEMM_B200_ERR_TOO_LARGE, "gemm_bf16_grouped: more than 2^31-1 rows");
+  }
+  if (rows == 0) return GEMM_B200_OK;
+  if (N > 0x7fffffff || K > 0x7fffffff) return fail(GEMM_B200_ERR_TOO_LARGE, "gemm_bf16_grouped: a dimension exceeds 2^31-1");
+  if (!C || (K > 0 && (!A || !B))) return fail(GEMM_B200_ERR_INVALID_ARG, "gemm_bf16_grouped: null pointer");
+  const int64_t b_row = (b_layout == GEMM_B200_B_ROW_MAJOR_KN) ? N : K, b_rows = (b_layout == GEMM_B200_B_ROW_MAJOR_KN) ? K : N;
+  if (lda < K || ldb < b_row || ldc < N || (groups > 1 && stride_b < (b_rows - 1) * ldb + b_row))
+    return fail(GEMM_B200_ERR_INVALID_ARG, "gemm_bf16_grouped: a leading dimension or stride_b is smaller than its matrix");
+  const int c_elem = out_dtype == GEMM_B200_OUT_F32 ? 4 : 2;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (K == 0) {
+    GEMM_B200_CUDA_TRY(cudaMemset2DAsync(C, (size_t)ldc * c_elem, 0, (size_t)N * c_elem, (size_t)rows, st));
+    return GEMM_B200_OK;
+  }
+  if ((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(B) | reinterpret_cast<uintptr_t>(C)) % 16 != 0)
+    return fail(GEMM_B200_ERR_ALIGNMENT, "gemm_bf16_grouped: A, B and C must be 16-byte aligned");
+  if (lda % 8 != 0 || ldb % 8 != 0 || stride_b % 8 != 0 || (ldc * c_elem) % 16 != 0 || N % (16 / c_elem) != 0)
+    return fail(GEMM_B200_ERR_ALIGNMENT,
+                "gemm_bf16_grouped: lda, ldb and stride_b must be multiples of 8, ldc*sizeof(C) and N*sizeof(C) of 16 bytes");
+  tc::DeviceInfo di;
+  if (int rc = tc::device_info(&di)) return rc;
+  if (di.cc_major != 10)
+    return fail(GEMM_B200_ERR_UNSUPPORTED, "gemm_bf16_grouped: device has compute capability %d.x, need 10.x (sm_100a)", di.cc_major);
+  const bool mn = b_layout == GEMM_B200_B_ROW_MAJOR_KN, f32 = out_dtype == GEMM_B200_OUT_F32;
+  // kMaxGroups groups per launch; their rows of A and C and their B matrices follow one another
+  int64_t row0 = 0;
+  for (int64_t g0 = 0; g0 < groups; g0 += tc::kMaxGroups) {
+    const int n = (int)(groups - g0 < tc::kMaxGroups ? groups - g0 : tc::kMaxGroups);
+    const char* a = static_cast<const char*>(A) + row0 * lda * 2;
+    const char* b = static_cast<const char*>(B) + g0 * stride_b * 2;
+    char* c = static_cast<char*>(C) + row0 * ldc * c_elem;
+    const int rc = mn ? (f32 ? tc::launch_bf16_grouped<true, true>(a, b, c, n, m_sizes + g0, N, K, lda, ldb, stride_b, ldc, st)
+                             : tc::launch_bf16_grouped<true, false>(a, b, c, n, m_sizes + g0, N, K, lda, ldb, stride_b, ldc, st))
+                      : (f32 ? tc::launch_bf16_grouped<false, true>(a, b, c, n, m_sizes + g0, N, K, lda, ldb, stride_b, ldc, st)
+                             : tc::launch_bf16_grouped<false, false>(a, b, c, n, m_sizes + g0, N, K, lda, ldb, stride_b, ldc, st));
+    if (rc) return rc;
+    for (int g = 0; g < n; ++g) row0 += m_sizes[g0 + g];
+  }
+  return GEMM_B200_OK;
 }
 
 extern "C" int gemm_b200_gemm_bf16_batched(const void* A, const void* B, void* C, int64_t batch, int64_t M, int64_t N,

@@ -14,7 +14,7 @@ from . import _lib
 from ._lib import lib, check
 
 __all__ = [
-    "sgemm_f32", "sgemm_f32_batched", "gemm_bf16", "gemm_bf16_batched", "check_status", "sgemm_f32_host", "gemm_bf16_host",
+    "sgemm_f32", "sgemm_f32_batched", "gemm_bf16", "gemm_bf16_batched", "gemm_bf16_grouped", "check_status", "sgemm_f32_host", "gemm_bf16_host",
     "sgemm_f32_configs", "gemm_bf16_configs", "launch_count",
     "quantize_mxfp8", "gemm_mxfp8", "gemm_mxfp8_configs", "MxFp8Tensor", "gemm_mxfp8_splitk", "gemm_mxfp8_auto_splits", "gemm_mxfp8_quant_out",
 ]
@@ -183,6 +183,31 @@ def sgemm_f32_batched(A: torch.Tensor, B: torch.Tensor, out: torch.Tensor | None
     with _OnDevice(A.device):
         check(lib.gemm_b200_sgemm_f32_batched(A.data_ptr(), B.data_ptr(), out.data_ptr(), batch, M, N, K, lda, ldb, ldc,
                                               sa, sb, sc, _stream(A)))
+    return out
+
+
+def gemm_bf16_grouped(A: torch.Tensor, B: torch.Tensor, m_sizes, out: torch.Tensor | None = None, *, b_is_nk: bool = False,
+                      out_dtype: torch.dtype = torch.bfloat16) -> torch.Tensor:
+    """Grouped (ragged) BF16 GEMM: rows of ``A`` [sum(m_sizes), K] belong to consecutive groups,
+    group g is multiplied by ``B[g]`` ([groups, K, N], or [groups, N, K] with ``b_is_nk``) into the
+    same rows of ``out`` [sum(m_sizes), N].  ``m_sizes``: a sequence of row counts on the host."""
+    _require(A.is_cuda and B.is_cuda, "A and B must be CUDA tensors")
+    _require(A.dtype == torch.bfloat16 and B.dtype == torch.bfloat16, "expected bfloat16")
+    _require(A.dim() == 2 and B.dim() == 3, "A must be 2-D and B 3-D")
+    sizes = [int(m) for m in m_sizes]
+    groups, rows, K = len(sizes), int(A.shape[0]), int(A.shape[1])
+    _require(B.shape[0] == groups and sum(sizes) == rows, f"{groups} groups with {sum(sizes)} rows, but A has {rows} rows and B {B.shape[0]} matrices")
+    N = int(B.shape[1] if b_is_nk else B.shape[2])
+    _require(int(B.shape[2] if b_is_nk else B.shape[1]) == K, f"A is {tuple(A.shape)} but B is {tuple(B.shape)}")
+    ldb, sb = _batch_layout(B)
+    if out is None:
+        out = torch.empty((rows, N), device=A.device, dtype=out_dtype)
+    _require(out.is_cuda and out.dtype == out_dtype and tuple(out.shape) == (rows, N), "bad out tensor")
+    arr = (C.c_int64 * max(groups, 1))(*sizes)
+    with _OnDevice(A.device):
+        check(lib.gemm_b200_gemm_bf16_grouped(A.data_ptr(), B.data_ptr(), out.data_ptr(), groups, arr, N, K, _row_major_ld(A), ldb, sb,
+                                              _row_major_ld(out), _lib.B_ROW_MAJOR_NK if b_is_nk else _lib.B_ROW_MAJOR_KN,
+                                              _lib.OUT_F32 if out_dtype == torch.float32 else _lib.OUT_BF16, _stream(A)))
     return out
 
 

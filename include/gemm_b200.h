@@ -149,6 +149,18 @@ int gemm_b200_gemm_bf16_batched(const void* A, const void* B, void* C, int64_t b
                                 int64_t stride_a, int64_t stride_b, int64_t stride_c,
                                 int b_layout, int out_dtype, void* stream);
 
+/* Grouped (ragged) form: `groups` problems that share N and K but have their own row count,
+ *   C[rows of group g, :] = A[rows of group g, :] @ B_g,   B_g = B + g * stride_b,
+ * where the groups' rows follow one another in one tall A [sum m_sizes, K] (lda) and one tall
+ * C [sum m_sizes, N] (ldc): the layout of tokens sorted by expert in a mixture-of-experts layer.
+ * m_sizes is a HOST array of `groups` row counts (zero allowed).  One launch per 64 groups, each
+ * walking all (group, tile) pairs; bit-identical to one gemm_b200_gemm_bf16_cfg call per group with
+ * variant "1cta_128x256x64_s4_direct".  The reference multiplies one pair of matrices per call
+ * (naive/naive.cpp:6-22); no counterpart. */
+int gemm_b200_gemm_bf16_grouped(const void* A, const void* B, void* C, int64_t groups, const int64_t* m_sizes,
+                                int64_t N, int64_t K, int64_t lda, int64_t ldb, int64_t stride_b, int64_t ldc,
+                                int b_layout, int out_dtype, void* stream);
+
 /* -------------------------------------------------------------------------
  * MXFP8 (OCP microscaling): e4m3 data with one UE8M0 scale per 32 consecutive
  * K elements.  No counterpart in the reference; same operator semantics as
