@@ -12,7 +12,7 @@ from pathlib import Path
 LIB_PATH = Path(os.environ.get("GEMM_B200_LIB") or (Path(__file__).resolve().parent / "libgemm_b200.so"))
 
 OK = 0
-ERR_INVALID_ARG, ERR_ALIGNMENT, ERR_UNSUPPORTED, ERR_CUDA, ERR_TIMEOUT, ERR_TOO_LARGE = -1, -2, -3, -4, -5, -6
+ERR_INVALID_ARG, ERR_ALIGNMENT, ERR_UNSUPPORTED, ERR_CUDA, ERR_TIMEOUT, ERR_TOO_LARGE, ERR_BOUNDS = -1, -2, -3, -4, -5, -6, -7
 OUT_BF16, OUT_F32 = 0, 1
 B_ROW_MAJOR_KN, B_ROW_MAJOR_NK = 0, 1
 

@@ -9,6 +9,7 @@ Produces, next to the sources (all git-ignored, all shipped with the working tre
   not part of the GEMM library);
 * ``gemm_b200/profiling/libgemm_b200_trace.so`` — the library compiled with its opt-in stage
   timeline (``-DGEMM_B200_TRACE``), for ``python -m gemm_b200.profiling.run_trace``;
+* ``gemm_b200/profiling/libgemm_b200_debug.so`` — the bounds-checking build (``-DGEMM_B200_DEBUG``);
 * ``gemm_b200/variants/<variant>/<module>.so`` — one PyTorch extension module per reference
   variant, with the reference's module and function names
   (naive/test.py:5-11, shared/test.py:5-11, blocktile_1d/test.py:5-11).
@@ -114,19 +115,30 @@ def build_probe(force: bool = False) -> Path:
     return PROBE_LIB
 
 
+def build_debug(force: bool = False) -> Path:
+    """The bounds-checking build (-DGEMM_B200_DEBUG): gemm_b200/profiling/libgemm_b200_debug.so.  Every
+    access the kernels address themselves is checked against its matrix first; one that falls
+    outside is skipped and recorded (GEMM_B200_ERR_BOUNDS), never made.  Load it with GEMM_B200_LIB."""
+    return _build_flavour("debug", "-DGEMM_B200_DEBUG", force)
+
+
 def build_trace(force: bool = False) -> Path:
     """The library with the stage timeline compiled in (-DGEMM_B200_TRACE), for gemm_b200.profiling.run_trace:
     gemm_b200/profiling/libgemm_b200_trace.so.  Load it with GEMM_B200_LIB=<that path>."""
-    out = PKG / "profiling" / "libgemm_b200_trace.so"
+    return _build_flavour("trace", "-DGEMM_B200_TRACE", force)
+
+
+def _build_flavour(name: str, define: str, force: bool) -> Path:
+    out = PKG / "profiling" / f"libgemm_b200_{name}.so"
     if not force and _newer(out, [CSRC / src for src in LIB_SOURCES] + _headers()):
         return out
-    bdir = BUILD / "trace"
+    bdir = BUILD / name
     bdir.mkdir(parents=True, exist_ok=True)
     objs, jobs = [], []
     for src, extra in LIB_SOURCES.items():
         o = bdir / (Path(src).stem + ".o")
         objs.append(o)
-        jobs.append([nvcc(), *ARCH, *NVCC_COMMON, *HOST_WARNINGS, *extra, "-DGEMM_B200_TRACE", "-c", str(CSRC / src), "-o", str(o)])
+        jobs.append([nvcc(), *ARCH, *NVCC_COMMON, *HOST_WARNINGS, *extra, define, "-c", str(CSRC / src), "-o", str(o)])
     with cf.ThreadPoolExecutor(max_workers=len(jobs)) as ex:
         list(ex.map(_run, jobs))
     _run([nvcc(), *ARCH, "-shared", "-o", str(out), *map(str, objs)])
@@ -177,6 +189,7 @@ def build_all(variants: bool = True, force: bool = False, verbose: bool = False)
     build_library(force=force, verbose=verbose)
     build_probe(force=force)
     build_trace(force=force)
+    build_debug(force=force)
     if variants:
         with cf.ThreadPoolExecutor(max_workers=3) as ex:
             list(ex.map(lambda v: build_variant(v, force=force), VARIANTS))
@@ -189,9 +202,13 @@ def main(argv: list[str] | None = None) -> int:
     ap.add_argument("--verbose", action="store_true", help="pass -Xptxas=-v")
     ap.add_argument("--tuning", action="store_true", help="also build the kernel variants only tuning sweeps use")
     ap.add_argument("--trace", action="store_true", help="build only the stage-timeline variant of the library (profiling/)")
+    ap.add_argument("--debug", action="store_true", help="build only the bounds-checking variant of the library (profiling/)")
     a = ap.parse_args(argv)
     if a.trace:
         print(build_trace(force=True))
+        return 0
+    if a.debug:
+        print(build_debug(force=True))
         return 0
     if a.tuning:
         TUNING.append("-DGEMM_B200_TUNING")

@@ -57,4 +57,47 @@ inline bool log_enabled() {
   return on;
 }
 
+// ---------------------------------------------------------------------------------------
+// Bounds-checking build (-DGEMM_B200_DEBUG, `python -m gemm_b200.build --debug`): every global
+// access that the kernels address themselves (TMA transfers are clipped by the tensor map in
+// hardware) is first checked against the extent of its matrix.  An access that falls outside is
+// NOT made: the thread records {GEMM_B200_ERR_BOUNDS, block, site, byte offset} in a status word
+// of its translation unit and goes on, so a wrong index shows up as an error code on the host, never
+// as a fault.  gemm_b200_debug_bounds_f32 / _tc read and clear the word.  Release builds compile
+// the checks away.
+// ---------------------------------------------------------------------------------------
+#ifdef GEMM_B200_DEBUG
+namespace dbg {
+static __device__ __attribute__((unused)) int32_t g_bounds[4];
+// test knob: every checked extent is understated by this many bytes, so that accesses near the end
+// of a matrix are refused (and skipped) without any access ever leaving the matrix
+static __device__ __attribute__((unused)) long long g_shrink;
+__device__ __forceinline__ bool in_bounds(const void* p, const void* base, long long bytes, int access, int site) {
+  const long long off = static_cast<const char*>(p) - static_cast<const char*>(base);
+  if (off >= 0 && off + access <= bytes - g_shrink) return true;
+  if (atomicCAS(&g_bounds[0], 0, GEMM_B200_ERR_BOUNDS) == 0) {
+    g_bounds[1] = (int32_t)blockIdx.x;
+    g_bounds[2] = site;
+    g_bounds[3] = (int32_t)(off < 0 ? -1 : (off > 0x7fffffffLL ? 0x7fffffffLL : off));
+  }
+  return false;
+}
+// host side of the two debug entry points: read and clear the word, set the test knob
+static inline int read_bounds(int32_t out[4], long long shrink) {
+  GEMM_B200_CUDA_TRY(cudaDeviceSynchronize());
+  int32_t h[4] = {0, 0, 0, 0};
+  GEMM_B200_CUDA_TRY(cudaMemcpyFromSymbol(h, g_bounds, sizeof(h)));
+  const int32_t z[4] = {0, 0, 0, 0};
+  GEMM_B200_CUDA_TRY(cudaMemcpyToSymbol(g_bounds, z, sizeof(z)));
+  GEMM_B200_CUDA_TRY(cudaMemcpyToSymbol(g_shrink, &shrink, sizeof(shrink)));
+  if (out)
+    for (int i = 0; i < 4; ++i) out[i] = h[i];
+  return h[0];
+}
+}  // namespace dbg
+#define GEMM_B200_IN_BOUNDS(p, base, bytes, access, site) ::gemm_b200::dbg::in_bounds(p, base, (long long)(bytes), access, site)
+#else
+#define GEMM_B200_IN_BOUNDS(p, base, bytes, access, site) true
+#endif
+
 }  // namespace gemm_b200

@@ -449,18 +449,22 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           tmem_ld_32x32b_x32(t_addr + c * 32, v);
           tmem_ld_wait();
           const int col = n0 + c * 32;
+          // extent of everything this launch may store to (bounds-checking build)
+          const long long c_elems = (long long)(shape.batch - 1) * shape.c_batch_stride + (long long)(shape.k_splits - 1) * shape.split_stride +
+                                    (long long)(shape.M - 1) * ldc + shape.N;
+          (void)c_elems;
           if (row < row_end) {
             if constexpr (OUT_F32) {
               float* dst = reinterpret_cast<float*>(Cptr) + bi * shape.c_batch_stride + split * shape.split_stride + (int64_t)row * ldc + col;
 #pragma unroll
               for (int j = 0; j < 8; ++j)
-                if (col + 4 * j < shape.N)
+                if (col + 4 * j < shape.N && GEMM_B200_IN_BOUNDS(dst + 4 * j, Cptr, c_elems * 4, 16, 10))
                   *reinterpret_cast<uint4*>(dst + 4 * j) = make_uint4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
             } else {
               __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(Cptr) + bi * shape.c_batch_stride + (int64_t)row * ldc + col;
 #pragma unroll
               for (int j = 0; j < 4; ++j) {
-                if (col + 8 * j < shape.N) {
+                if (col + 8 * j < shape.N && GEMM_B200_IN_BOUNDS(dst + 8 * j, Cptr, c_elems * 2, 16, 11)) {
                   uint32_t p[4];
 #pragma unroll
                   for (int e = 0; e < 4; ++e) {

@@ -395,6 +395,9 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
         if (row < rows_pad && nb0 < kchunks * 4)                          // inside the padded scale buffer
           *reinterpret_cast<uint32_t*>(SFC + mx::scale_offset(kchunks, row, nb0)) = scale_word;   // padding -> 0
       } else if (row < shape.M) {
+        // extent of everything this launch may store to (bounds-checking build)
+        const long long c_elems = (long long)(shape.k_splits - 1) * shape.split_stride + (long long)(shape.M - 1) * ldc + shape.N;
+        (void)c_elems;
 #pragma unroll
         for (int c = 0; c < NCH; ++c) {
           const int col = col0 + c * 32;
@@ -402,14 +405,14 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
             float* dst = reinterpret_cast<float*>(Cptr) + (int64_t)split * shape.split_stride + (int64_t)row * ldc + col;
 #pragma unroll
             for (int j = 0; j < 8; ++j)
-              if (col + 4 * j < shape.N)
+              if (col + 4 * j < shape.N && GEMM_B200_IN_BOUNDS(dst + 4 * j, Cptr, c_elems * 4, 16, 20))
                 *reinterpret_cast<uint4*>(dst + 4 * j) =
                     make_uint4(v[c][4 * j], v[c][4 * j + 1], v[c][4 * j + 2], v[c][4 * j + 3]);
           } else {
             __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(Cptr) + (int64_t)row * ldc + col;   // k_splits == 1
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
-              if (col + 8 * j < shape.N) {
+              if (col + 8 * j < shape.N && GEMM_B200_IN_BOUNDS(dst + 8 * j, Cptr, c_elems * 2, 16, 21)) {
                 uint32_t p[4];
 #pragma unroll
                 for (int e = 0; e < 4; ++e) {
@@ -467,11 +470,19 @@ splitk_reduce_kernel(const float* __restrict__ W, int64_t split_stride, int64_t 
   if (idx >= (int64_t)M * n4) return;
   const int64_t r = idx / n4, c = (idx % n4) * 4;
   const float* src = W + r * ldw + c;
+  const long long w_bytes = ((long long)(k_splits - 1) * split_stride + (long long)(M - 1) * ldw + N) * 4;
+  const long long c_elems = (long long)(M - 1) * ldc + N;
+  (void)w_bytes; (void)c_elems;
+  if (!GEMM_B200_IN_BOUNDS(src, W, w_bytes, 16, 30)) return;
   float4 acc = *reinterpret_cast<const float4*>(src);
   for (int s = 1; s < k_splits; ++s) {
+    if (!GEMM_B200_IN_BOUNDS(src + (int64_t)s * split_stride, W, w_bytes, 16, 30)) return;
     const float4 v = *reinterpret_cast<const float4*>(src + (int64_t)s * split_stride);
     acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
   }
+  if (!GEMM_B200_IN_BOUNDS(reinterpret_cast<char*>(Cptr) + (r * ldc + c) * (OUT_F32 ? 4 : 2), Cptr, c_elems * (OUT_F32 ? 4 : 2),
+                           OUT_F32 ? 16 : 8, 31))
+    return;
   if constexpr (OUT_F32) {
     *reinterpret_cast<float4*>(reinterpret_cast<float*>(Cptr) + r * ldc + c) = acc;
   } else {

@@ -64,7 +64,8 @@ quantize_rows_kernel(const __nv_bfloat16* __restrict__ X, int64_t rows, int64_t 
   if (r >= rows_pad) return;
   const int64_t KB = K / 32, kchunks = kb_pad / 4;
   uint32_t byte = 0;
-  if (r < rows && kb < KB) {
+  if (r < rows && kb < KB && GEMM_B200_IN_BOUNDS(X + r * ldx + kb * 32, X, ((rows - 1) * ldx + K) * 2, 64, 40) &&
+      GEMM_B200_IN_BOUNDS(Xq + r * K + kb * 32, Xq, rows * K, 32, 41)) {
     const uint4* src = reinterpret_cast<const uint4*>(X + r * ldx + kb * 32);
     uint32_t w[16], q[8];
 #pragma unroll
@@ -77,7 +78,8 @@ quantize_rows_kernel(const __nv_bfloat16* __restrict__ X, int64_t rows, int64_t 
     dst[0] = make_uint4(q[0], q[1], q[2], q[3]);
     dst[1] = make_uint4(q[4], q[5], q[6], q[7]);
   }
-  SF[scale_offset(kchunks, r, kb)] = (uint8_t)byte;
+  if (GEMM_B200_IN_BOUNDS(SF + scale_offset(kchunks, r, kb), SF, (rows_pad / 128) * kchunks * 512, 1, 42))
+    SF[scale_offset(kchunks, r, kb)] = (uint8_t)byte;
 }
 
 // X [K, rows] row-major (ldx): quantise every column along K, write Xq [rows, K] K-contiguous.

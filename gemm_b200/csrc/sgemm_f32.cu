@@ -122,14 +122,16 @@ sgemm_kernel(const float* __restrict__ A, const float* __restrict__ B, float* __
 #pragma unroll
       for (int it = 0; it < A_IT; ++it) {
         if (!A_EVEN && a_r + it * A_RPI >= BM) break;
-        const bool ok = a_k_ok && (row0 + a_r + it * A_RPI < M);
         const float* src = a_src + (int64_t)(it * A_RPI) * lda + k0;
+        const bool ok = a_k_ok && (row0 + a_r + it * A_RPI < M) &&
+                        GEMM_B200_IN_BOUNDS(src, A, ((long long)(M - 1) * lda + K) * 4, 16, 3);
         cp_async16(a_sdst + (slot * C::A_STAGE + it * A_RPI * LDA_S) * 4, ok ? src : A, ok ? 16 : 0);
       }
 #pragma unroll
       for (int it = 0; it < B_IT; ++it) {
-        const bool ok = b_col_ok && (k0 + b_r + it * B_RPI < K);
         const float* src = b_src + (int64_t)(k0 + it * B_RPI) * ldb;
+        const bool ok = b_col_ok && (k0 + b_r + it * B_RPI < K) &&
+                        GEMM_B200_IN_BOUNDS(src, B, ((long long)(K - 1) * ldb + N) * 4, 16, 4);
         cp_async16(b_sdst + (slot * C::B_STAGE + it * B_RPI * BN) * 4, ok ? src : B, ok ? 16 : 0);
       }
     } else {
@@ -235,17 +237,19 @@ sgemm_kernel(const float* __restrict__ A, const float* __restrict__ B, float* __
     const int gr = row0 + wm * (BM / C::WMW) + ty + 4 * i;
     if (gr >= M) continue;
     float* crow = Cm + (int64_t)gr * ldc;
+    const long long c_bytes = ((long long)(M - 1) * ldc + N) * 4;   // extent of C (bounds-checking build)
+    (void)c_bytes;
 #pragma unroll
     for (int c = 0; c < TNC; ++c) {
       const int gc = col0 + wn * (BN / C::WNW) + c * 32 + tx * 4;
       if constexpr (VEC == 4) {
-        if (gc < N)
+        if (gc < N && GEMM_B200_IN_BOUNDS(crow + gc, Cm, c_bytes, 16, 1))
           *reinterpret_cast<float4*>(crow + gc) =
               make_float4(acc2[i][2 * c].x, acc2[i][2 * c].y, acc2[i][2 * c + 1].x, acc2[i][2 * c + 1].y);
       } else {
 #pragma unroll
         for (int e = 0; e < 4; ++e)
-          if (gc + e < N) crow[gc + e] = (e & 1) ? acc2[i][2 * c + e / 2].y : acc2[i][2 * c + e / 2].x;
+          if (gc + e < N && GEMM_B200_IN_BOUNDS(crow + gc + e, Cm, c_bytes, 4, 2)) crow[gc + e] = (e & 1) ? acc2[i][2 * c + e / 2].y : acc2[i][2 * c + e / 2].x;
       }
     }
   }
@@ -467,3 +471,9 @@ extern "C" const char* gemm_b200_sgemm_f32_config_name(int config) {
   if (config < 0 || config >= gemm_b200::f32::kNumConfigs) return "";
   return gemm_b200::f32::kConfigs[config].name;
 }
+
+#ifdef GEMM_B200_DEBUG
+// Bounds-checking build only: reads and clears the status word of the FP32 kernels' checks
+// ({code, block, site, byte offset}; code 0 = clean) and sets the test knob `shrink`.
+extern "C" int gemm_b200_debug_bounds_f32(int32_t out[4], long long shrink) { return gemm_b200::dbg::read_bounds(out, shrink); }
+#endif

@@ -1444,3 +1444,10 @@ extern "C" int gemm_b200_trace_read(unsigned long long* out, int blocks) {
   return GEMM_B200_OK;
 }
 #endif
+
+#ifdef GEMM_B200_DEBUG
+// Bounds-checking build only: reads and clears the status word of the tensor-core side's checks
+// (direct-store epilogues, split-K partial sums and their reduction, the row-wise quantiser) and
+// sets the test knob `shrink`.  {code, block, site, byte offset}; code 0 = clean.
+extern "C" int gemm_b200_debug_bounds_tc(int32_t out[4], long long shrink) { return gemm_b200::dbg::read_bounds(out, shrink); }
+#endif

@@ -34,6 +34,7 @@ extern "C" {
 #define GEMM_B200_ERR_CUDA          -4  /* a CUDA runtime / driver call failed             */
 #define GEMM_B200_ERR_TIMEOUT       -5  /* a bounded device-side wait ran out              */
 #define GEMM_B200_ERR_TOO_LARGE     -6  /* size exceeds a documented maximum               */
+#define GEMM_B200_ERR_BOUNDS        -7  /* bounds-checking build: an access fell outside its matrix (skipped, not made) */
 
 /* element types of C for the tensor-core paths */
 #define GEMM_B200_OUT_BF16 0

@@ -30,6 +30,17 @@ def test_library_exports_every_declared_symbol():
     assert set(_lib.SIGNATURES) == set(declared_symbols())
 
 
+def test_diagnostic_builds_export_the_same_entry_points_plus_their_own():
+    prof = ROOT / "gemm_b200" / "profiling"
+    for lib, extra in (("libgemm_b200_debug.so", ["gemm_b200_debug_bounds_f32", "gemm_b200_debug_bounds_tc"]),
+                       ("libgemm_b200_trace.so", ["gemm_b200_trace_read"])):
+        raw = C.CDLL(str(prof / lib))
+        for name in declared_symbols() + extra:
+            assert hasattr(raw, name), (lib, name)
+    release = C.CDLL(str(ROOT / "gemm_b200" / "libgemm_b200.so"))
+    assert not hasattr(release, "gemm_b200_debug_bounds_tc") and not hasattr(release, "gemm_b200_trace_read")
+
+
 def test_version_and_config_tables():
     from gemm_b200 import _lib
     assert _lib.lib.gemm_b200_version() == 100
