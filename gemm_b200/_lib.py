@@ -28,6 +28,7 @@ SIGNATURES = {
     "gemm_b200_gemm_bf16": (i32, [vp, vp, vp, i64, i64, i64, i64, i64, i64, i32, i32, vp]),
     "gemm_b200_gemm_bf16_cfg": (i32, [vp, vp, vp, i64, i64, i64, i64, i64, i64, i32, i32, i32, vp]),
     "gemm_b200_gemm_bf16_batched": (i32, [vp, vp, vp, i64, i64, i64, i64, i64, i64, i64, i64, i64, i64, i32, i32, vp]),
+    "gemm_b200_gemm_bf16_at": (i32, [vp, vp, vp, i64, i64, i64, i64, i64, i64, i32, i32, vp]),
     "gemm_b200_gemm_bf16_grouped": (i32, [vp, vp, vp, i64, C.POINTER(C.c_int64), i64, i64, i64, i64, i64, i64, i32, i32, vp]),
     "gemm_b200_gemm_bf16_splitk": (i32, [vp, vp, vp, i64, i64, i64, i64, i64, i64, i32, i32, i32, vp, sz, vp]),
     "gemm_b200_gemm_bf16_cluster_splitk": (i32, [vp, vp, vp, i64, i64, i64, i64, i64, i64, i32, i32, i32, vp]),

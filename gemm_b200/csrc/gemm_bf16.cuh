@@ -190,7 +190,7 @@ __device__ __forceinline__ void tile_coord(int t, const GemmShape& sh, int& tm, 
   }
 }
 
-template <class Cfg, bool B_MN, bool OUT_F32>
+template <class Cfg, bool B_MN, bool OUT_F32, bool A_MN = false>
 __global__ void __launch_bounds__(Cfg::THREADS, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                  const __grid_constant__ CUtensorMap tmC, void* __restrict__ Cptr, int64_t ldc,
@@ -328,7 +328,13 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         if (issuer) {
           if (cta_rank == 0) mbar_arrive_expect_tx(full_bar(s), CG * Cfg::STAGE_BYTES);
           if (it == 0) trace_stamp(2);
-          load_p(a_dst, &tmA, kb * kBlockK, m0, az, bar, pol_a);
+          if constexpr (A_MN) {
+            // A stored transposed ([K, M] row-major): 64-row chunks of 64 k x 128 bytes, like B in that layout
+#pragma unroll
+            for (int j = 0; j < kBlockM / 64; ++j) load_p(a_dst + j * 8192, &tmA, m0 + j * 64, kb * kBlockK, az, bar, pol_a);
+          } else {
+            load_p(a_dst, &tmA, kb * kBlockK, m0, az, bar, pol_a);
+          }
 #pragma unroll
           for (int nt = 0; nt < NT; ++nt) {
             const uint32_t b_dst = sB0 + (s * NT + nt) * Cfg::B_BYTES;
@@ -359,8 +365,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     // one elected lane issues the tcgen05 instructions.
     if (cta_rank == 0) {
       const bool issuer = elect_one();
-      constexpr uint32_t idesc = make_idesc_bf16(kBlockM * CG, BN, 0, B_MN ? 1 : 0);
-      constexpr uint64_t a_hi = make_smem_desc_hi(16, 1024, kLayoutSw128);
+      constexpr uint32_t idesc = make_idesc_bf16(kBlockM * CG, BN, A_MN ? 1 : 0, B_MN ? 1 : 0);
+      constexpr uint64_t a_hi = A_MN ? make_smem_desc_hi(8192, 1024, kLayoutSw128)
+                                     : make_smem_desc_hi(16, 1024, kLayoutSw128);
+      constexpr uint32_t a_kstep = A_MN ? (kUmmaK * 128) : (kUmmaK * 2);
       constexpr uint64_t b_hi = B_MN ? make_smem_desc_hi(8192, 1024, kLayoutSw128)
                                      : make_smem_desc_hi(16, 1024, kLayoutSw128);
       constexpr uint32_t b_kstep = B_MN ? (kUmmaK * 128) : (kUmmaK * 2);
@@ -397,7 +405,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
 #pragma unroll
               for (int nt = 0; nt < NT; ++nt) {
                 const uint32_t b_addr = sB0 + (s * NT + nt) * Cfg::B_BYTES;
-                mma_f16<CG>(d_tmem + nt * BN, smem_desc(a_hi, a_addr + k * (kUmmaK * 2)),
+                mma_f16<CG>(d_tmem + nt * BN, smem_desc(a_hi, a_addr + k * a_kstep),
                             smem_desc(b_hi, b_addr + k * b_kstep), idesc, k != 0 ? 1u : first);
               }
             }

@@ -326,8 +326,8 @@ struct Bf16Args {
   int k_splits = 1;
 };
 
-// One instantiation per (config, B layout, output type).
-template <class Cfg, bool B_MN, bool OUT_F32>
+// One instantiation per (config, B layout, output type); A_MN: A is stored transposed, [K, M] row-major.
+template <class Cfg, bool B_MN, bool OUT_F32, bool A_MN = false>
 static int launch_bf16(const Bf16Args& a) {
   constexpr int CG = Cfg::CG;
   DeviceInfo di;
@@ -335,12 +335,18 @@ static int launch_bf16(const Bf16Args& a) {
   CUtensorMap tmA, tmB, tmC;
   // a shared operand (stride 0) is mapped as one matrix; the kernel then always asks for matrix 0
   const int64_t za = a.stride_a ? a.batch : 1, zb = a.stride_b ? a.batch : 1;
-  const int64_t sa = a.stride_a ? a.stride_a : a.M * a.lda;
+  const int64_t sa = a.stride_a ? a.stride_a : (A_MN ? a.K : a.M) * a.lda;
   const int64_t sb = a.stride_b ? a.stride_b : (B_MN ? a.K : a.N) * a.ldb;
   const int64_t sc = a.batch > 1 ? a.stride_c : a.M * a.ldc;
-  if (int rc = make_map_3d(&tmA, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, a.A, a.M, a.K, a.lda, za, sa, kBlockK, kBlockM,
-                           CU_TENSOR_MAP_SWIZZLE_128B))
-    return rc;
+  if (A_MN) {
+    if (int rc = make_map_3d(&tmA, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, a.A, a.K, a.M, a.lda, za, sa, 64, kBlockK,
+                             CU_TENSOR_MAP_SWIZZLE_128B))
+      return rc;
+  } else {
+    if (int rc = make_map_3d(&tmA, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, a.A, a.M, a.K, a.lda, za, sa, kBlockK, kBlockM,
+                             CU_TENSOR_MAP_SWIZZLE_128B))
+      return rc;
+  }
   if (B_MN) {
     if (int rc = make_map_3d(&tmB, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, a.B, a.K, a.N, a.ldb, zb, sb, 64, kBlockK,
                              CU_TENSOR_MAP_SWIZZLE_128B))
@@ -359,7 +365,7 @@ static int launch_bf16(const Bf16Args& a) {
     tmC = tmA;   // unused by the kernel
   }
 
-  auto kern = gemm_bf16_kernel<Cfg, B_MN, OUT_F32>;
+  auto kern = gemm_bf16_kernel<Cfg, B_MN, OUT_F32, A_MN>;
   int max_clusters = 0;
   if (int rc = persistent_clusters(kern, CG, Cfg::THREADS, Cfg::SMEM_BYTES, di, &max_clusters)) return rc;
 
@@ -525,6 +531,27 @@ static const Bf16ConfigEntry kBf16Configs[] = {
 #endif
 };
 static_assert(sizeof(kBf16Configs) / sizeof(kBf16Configs[0]) == kNumBf16Configs, "table and enum out of step");
+
+// A stored transposed ([K, M] row-major, the layout of an activation matrix in the weight-gradient
+// product X^T dY): the multi-round tile shapes and the single-CTA tile.
+struct Bf16AtEntry {
+  int config;
+  int (*launch[2][2])(const Bf16Args&);   // [b_layout][out_dtype]
+};
+#define GEMM_B200_BF16_AT_ENTRY(ID, CFG)                                                         \
+  {                                                                                              \
+    ID, {                                                                                        \
+      {launch_bf16<CFG, true, false, true>, launch_bf16<CFG, true, true, true>},                 \
+      {launch_bf16<CFG, false, false, true>, launch_bf16<CFG, false, true, true>}                \
+    }                                                                                            \
+  }
+static const Bf16AtEntry kBf16AtConfigs[] = {
+    GEMM_B200_BF16_AT_ENTRY(kBf16Cfg1cta, Bf16_1cta_tma),
+    GEMM_B200_BF16_AT_ENTRY(kBf16Cfg256, Bf16_2cta_tma_m),
+    GEMM_B200_BF16_AT_ENTRY(kBf16Cfg512, Bf16_2cta_n512_s3),
+    GEMM_B200_BF16_AT_ENTRY(kBf16Cfg256Dyn, Bf16_2cta_tma_m_dyn),
+    GEMM_B200_BF16_AT_ENTRY(kBf16Cfg512Dyn, Bf16_2cta_n512_s3_dyn),
+};
 
 // 256x512 tiles move 25 % fewer operand bytes per flop and measure ~4 % faster when both tile
 // shapes fill their rounds equally well; with few tiles the coarser grid wastes more of the last
@@ -756,8 +783,80 @@ static int bf16_entry(const void* A, const void* B, void* C, int64_t batch, int6
   return kBf16Configs[config].launch[b_layout][out_dtype](args);
 }
 
+// C = A^T-stored @ B: A is [K, M] row-major (lda >= M).  One launch, tile shape by the same rule as
+// the plain entry; no K splits.
+static int bf16_at_entry(const void* A, const void* B, void* C, int64_t M, int64_t N, int64_t K, int64_t lda, int64_t ldb,
+                         int64_t ldc, int b_layout, int out_dtype, void* stream) {
+  if (M < 0 || N < 0 || K < 0) return fail(GEMM_B200_ERR_INVALID_ARG, "gemm_bf16_at: negative size");
+  if (b_layout != GEMM_B200_B_ROW_MAJOR_KN && b_layout != GEMM_B200_B_ROW_MAJOR_NK)
+    return fail(GEMM_B200_ERR_INVALID_ARG, "gemm_bf16_at: b_layout %d", b_layout);
+  if (out_dtype != GEMM_B200_OUT_BF16 && out_dtype != GEMM_B200_OUT_F32)
+    return fail(GEMM_B200_ERR_INVALID_ARG, "gemm_bf16_at: out_dtype %d", out_dtype);
+  if (M == 0 || N == 0) return GEMM_B200_OK;
+  if (!C || (K > 0 && (!A || !B))) return fail(GEMM_B200_ERR_INVALID_ARG, "gemm_bf16_at: null pointer");
+  const int64_t b_row = (b_layout == GEMM_B200_B_ROW_MAJOR_KN) ? N : K;
+  if (lda < M || ldb < b_row || ldc < N)
+    return fail(GEMM_B200_ERR_INVALID_ARG, "gemm_bf16_at: leading dimension smaller than the row (lda=%lld ldb=%lld ldc=%lld)",
+                (long long)lda, (long long)ldb, (long long)ldc);
+  if (M > 0x7fffffff || N > 0x7fffffff || K > 0x7fffffff)
+    return fail(GEMM_B200_ERR_TOO_LARGE, "gemm_bf16_at: a dimension exceeds 2^31-1");
+  const int c_elem = out_dtype == GEMM_B200_OUT_F32 ? 4 : 2;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (K == 0) {
+    GEMM_B200_CUDA_TRY(cudaMemset2DAsync(C, (size_t)ldc * c_elem, 0, (size_t)N * c_elem, (size_t)M, st));
+    return GEMM_B200_OK;
+  }
+  if ((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(B) | reinterpret_cast<uintptr_t>(C)) % 16 != 0)
+    return fail(GEMM_B200_ERR_ALIGNMENT, "gemm_bf16_at: A, B and C must be 16-byte aligned");
+  if (lda % 8 != 0 || ldb % 8 != 0 || (ldc * c_elem) % 16 != 0 || N % (16 / c_elem) != 0)
+    return fail(GEMM_B200_ERR_ALIGNMENT,
+                "gemm_bf16_at: lda and ldb must be multiples of 8, ldc*sizeof(C) and N*sizeof(C) multiples of 16 bytes "
+                "(lda=%lld ldb=%lld ldc=%lld N=%lld)", (long long)lda, (long long)ldb, (long long)ldc, (long long)N);
+  DeviceInfo di;
+  if (int rc = device_info(&di)) return rc;
+  if (di.cc_major != 10)
+    return fail(GEMM_B200_ERR_UNSUPPORTED, "gemm_bf16_at: device has compute capability %d.x, need 10.x (sm_100a)", di.cc_major);
+  Bf16Args args{A, B, C, M, N, K, lda, ldb, ldc, st};
+  {
+    // few output tiles and a long K (a weight gradient over many tokens): FP32 partial sums per
+    // K range on the library's scratch, then the reduction pass, as in the plain entry
+    const int splits = bf16_auto_splits(M, N, K, di.sms);
+    float* ws = nullptr;
+    if (splits > 1) {
+      if (int rc = cached_scratch(di.dev, (size_t)splits * M * N * sizeof(float), &ws, st)) return rc;
+    }
+    if (ws) {
+      Bf16Args part = args;
+      part.C = ws;
+      part.ldc = N;
+      part.k_splits = splits;
+      if (log_enabled())
+        fprintf(stderr, "[gemm_b200] gemm_bf16_at %lldx%lldx%lld -> %s, %d K splits\n", (long long)M, (long long)K, (long long)N,
+                kBf16Configs[kBf16Cfg1ctaDirect].name, splits);
+      if (int rc = (b_layout == GEMM_B200_B_ROW_MAJOR_KN) ? launch_bf16<Bf16_1cta_direct, true, true, true>(part)
+                                                          : launch_bf16<Bf16_1cta_direct, false, true, true>(part))
+        return rc;
+      const int num_kb = (int)ceil_div64(K, kBlockK);
+      const int used = (int)ceil_div64(num_kb, ceil_div64(num_kb, splits));
+      return launch_splitk_reduce(ws, M, N, used, C, ldc, out_dtype, st);
+    }
+  }
+  const int config = pick_bf16_config(M, N, K, di.sms);
+  if (log_enabled())
+    fprintf(stderr, "[gemm_b200] gemm_bf16_at %lldx%lldx%lld -> %s\n", (long long)M, (long long)K, (long long)N,
+            kBf16Configs[config].name);
+  for (const Bf16AtEntry& e : kBf16AtConfigs)
+    if (e.config == config) return e.launch[b_layout][out_dtype](args);
+  return fail(GEMM_B200_ERR_UNSUPPORTED, "gemm_bf16_at: no transposed-A build of %s", kBf16Configs[config].name);
+}
+
 }  // namespace tc
 }  // namespace gemm_b200
+
+extern "C" int gemm_b200_gemm_bf16_at(const void* A, const void* B, void* C, int64_t M, int64_t N, int64_t K, int64_t lda,
+                                      int64_t ldb, int64_t ldc, int b_layout, int out_dtype, void* stream) {
+  return gemm_b200::tc::bf16_at_entry(A, B, C, M, N, K, lda, ldb, ldc, b_layout, out_dtype, stream);
+}
 
 extern "C" int gemm_b200_gemm_bf16_cfg(const void* A, const void* B, void* C, int64_t M, int64_t N, int64_t K,
                                        int64_t lda, int64_t ldb, int64_t ldc, int b_layout, int out_dtype,

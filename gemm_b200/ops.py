@@ -14,7 +14,7 @@ from . import _lib
 from ._lib import lib, check
 
 __all__ = [
-    "sgemm_f32", "sgemm_f32_batched", "gemm_bf16", "gemm_bf16_batched", "gemm_bf16_grouped", "check_status", "sgemm_f32_host", "gemm_bf16_host",
+    "sgemm_f32", "sgemm_f32_batched", "gemm_bf16", "gemm_bf16_batched", "gemm_bf16_grouped", "gemm_bf16_at", "check_status", "sgemm_f32_host", "gemm_bf16_host",
     "sgemm_f32_configs", "gemm_bf16_configs", "launch_count",
     "quantize_mxfp8", "gemm_mxfp8", "gemm_mxfp8_configs", "MxFp8Tensor", "gemm_mxfp8_splitk", "gemm_mxfp8_auto_splits", "gemm_mxfp8_quant_out",
 ]
@@ -116,6 +116,31 @@ def gemm_bf16(A: torch.Tensor, B: torch.Tensor, out: torch.Tensor | None = None,
             check(lib.gemm_b200_gemm_bf16_cfg(
                 A.data_ptr(), B.data_ptr(), out.data_ptr(), M, N, K, _row_major_ld(A), _row_major_ld(B), _row_major_ld(out),
                 layout, od, config, _stream(A)))
+    return out
+
+
+def gemm_bf16_at(At: torch.Tensor, B: torch.Tensor, out: torch.Tensor | None = None, *, b_is_nk: bool = False,
+                 out_dtype: torch.dtype = torch.bfloat16) -> torch.Tensor:
+    """BF16 ``C = At.T @ B`` with A given as its transpose ``At`` ``[K, M]`` row-major — the layout in which an
+    activation matrix enters a weight-gradient product — without a transposing copy."""
+    _require(At.is_cuda and B.is_cuda, "At and B must be CUDA tensors")
+    _require(At.dtype == torch.bfloat16 and B.dtype == torch.bfloat16, "expected bfloat16")
+    _require(out_dtype in (torch.bfloat16, torch.float32), "out_dtype must be bfloat16 or float32")
+    K, M = At.shape
+    if b_is_nk:
+        N = B.shape[0]
+        _require(B.shape[1] == K, f"At is {tuple(At.shape)} but Bt is {tuple(B.shape)}")
+    else:
+        N = B.shape[1]
+        _require(B.shape[0] == K, f"At is {tuple(At.shape)} but B is {tuple(B.shape)}")
+    if out is None:
+        out = torch.empty((M, N), device=At.device, dtype=out_dtype)
+    _require(out.is_cuda and out.dtype == out_dtype and tuple(out.shape) == (M, N), "bad out tensor")
+    layout = _lib.B_ROW_MAJOR_NK if b_is_nk else _lib.B_ROW_MAJOR_KN
+    od = _lib.OUT_F32 if out_dtype == torch.float32 else _lib.OUT_BF16
+    with _OnDevice(At.device):
+        check(lib.gemm_b200_gemm_bf16_at(At.data_ptr(), B.data_ptr(), out.data_ptr(), M, N, K, _row_major_ld(At), _row_major_ld(B),
+                                         _row_major_ld(out), layout, od, _stream(At)))
     return out
 
 

@@ -150,6 +150,18 @@ int gemm_b200_gemm_bf16_batched(const void* A, const void* B, void* C, int64_t b
                                 int64_t stride_a, int64_t stride_b, int64_t stride_c,
                                 int b_layout, int out_dtype, void* stream);
 
+/* Transposed-A form: A is given as its transpose At[K, M] row-major (lda >= M, M contiguous),
+ *   C[M,N] = At^T @ B,
+ * the layout in which an activation matrix X[tokens, features] enters the weight-gradient product
+ * X^T dY without a transposing copy.  The reference assumes row-major A[M,K] silently
+ * (naive/naive.cpp:15-17); no counterpart.  Requirements as gemm_b200_gemm_bf16 (lda a multiple
+ * of 8).  Few output tiles with a long K are cut into K ranges on library-owned scratch as in
+ * gemm_b200_gemm_bf16 (same per-(device, stream) ownership).  Results are bit-identical to
+ * gemm_b200_gemm_bf16 on a transposed copy of At whenever both take the same tile shape. */
+int gemm_b200_gemm_bf16_at(const void* At, const void* B, void* C, int64_t M, int64_t N, int64_t K,
+                           int64_t lda, int64_t ldb, int64_t ldc,
+                           int b_layout, int out_dtype, void* stream);
+
 /* Grouped (ragged) form: `groups` problems that share N and K but have their own row count,
  *   C[rows of group g, :] = A[rows of group g, :] @ B_g,   B_g = B + g * stride_b,
  * where the groups' rows follow one another in one tall A [sum m_sizes, K] (lda) and one tall
