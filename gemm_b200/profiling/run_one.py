@@ -35,6 +35,8 @@ def main(argv=None) -> int:
         B = torch.rand(K, N, device="cuda", generator=g) * 2 - 1
         C = torch.empty(M, N, device="cuda")
         fn = lambda: ops.sgemm_f32(A, B, C, config=a.config)
+        if a.cublas:
+            fn = lambda: torch.matmul(A, B, out=C)
     elif a.op == "bf16":
         A = torch.randn(M, K, device="cuda", generator=g).bfloat16()
         B = torch.randn(K, N, device="cuda", generator=g).bfloat16()
