@@ -387,10 +387,13 @@ def per_dtype_table(peaks: dict) -> dict:
         out[f"bf16_{M}x{K}x{N}"] = {
             "tflops": round(tf, 1), "tflops_best": round(flops / t_best / 1e12, 1),
             "frac_of_nominal_2250": round(tf / 2250.0, 4), "frac_of_measured_burst": round(tf / burst, 4)}
+        # the vendor library on the same operands, same protocol (context, not the product path)
+        torch.matmul(A, B, out=C)
+        out[f"bf16_{M}x{K}x{N}"]["cublas"] = round(flops / time_alone(lambda: torch.matmul(A, B, out=C)) / 1e12, 1)
         del A, B, C
     if hasattr(ops, "gemm_mxfp8") and ops.gemm_mxfp8_configs():
         hbm = float(peaks.get("hbm_gbs", 6650.0))
-        for (M, K, N) in ((16384, 8192, 28672), (16, 8192, 28672)):
+        for (M, K, N) in ((8192, 8192, 8192), (16384, 8192, 28672), (16, 8192, 28672)):
             A = torch.randn(M, K, device="cuda", generator=g).bfloat16()
             B = torch.randn(K, N, device="cuda", generator=g).bfloat16()
             Aq = ops.quantize_mxfp8(A)
@@ -405,6 +408,18 @@ def per_dtype_table(peaks: dict) -> dict:
                    "frac_of_nominal_4500": round(tf / 4500.0, 4), "gbps": round(bytes_ / t / 1e9, 1),
                    "frac_of_measured_hbm": round(bytes_ / t / 1e9 / hbm, 4)}
             out[f"mxfp8_{M}x{K}x{N}"] = row
+            try:
+                # the vendor library's block-scaled GEMM on the same packed bytes (context only)
+                a8, b8 = Aq.data.view(torch.float8_e4m3fn), Bq.data.view(torch.float8_e4m3fn).t()
+                sa, sb = Aq.scales.view(torch.float8_e8m0fnu), Bq.scales.view(torch.float8_e8m0fnu)
+                lib_mm = lambda: torch._scaled_mm(a8, b8, scale_a=sa, scale_b=sb, out_dtype=torch.bfloat16)
+                lib_mm()
+                t_l = time_alone(lib_mm)
+                row["cublaslt_scaled_mm"] = round(flops / t_l / 1e12, 1)
+                if M < 1024:
+                    row["cublaslt_scaled_mm_gbps"] = round(bytes_ / t_l / 1e9, 1)
+            except (RuntimeError, NotImplementedError, AttributeError):
+                row["cublaslt_scaled_mm"] = None
             if M < 1024:
                 # The HBM-bound decode shape.  `gbps` above is one call after the usual 252 MB WRITE
                 # flush; that flush leaves the L2 full of dirty lines whose write-back competes with
@@ -439,7 +454,7 @@ def per_dtype_table(peaks: dict) -> dict:
                 row["frac_of_measured_hbm_back_to_back"] = round(bytes_ / t_r / 1e9 / hbm, 4)
                 row["back_to_back"] = "4 copies of B in turn (940 MB > L2), 30 rounds, no flush kernel"
                 del copies
-            else:
+            elif N > 8192:
                 # the same GEMM with the quantising epilogue vs GEMM (bf16 out) + separate quantise pass,
                 # timed alternately: on a power-capped board the clock drifts with what ran just before
                 t_f, t_p, t_q = time_interleaved([lambda: ops.gemm_mxfp8_quant_out(Aq, Bq),
