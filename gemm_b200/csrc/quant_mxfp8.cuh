@@ -84,71 +84,108 @@ quantize_rows_kernel(const __nv_bfloat16* __restrict__ X, int64_t rows, int64_t 
 
 // X [K, rows] row-major (ldx): quantise every column along K, write Xq [rows, K] K-contiguous.
 // A CTA of 256 threads owns 128 k (one 4-block scale chunk) x 64 columns:
-//   1. the bf16 tile is staged with 16-byte loads, 8 threads per 128-byte row segment;
-//   2. thread (column c = t % 64, block kb = t / 64) reads its 32 values down the tile, quantises
-//      them and parks the 32 e4m3 bytes in a [64][128] byte tile, the scale byte in a [64][4] one;
-//   3. the byte tile leaves as whole 128-byte lines of Xq (8 threads x 16 bytes per row) and the
-//      four scale bytes of a row as one 32-bit word of the packed layout.
-// Every global access is a full line; rows of the shared tiles are padded by 16 bytes so that the
-// 16-byte accesses of a quarter warp and the 2-byte column walks fall in distinct banks.
-constexpr int kQcK = 128, kQcCols = 64;
+//   1. the bf16 tile is staged in shared memory as it lies in X ([k][column], 16-byte cp.async, 8
+//      threads per 128-byte row segment; 2-byte loads for unaligned operands);
+//   2. warp w owns columns 8 w .. 8 w + 7 and walks the four K blocks.  One ldmatrix.x4.trans per
+//      block transposes 32 k x 8 columns: the row addresses are chosen so that lane 4 c + j
+//      receives, as four ready-packed bf16 pairs, k = 8 j .. 8 j + 7 of column c.  The block
+//      maximum is two shuffles away (the four lanes of a column); each lane converts its eight
+//      values and stores eight e4m3 bytes, so a column's block leaves as one 32-byte sector;
+//   3. lane 4 c keeps the four scale bytes of its column and stores them as one 32-bit word of
+//      the packed layout.
+// Rows of the shared tile are padded by 16 bytes so that the eight row addresses of an ldmatrix
+// fall in distinct 16-byte bank groups.
+constexpr int kQcK = 128, kQcCols = 64, kQcMaxTiles = 8;
 template <int COLS>
 __global__ void __launch_bounds__(COLS * 4)
 quantize_cols_kernel(const __nv_bfloat16* __restrict__ X, int64_t rows, int64_t K, int64_t ldx,
-                     uint8_t* __restrict__ Xq, uint8_t* __restrict__ SF, int64_t kb_pad, int vec_ok) {
-  constexpr int kThreads = COLS * 4;
-  // the byte tile reuses the bf16 tile's storage once every thread holds its 32 values in registers
-  __shared__ __align__(16) uint16_t tile[kQcK][COLS + 8];
-  uint8_t (*qtile)[kQcK + 16] = reinterpret_cast<uint8_t (*)[kQcK + 16]>(&tile[0][0]);
-  __shared__ __align__(4) uint8_t sft[COLS][4];
-  const int64_t c0 = (int64_t)blockIdx.x * COLS, kc = blockIdx.y, k0 = kc * kQcK;
+                     uint8_t* __restrict__ Xq, uint8_t* __restrict__ SF, int64_t kb_pad, int vec_ok, int tiles_per_cta) {
+  static_assert(COLS * 4 == 32 * (COLS / 8), "one warp per eight columns");
+  // two tiles: the CTA walks tiles_per_cta consecutive K chunks of its columns and fetches chunk i + 1
+  // (cp.async, straight into shared memory) while it quantises chunk i, so loads are in flight
+  // all the time
+  __shared__ __align__(16) uint16_t tile[2][kQcK][COLS + 8];
+  const int64_t c0 = (int64_t)blockIdx.x * COLS;
   const int64_t KB = K / 32, kchunks = kb_pad / 4;
+  const int64_t kc_first = (int64_t)blockIdx.y * tiles_per_cta;
+  const int n_tiles = (int)((kchunks - kc_first < tiles_per_cta) ? (kchunks - kc_first) : tiles_per_cta);
   const int t = threadIdx.x;
   const uint16_t* Xu = reinterpret_cast<const uint16_t*>(X);
-  if (vec_ok) {
+  const int warp = t >> 5, lane = t & 31;
+  const int j = lane & 3, c = warp * 8 + (lane >> 2);       // this lane's k octet and column
+  // row address this lane hands to ldmatrix: matrix m = lane / 8, row slot r = lane % 8  ->  k = 8 (r / 2) + 2 m + r % 2
+  const int lm = lane >> 3, lr = lane & 7;
+  const int k_addr = 8 * (lr >> 1) + 2 * lm + (lr & 1);
+  const uint32_t row_addr0 = (uint32_t)__cvta_generic_to_shared(&tile[0][k_addr][warp * 8]);
+  constexpr uint32_t kTileBytes = kQcK * (COLS + 8) * 2;
+  const bool col_ok = c0 + c < rows;
+
+  auto fetch = [&](int i) {       // chunk i of this CTA into buffer i % 2 (16-byte path)
     constexpr int kPerRow = COLS / 8;          // threads per k row, 8 columns each; 32 k rows per pass
     const int cg = (t % kPerRow) * 8, kr = t / kPerRow;
+    const int64_t k0 = (kc_first + i) * kQcK;
 #pragma unroll
     for (int p = 0; p < 4; ++p) {
       const int k = kr + 32 * p;
-      uint4 v = make_uint4(0, 0, 0, 0);
-      if (k0 + k < K && c0 + cg < rows) v = __ldg(reinterpret_cast<const uint4*>(Xu + (k0 + k) * ldx + c0 + cg));   // rows % 8 == 0
-      *reinterpret_cast<uint4*>(&tile[k][cg]) = v;
+      const bool ok = k0 + k < K && c0 + cg < rows;       // rows % 8 == 0: a chunk of 8 columns is all in or all out
+      const uint16_t* src = ok ? Xu + (k0 + k) * ldx + c0 + cg : Xu;
+      const uint32_t dst = (uint32_t)__cvta_generic_to_shared(&tile[i & 1][k][cg]);
+      asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(dst), "l"(src), "r"(ok ? 16 : 0));
     }
-  } else {
-    const int c = t % COLS, kr = t / COLS;  // one thread per column, 4 k rows per pass
+  };
+
+  if (vec_ok && n_tiles > 0) fetch(0);
+  asm volatile("cp.async.commit_group;\n" ::);
+  for (int i = 0; i < n_tiles; ++i) {
+    const int64_t kc = kc_first + i, k0 = kc * kQcK;
+    if (vec_ok) {
+      if (i + 1 < n_tiles) fetch(i + 1);
+      asm volatile("cp.async.commit_group;\n" ::);
+      asm volatile("cp.async.wait_group 1;\n" ::);
+    } else {
+      const int cc = t % COLS, kr = t / COLS;  // one thread per column, 4 k rows per pass
 #pragma unroll 4
-    for (int p = 0; p < 32; ++p) {
-      const int k = kr + 4 * p;
-      tile[k][c] = (k0 + k < K && c0 + c < rows) ? Xu[(k0 + k) * ldx + c0 + c] : (uint16_t)0;
+      for (int p = 0; p < 32; ++p) {
+        const int k = kr + 4 * p;
+        tile[i & 1][k][cc] = (k0 + k < K && c0 + cc < rows) ? Xu[(k0 + k) * ldx + c0 + cc] : (uint16_t)0;
+      }
     }
-  }
-  __syncthreads();
-  {
-    const int c = t % COLS, kb = t / COLS;
-    uint32_t w[16], q[8];
-#pragma unroll
-    for (int i = 0; i < 16; ++i) w[i] = (uint32_t)tile[32 * kb + 2 * i][c] | ((uint32_t)tile[32 * kb + 2 * i + 1][c] << 16);
     __syncthreads();
-    // columns / K-blocks past the end hold zeros: they quantise to byte 0, the padding value
-    const uint32_t byte = quantise_block(w, q);
-    uint4* dst = reinterpret_cast<uint4*>(&qtile[c][32 * kb]);
-    dst[0] = make_uint4(q[0], q[1], q[2], q[3]);
-    dst[1] = make_uint4(q[4], q[5], q[6], q[7]);
-    sft[c][kb] = (uint8_t)byte;
-  }
-  __syncthreads();
-  {
-    const int j = t & 7, cr = t >> 3;             // 16-byte piece j of the row; half of the rows per pass
+    const uint32_t row_addr = row_addr0 + (uint32_t)(i & 1) * kTileBytes;
+    uint32_t scale_word = 0;
 #pragma unroll
-    for (int p = 0; p < 2; ++p) {
-      const int c = cr + (kThreads / 8) * p;
-      if (c0 + c < rows && kc * 4 + j / 2 < KB)
-        *reinterpret_cast<uint4*>(Xq + (c0 + c) * K + k0 + 16 * j) = *reinterpret_cast<const uint4*>(&qtile[c][16 * j]);
+    for (int kb = 0; kb < 4; ++kb) {
+      uint32_t w[4];
+      asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];"
+                   : "=r"(w[0]), "=r"(w[1]), "=r"(w[2]), "=r"(w[3])
+                   : "r"(row_addr + (uint32_t)(32 * kb * (COLS + 8) * 2)));
+      uint32_t amax_bits = 0;
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const uint32_t lo = (w[e] << 16) & 0x7fffffffu, hi = w[e] & 0x7fff0000u;
+        amax_bits = max(amax_bits, max(lo, hi));
+      }
+      amax_bits = max(amax_bits, __shfl_xor_sync(0xffffffffu, amax_bits, 1));
+      amax_bits = max(amax_bits, __shfl_xor_sync(0xffffffffu, amax_bits, 2));
+      // columns / K blocks past the end hold zeros: they quantise to byte 0, the padding value
+      const int eb = (int)(amax_bits >> 23);
+      const uint32_t byte = (uint32_t)max(eb - 8, 0);
+      const float inv = __uint_as_float((uint32_t)(254 - (int)byte) << 23);   // 2^(127 - byte)
+      uint32_t q[2];
+#pragma unroll
+      for (int e = 0; e < 2; ++e) {
+        const float a = bf16_bits_to_float(w[2 * e] & 0xffffu) * inv, b = bf16_bits_to_float(w[2 * e] >> 16) * inv;
+        const float cc = bf16_bits_to_float(w[2 * e + 1] & 0xffffu) * inv, d = bf16_bits_to_float(w[2 * e + 1] >> 16) * inv;
+        q[e] = pack4_e4m3(a, b, cc, d);
+      }
+      if (col_ok && kc * 4 + kb < KB)
+        *reinterpret_cast<uint2*>(Xq + (c0 + c) * K + k0 + 32 * kb + 8 * j) = make_uint2(q[0], q[1]);
+      scale_word |= byte << (8 * kb);
     }
+    if (j == 0)   // the launch covers rows up to a multiple of 128: padding rows get zero scales
+      *reinterpret_cast<uint32_t*>(SF + scale_offset(kchunks, c0 + c, kc * 4)) = scale_word;
+    __syncthreads();   // every warp is done with this buffer before chunk i + 2 is fetched into it
   }
-  if (t < COLS)   // the launch covers rows up to a multiple of 128: padding rows get zero scales
-    *reinterpret_cast<uint32_t*>(SF + scale_offset(kchunks, c0 + t, kc * 4)) = *reinterpret_cast<const uint32_t*>(&sft[t][0]);
 }
 
 }  // namespace mx
