@@ -709,6 +709,31 @@ def main() -> int:
     e2e = None
     cpu = None
     extra = None
+    mx_leg = None
+    if not args.no_extras and not is_mx and ops.gemm_mxfp8_configs():
+        # The MXFP8 half of the row-sharded configuration, same operands quantised along K, same
+        # protocol (pre-load, barrier, device-timed steps, max over ranks) at this rank count.
+        Aq = ops.quantize_mxfp8(A)
+        Bq = ops.quantize_mxfp8(B, transposed_in=True)
+        sharded.broadcast_mxfp8(Bq, src=0)
+
+        def mx_step():
+            ops.gemm_mxfp8(Aq, Bq, C)
+        mx_step()
+        ops.check_status()
+        err = float((C[probe].float() - want).norm() / want.norm())
+        if not err < 0.06:
+            raise SystemExit(f"mxfp8 probe rows differ from the bf16 product by {err:.3f}")
+        barrier(world)
+        preload(mx_step, min(args.preload_s, 1.0))
+        mx_secs, _ = time_steps(mx_step, args.steps, max(args.warmup, 3), world)
+        ops.check_status()
+        mx_tf = flops / (mx_secs / args.steps) / 1e12
+        mx_leg = {"workload": "mxfp8_rowsharded_%dx%dx%d" % (M, K, N), "value": round(mx_tf, 1), "unit": "TFLOP/s",
+                  "ms_per_step": round(mx_secs / args.steps * 1e3, 4), "steps": args.steps, "n_gpus": world,
+                  "frac_of_2x_measured_bf16_sustained": round(mx_tf / world / (2 * float(peaks.get("bf16_tflops_sustained", 1400.0))), 4),
+                  "operands": "e4m3 data + one ue8m0 scale per 32 k, quantised before the timed region; B's bytes broadcast from rank 0"}
+        del Aq, Bq
     if not args.no_extras and not is_mx:
         # end to end: pinned host operands -> C in pinned host memory, through the host-buffer C-ABI call
         hA = torch.empty(shard.rows, K, dtype=torch.bfloat16, pin_memory=True); hA.copy_(A)
@@ -747,6 +772,8 @@ def main() -> int:
             line["e2e"] = e2e
         if cpu is not None:
             line["cpu_baseline"] = cpu
+        if mx_leg is not None:
+            line["mxfp8_rowsharded"] = mx_leg
         if extra is not None:
             line["per_dtype"] = extra
         print(json.dumps(line), flush=True)
