@@ -490,9 +490,10 @@ using Bf16_1cta_n128    = Bf16Cfg<1, 6, 1, false, 1, 2, 128>;
 // the two multi-round shapes with units handed out at run time
 using Bf16_2cta_tma_m_dyn   = Bf16Cfg<2, 6, 1, true, 1, 2, kBlockN, true>;
 using Bf16_2cta_n512_s3_dyn = Bf16Cfg<2, 3, 1, true, 2, 2, kBlockN, true>;
+// CTA pair with direct stores: the split-K partial sums of problems with at least two row tiles
+using Bf16_2cta_direct = Bf16Cfg<2, 6, 0, false>;
 #ifdef GEMM_B200_TUNING
 // variants the heuristics never pick; built only for tuning sweeps
-using Bf16_2cta_direct = Bf16Cfg<2, 6, 0, false>;
 using Bf16_2cta_tma    = Bf16Cfg<2, 6, 1, false>;
 using Bf16_2cta_n512    = Bf16Cfg<2, 4, 1, true, 2>;
 using Bf16_2cta_n512_d  = Bf16Cfg<2, 4, 0, true, 2>;
@@ -588,9 +589,18 @@ static int launch_bf16_splitk(const Bf16Args& a, int b_layout, int out_dtype, in
   part.C = scratch;
   part.ldc = a.N;
   part.k_splits = k_splits;
-  if (int rc = (b_layout == GEMM_B200_B_ROW_MAJOR_KN) ? launch_bf16<Bf16_1cta_direct, true, true>(part)
-                                                      : launch_bf16<Bf16_1cta_direct, false, true>(part))
-    return rc;
+  // From two row tiles up the partial sums come from CTA pairs (256 x 256 per pair): each CTA then
+  // fetches 128 + 128 rows of operands per K block instead of 128 + 256, and these launches are
+  // bound by what one SM can take in from the L2.  Call time in us, single-CTA / pairs:
+  // 1024 x 32768 x 1024 80.9 / 72.7, 1024 x 16384 x 1024 45.8 / 43.7, 512 x 32768 x 512 39.9 / 37.9,
+  // 256 x 65536 x 256 43.8 / 41.7.  GEMM_B200_BF16_SPLITK_PAIR=0 keeps single CTAs.
+  static const bool pair = env_int("GEMM_B200_BF16_SPLITK_PAIR", 1) != 0;
+  const bool kn = b_layout == GEMM_B200_B_ROW_MAJOR_KN;
+  if (pair && a.M > kBlockM) {
+    if (int rc = kn ? launch_bf16<Bf16_2cta_direct, true, true>(part) : launch_bf16<Bf16_2cta_direct, false, true>(part)) return rc;
+  } else {
+    if (int rc = kn ? launch_bf16<Bf16_1cta_direct, true, true>(part) : launch_bf16<Bf16_1cta_direct, false, true>(part)) return rc;
+  }
   const int num_kb = (int)ceil_div64(a.K, kBlockK);
   const int kb_per = (int)ceil_div64(num_kb, k_splits);
   const int splits = (int)ceil_div64(num_kb, kb_per);

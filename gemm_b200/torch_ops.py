@@ -5,6 +5,8 @@ call them as opaque ops:
     C = torch.ops.gemm_b200.sgemm_f32(A, B)
     C = torch.ops.gemm_b200.gemm_bf16(A, B, b_is_nk=False, out_f32=False)
     C = torch.ops.gemm_b200.gemm_bf16_batched(A3, B3)         # [batch, M, K] x [batch, K, N] (or a shared 2-D B)
+    C = torch.ops.gemm_b200.gemm_bf16_at(At, B)               # At is A stored transposed, [K, M]
+    C = torch.ops.gemm_b200.gemm_bf16_grouped(A, B3, [m0, m1, ...])   # ragged groups sharing N and K
     aq, asf = torch.ops.gemm_b200.quantize_mxfp8(A)           # e4m3 bytes [M, K] + packed UE8M0 scales
     bq, bsf = torch.ops.gemm_b200.quantize_mxfp8(B, True)     # B given as [K, N]
     C = torch.ops.gemm_b200.gemm_mxfp8(aq, asf, bq, bsf)
@@ -51,6 +53,31 @@ def _(A, B, b_is_nk=False, out_f32=False):
     torch._check(A.dim() == 3 and B.dim() in (2, 3))
     n = B.shape[-2] if b_is_nk else B.shape[-1]
     return A.new_empty((A.shape[0], A.shape[1], n), dtype=torch.float32 if out_f32 else torch.bfloat16)
+
+
+@torch.library.custom_op("gemm_b200::gemm_bf16_at", mutates_args=())
+def gemm_bf16_at(At: torch.Tensor, B: torch.Tensor, b_is_nk: bool = False, out_f32: bool = False) -> torch.Tensor:
+    return ops.gemm_bf16_at(At, B, b_is_nk=b_is_nk, out_dtype=torch.float32 if out_f32 else torch.bfloat16)
+
+
+@gemm_bf16_at.register_fake
+def _(At, B, b_is_nk=False, out_f32=False):
+    torch._check(At.dim() == 2 and B.dim() == 2)
+    n = B.shape[0] if b_is_nk else B.shape[1]
+    return At.new_empty((At.shape[1], n), dtype=torch.float32 if out_f32 else torch.bfloat16)
+
+
+@torch.library.custom_op("gemm_b200::gemm_bf16_grouped", mutates_args=())
+def gemm_bf16_grouped(A: torch.Tensor, B: torch.Tensor, m_sizes: list[int], b_is_nk: bool = False,
+                      out_f32: bool = False) -> torch.Tensor:
+    return ops.gemm_bf16_grouped(A, B, m_sizes, b_is_nk=b_is_nk, out_dtype=torch.float32 if out_f32 else torch.bfloat16)
+
+
+@gemm_bf16_grouped.register_fake
+def _(A, B, m_sizes, b_is_nk=False, out_f32=False):
+    torch._check(A.dim() == 2 and B.dim() == 3)
+    n = B.shape[1] if b_is_nk else B.shape[2]
+    return A.new_empty((A.shape[0], n), dtype=torch.float32 if out_f32 else torch.bfloat16)
 
 
 # MXFP8: a quantised operand travels as two plain tensors, the e4m3 bytes [rows, K] and the packed

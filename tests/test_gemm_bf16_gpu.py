@@ -109,7 +109,7 @@ def test_alignment_errors(ops):
 
 
 @pytest.mark.parametrize("M,K,N,splits", [(256, 8192, 256, 8), (128, 4096, 264, 3), (16, 2048, 512, 5), (300, 1000, 520, 4),
-                                          (1, 512, 8, 2), (256, 65536, 256, 64)])
+                                          (1, 512, 8, 2), (256, 65536, 256, 64), (1024, 4096, 1032, 4), (520, 2048, 256, 3)])
 @pytest.mark.parametrize("b_is_nk", [False, True])
 def test_splitk_matches_the_oracle(ops, oracle, M, K, N, splits, b_is_nk):
     """K cut into ranges whose FP32 partial sums are added in split order: within the FP32 bound of

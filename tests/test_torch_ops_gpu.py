@@ -19,6 +19,13 @@ def test_custom_ops_match_direct_calls(ops, oracle):
     A3 = torch.stack([Ab, Ab * 0.5, -Ab]).cuda()
     c3 = torch.ops.gemm_b200.gemm_bf16_batched(A3, Bb.cuda())
     assert torch.equal(c3, ops.gemm_bf16_batched(A3, Bb.cuda())) and c3.shape == (3, 256, 264)
+    At = Ab.t().contiguous().cuda()
+    c4 = torch.ops.gemm_b200.gemm_bf16_at(At, Bb.cuda())
+    assert torch.equal(c4, ops.gemm_bf16_at(At, Bb.cuda())) and c4.shape == (256, 264)
+    torch.testing.assert_close(c4.float().cpu(), oracle.bf16_matmul_oracle(Ab, Bb), rtol=2e-2, atol=2e-2)
+    B3 = torch.stack([Bb, -Bb]).cuda()
+    c5 = torch.ops.gemm_b200.gemm_bf16_grouped(Ab.cuda(), B3, [100, 156])
+    assert torch.equal(c5, ops.gemm_bf16_grouped(Ab.cuda(), B3, [100, 156])) and c5.shape == (256, 264)
 
 
 def test_mxfp8_custom_ops_match_direct_calls(ops, oracle):
@@ -46,6 +53,10 @@ def test_fake_tensor_shapes():
         assert out.shape == (64, 48) and out.dtype == torch.float32
         A3 = torch.empty(5, 64, 32, device="cuda", dtype=torch.bfloat16)
         assert torch.ops.gemm_b200.gemm_bf16_batched(A3, Bt, True, False).shape == (5, 64, 48)
+        At = torch.empty(32, 64, device="cuda", dtype=torch.bfloat16)
+        assert torch.ops.gemm_b200.gemm_bf16_at(At, Bt, True, False).shape == (64, 48)
+        B3 = torch.empty(2, 32, 48, device="cuda", dtype=torch.bfloat16)
+        assert torch.ops.gemm_b200.gemm_bf16_grouped(Ab, B3, [24, 40]).shape == (64, 48)
         aq, asf = torch.ops.gemm_b200.quantize_mxfp8(Ab)
         bq, bsf = torch.ops.gemm_b200.quantize_mxfp8(Bt)
         assert aq.shape == (64, 32) and asf.shape == (512,) and bq.shape == (48, 32)
