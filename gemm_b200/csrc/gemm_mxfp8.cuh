@@ -473,12 +473,25 @@ splitk_reduce_kernel(const float* __restrict__ W, int64_t split_stride, int64_t 
   const long long w_bytes = ((long long)(k_splits - 1) * split_stride + (long long)(M - 1) * ldw + N) * 4;
   const long long c_elems = (long long)(M - 1) * ldc + N;
   (void)w_bytes; (void)c_elems;
-  if (!GEMM_B200_IN_BOUNDS(src, W, w_bytes, 16, 30)) return;
-  float4 acc = *reinterpret_cast<const float4*>(src);
-  for (int s = 1; s < k_splits; ++s) {
-    if (!GEMM_B200_IN_BOUNDS(src + (int64_t)s * split_stride, W, w_bytes, 16, 30)) return;
-    const float4 v = *reinterpret_cast<const float4*>(src + (int64_t)s * split_stride);
-    acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+  // four slices are fetched before the first of them is added (the loads are independent, the
+  // additions keep their ascending order)
+  float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+  for (int s0 = 0; s0 < k_splits; s0 += 4) {
+    float4 v[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      v[j] = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (s0 + j < k_splits && GEMM_B200_IN_BOUNDS(src + (int64_t)(s0 + j) * split_stride, W, w_bytes, 16, 30))
+        v[j] = *reinterpret_cast<const float4*>(src + (int64_t)(s0 + j) * split_stride);
+    }
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      if (s0 + j == 0) {
+        acc = v[0];
+      } else if (s0 + j < k_splits) {
+        acc.x += v[j].x; acc.y += v[j].y; acc.z += v[j].z; acc.w += v[j].w;
+      }
+    }
   }
   if (!GEMM_B200_IN_BOUNDS(reinterpret_cast<char*>(Cptr) + (r * ldc + c) * (OUT_F32 ? 4 : 2), Cptr, c_elems * (OUT_F32 ? 4 : 2),
                            OUT_F32 ? 16 : 8, 31))

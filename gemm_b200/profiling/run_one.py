@@ -24,6 +24,7 @@ def main(argv=None) -> int:
     ap.add_argument("--config", type=int, default=-1)
     ap.add_argument("--reps", type=int, default=4)
     ap.add_argument("--out-f32", action="store_true", help="FP32 output for the tensor-core operators")
+    ap.add_argument("--k-splits", type=int, default=0, help="bf16: K ranges of the two-launch split (0: library decides, 1: never)")
     ap.add_argument("--cluster-splits", type=int, default=0, help="bf16: split K over clusters of 2, 4 or 8 CTAs")
     ap.add_argument("--cublas", action="store_true", help="bf16 / f32: run torch.matmul instead (for comparison)")
     a = ap.parse_args(argv)
@@ -41,7 +42,7 @@ def main(argv=None) -> int:
         A = torch.randn(M, K, device="cuda", generator=g).bfloat16()
         B = torch.randn(K, N, device="cuda", generator=g).bfloat16()
         C = torch.empty(M, N, device="cuda", dtype=od)
-        fn = lambda: ops.gemm_bf16(A, B, C, out_dtype=od, config=a.config, cluster_splits=a.cluster_splits)
+        fn = lambda: ops.gemm_bf16(A, B, C, out_dtype=od, config=a.config, k_splits=a.k_splits, cluster_splits=a.cluster_splits)
         if a.cublas:
             fn = lambda: torch.matmul(A, B, out=C)
     else:

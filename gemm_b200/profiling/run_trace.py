@@ -29,6 +29,7 @@ def main(argv=None) -> int:
     ap.add_argument("--k", type=int, default=4096)
     ap.add_argument("--n", type=int, default=4096)
     ap.add_argument("--config", type=int, default=-1)
+    ap.add_argument("--k-splits", type=int, default=0, help="bf16: K ranges of the two-launch split (0: library decides, 1: never)")
     ap.add_argument("--cluster-splits", type=int, default=0)
     a = ap.parse_args(argv)
     lib = _lib.lib
@@ -42,7 +43,7 @@ def main(argv=None) -> int:
     B = torch.randn(a.k, a.n, device="cuda", generator=g).bfloat16()
     C = torch.empty(a.m, a.n, device="cuda", dtype=torch.bfloat16)
     if a.op == "bf16":
-        fn = lambda: ops.gemm_bf16(A, B, C, config=a.config, cluster_splits=a.cluster_splits)
+        fn = lambda: ops.gemm_bf16(A, B, C, config=a.config, k_splits=a.k_splits, cluster_splits=a.cluster_splits)
     else:
         Aq, Bq = ops.quantize_mxfp8(A), ops.quantize_mxfp8(B, transposed_in=True)
         fn = lambda: ops.gemm_mxfp8(Aq, Bq, C, config=a.config, cluster_splits=a.cluster_splits)
