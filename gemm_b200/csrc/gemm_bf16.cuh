@@ -525,7 +525,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           __syncwarp();
           const int x = n0 + c * 64;
           if (lane == 0) {
-            if (m0 < shape.M && x < shape.N) tma_store_3d(&tmC, x, m0, shape.k_splits > 1 ? split : bi, buf)   // split-K: slice `split` of the scratch;
+            if (m0 < shape.M && x < shape.N) tma_store_3d(&tmC, x, m0, shape.k_splits > 1 ? split : bi, buf);   // split-K: slice `split` of the scratch
             tma_store_commit();
           }
         }
@@ -573,7 +573,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           __syncwarp();
           const int x = n0 + c * SLAB_COLS;
           if (lane == 0) {
-            if (m0 < shape.M && x < shape.N) tma_store_3d(&tmC, x, m0, shape.k_splits > 1 ? split : bi, buf)   // split-K: slice `split` of the scratch;
+            if (m0 < shape.M && x < shape.N) tma_store_3d(&tmC, x, m0, shape.k_splits > 1 ? split : bi, buf);   // split-K: slice `split` of the scratch
             tma_store_commit();
           }
         }

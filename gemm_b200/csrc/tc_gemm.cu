@@ -584,26 +584,33 @@ static int pick_bf16_config(int64_t M, int64_t N, int64_t K, int sms, int64_t ba
 // Split-K BF16 GEMM: FP32 partial sums of every (tile, K range) unit go to `scratch`
 // ([k_splits][M][N] floats) through TMA stores, then one pass sums the slices in
 // ascending split order and writes C.
-static int launch_bf16_splitk(const Bf16Args& a, int b_layout, int out_dtype, int k_splits, float* scratch) {
+static bool bf16_splitk_pairs(int64_t M) {
+  // From two row tiles up the partial sums come from CTA pairs (256 x 256 per pair): each CTA then
+  // fetches 128 + 128 rows of operands per K block instead of 128 + 256, and these launches are
+  // bound by what one SM can take in from the L2.  GEMM_B200_BF16_SPLITK_PAIR=0 keeps single CTAs.
+  static const bool pair = env_int("GEMM_B200_BF16_SPLITK_PAIR", 1) != 0;
+  return pair && M > kBlockM;
+}
+
+static int launch_bf16_splitk(const Bf16Args& a, int b_layout, int out_dtype, int k_splits, float* scratch, bool a_mn = false) {
   Bf16Args part = a;
   part.C = scratch;
   part.ldc = a.N;
   part.k_splits = k_splits;
-  // From two row tiles up the partial sums come from CTA pairs (256 x 256 per pair): each CTA then
-  // fetches 128 + 128 rows of operands per K block instead of 128 + 256, and these launches are
-  // bound by what one SM can take in from the L2.  Call time in us, single-CTA / pairs:
-  // 1024 x 32768 x 1024 80.9 / 72.7, 1024 x 16384 x 1024 45.8 / 43.7, 512 x 32768 x 512 39.9 / 37.9,
-  // 256 x 65536 x 256 43.8 / 41.7.  GEMM_B200_BF16_SPLITK_PAIR=0 keeps single CTAs.
-  static const bool pair = env_int("GEMM_B200_BF16_SPLITK_PAIR", 1) != 0;
+  // The partial sums leave through TMA stores (32 x 32 boxes, whole 128-byte rows).  All CTAs finish
+  // together, so the stores arrive as one burst of k_splits x M x N x 4 bytes; per-thread 16-byte
+  // stores to 32 different rows per instruction took 6 us for 16.8 MB (1024 x 8192 x 1024, four K
+  // ranges), the TMA stores about 2.
   const bool kn = b_layout == GEMM_B200_B_ROW_MAJOR_KN;
-  // The partial sums leave through TMA stores.  All CTAs finish together, so their stores arrive as
-  // one burst of k_splits x M x N x 4 bytes: 16.8 MB in ~6 us of a 20 us launch at 1024 x 8192 x 1024
-  // with four K ranges, the same with per-thread 16-byte stores.
-  if (pair && a.M > kBlockM) {
-    if (int rc = kn ? launch_bf16<Bf16_2cta_tma_m, true, true>(part) : launch_bf16<Bf16_2cta_tma_m, false, true>(part)) return rc;
+  int rc;
+  if (bf16_splitk_pairs(a.M)) {
+    rc = a_mn ? (kn ? launch_bf16<Bf16_2cta_tma_m, true, true, true>(part) : launch_bf16<Bf16_2cta_tma_m, false, true, true>(part))
+              : (kn ? launch_bf16<Bf16_2cta_tma_m, true, true>(part) : launch_bf16<Bf16_2cta_tma_m, false, true>(part));
   } else {
-    if (int rc = kn ? launch_bf16<Bf16_1cta_tma, true, true>(part) : launch_bf16<Bf16_1cta_tma, false, true>(part)) return rc;
+    rc = a_mn ? (kn ? launch_bf16<Bf16_1cta_tma, true, true, true>(part) : launch_bf16<Bf16_1cta_tma, false, true, true>(part))
+              : (kn ? launch_bf16<Bf16_1cta_tma, true, true>(part) : launch_bf16<Bf16_1cta_tma, false, true>(part));
   }
+  if (rc) return rc;
   const int num_kb = (int)ceil_div64(a.K, kBlockK);
   const int kb_per = (int)ceil_div64(num_kb, k_splits);
   const int splits = (int)ceil_div64(num_kb, kb_per);
@@ -677,11 +684,39 @@ static int bf16_cluster_splits(int64_t M, int64_t N, int64_t K) {
   return s;
 }
 
+// K ranges for a BF16 problem whose tiles alone leave most of the GPU idle; 1 = do not split.
+// Estimated call time in us, fitted to measurements on a B200:
+//   unsplit   rounds x K blocks x t_kb                      (256-wide tiles; t_kb = 0.195 for 256 x 128 pair tiles)
+//   s ranges  rounds(s) x K blocks per range x t_kb  +  s x (M N 8 bytes / 7.8 TB/s)  +  6
+// with t_kb = 0.30 us per 64-wide K block for a CTA pair on a 256 x 256 tile and 0.39 for a single CTA
+// on 128 x 256 (both bound by the ~64 bytes per clock one SM takes in from the L2), the second term
+// the FP32 slice every range writes and the reduction reads, the third the reduction launch.
+// 1024 x 8192 x 1024: unsplit 33.8 us measured, 4 ranges 27.6 (the choice), 8 ranges 31.7;
+// 1024 x 16384 x 1024: 85 / 39.8 / 43.9; 512 x 32768 x 512: 16 ranges 33.8 (the choice), 8 ranges 37.9.
 static int bf16_auto_splits(int64_t M, int64_t N, int64_t K, int sms) {
-  // counted in K units of 256: no split below K = 2048, at least 1024 of K per split (1024^3 with
-  // 32 tiles: 15.4 us unsplit, 19.4 us cut in two; 16 x 8192 x 8192: 50 us unsplit, 30 us cut in four)
-  const int s = auto_splits_units(ceil_div64(M, kBlockM) * ceil_div64(N, kBlockN), ceil_div64(K, 4 * kBlockK), sms);
-  return (N % 4 == 0) ? s : 1;
+  if (N % 4 != 0) return 1;
+  const bool pair = bf16_splitk_pairs(M);
+  const int64_t tiles = ceil_div64(M, pair ? 2 * kBlockM : kBlockM) * ceil_div64(N, kBlockN);
+  const int64_t slots = pair ? (sms / 2 > 0 ? sms / 2 : 1) : sms;
+  const int64_t num_kb = ceil_div64(K, kBlockK);
+  if (3 * tiles >= 2 * slots || num_kb < 32) return 1;          // the tiles fill two thirds of the GPU, or K < 2048
+  const double t_kb = pair ? 0.30 : 0.39;
+  const double slice_us = (double)M * (double)N * 8.0 / 7.8e6;
+  double best_cost = (double)ceil_div64(tiles, slots) * (double)num_kb * t_kb;
+  if (pair) {
+    const int64_t units128 = ceil_div64(M, 2 * kBlockM) * ceil_div64(N, 128);
+    const double c128 = (double)ceil_div64(units128, slots) * (double)num_kb * 0.195;
+    if (c128 < best_cost) best_cost = c128;
+  }
+  int best = 1;
+  for (int s = 2; s <= 32; ++s) {
+    const int64_t kb_per = ceil_div64(num_kb, s);
+    if (kb_per < 8) break;                                       // at least 512 of K per range
+    if (ceil_div64(num_kb, kb_per) != s) continue;               // no empty range
+    const double cost = (double)ceil_div64(tiles * s, slots) * (double)kb_per * t_kb + s * slice_us + 6.0;
+    if (cost < best_cost) { best_cost = cost; best = s; }
+  }
+  return best;
 }
 
 }  // namespace tc
@@ -756,6 +791,20 @@ static int bf16_entry(const void* A, const void* B, void* C, int64_t batch, int6
       return launch_bf16_cluster_splitk_dispatch(args, b_layout, out_dtype, cs);
     }
   }
+  if (config < 0 && k_splits == 0 && batch == 1 && static_cast<int>(env_int("GEMM_B200_BF16_CONFIG", -1)) < 0) {
+    // few output tiles and a long K: cut K so the whole GPU works on the problem
+    const int splits = bf16_auto_splits(M, N, K, di.sms);
+    if (splits > 1) {
+      float* ws = nullptr;
+      if (int rc = cached_scratch(di.dev, (size_t)splits * M * N * sizeof(float), &ws, st)) return rc;
+      if (ws) {
+        if (log_enabled())
+          fprintf(stderr, "[gemm_b200] gemm_bf16 %lldx%lldx%lld -> %s, %d K splits\n", (long long)M, (long long)K,
+                  (long long)N, kBf16Configs[bf16_splitk_pairs(M) ? kBf16Cfg256 : kBf16Cfg1cta].name, splits);
+        return launch_bf16_splitk(args, b_layout, out_dtype, splits, ws);
+      }
+    }
+  }
   if (config < 0 && batch == 1 && static_cast<int>(env_int("GEMM_B200_BF16_CONFIG", -1)) < 0) {
     // Problems whose 256-column tiles leave most SMs idle and whose K is not long enough for K
     // splits to pay: 128-column tiles give twice the units in one launch (256 x 8192 x 8192:
@@ -768,20 +817,6 @@ static int bf16_entry(const void* A, const void* B, void* C, int64_t batch, int6
       config = kBf16Cfg2ctaN128;
     else if (M > 32 && M <= kBlockM && tiles128 >= 24 && tiles128 <= di.sms && K <= 4096)
       config = kBf16Cfg1ctaN128;
-  }
-  if (config < 0 && k_splits == 0 && batch == 1) {
-    // few output tiles and a long K: cut K so the whole GPU works on the problem
-    const int splits = bf16_auto_splits(M, N, K, di.sms);
-    if (splits > 1) {
-      float* ws = nullptr;
-      if (int rc = cached_scratch(di.dev, (size_t)splits * M * N * sizeof(float), &ws, st)) return rc;
-      if (ws) {
-        if (log_enabled())
-          fprintf(stderr, "[gemm_b200] gemm_bf16 %lldx%lldx%lld -> %s, %d K splits\n", (long long)M, (long long)K,
-                  (long long)N, kBf16Configs[kBf16Cfg1cta].name, splits);
-        return launch_bf16_splitk(args, b_layout, out_dtype, splits, ws);
-      }
-    }
   }
   if (config < 0) {
     static const int forced = env_int("GEMM_B200_BF16_CONFIG", -1);
@@ -839,19 +874,9 @@ static int bf16_at_entry(const void* A, const void* B, void* C, int64_t M, int64
       if (int rc = cached_scratch(di.dev, (size_t)splits * M * N * sizeof(float), &ws, st)) return rc;
     }
     if (ws) {
-      Bf16Args part = args;
-      part.C = ws;
-      part.ldc = N;
-      part.k_splits = splits;
       if (log_enabled())
-        fprintf(stderr, "[gemm_b200] gemm_bf16_at %lldx%lldx%lld -> %s, %d K splits\n", (long long)M, (long long)K, (long long)N,
-                kBf16Configs[kBf16Cfg1cta].name, splits);
-      if (int rc = (b_layout == GEMM_B200_B_ROW_MAJOR_KN) ? launch_bf16<Bf16_1cta_tma, true, true, true>(part)
-                                                          : launch_bf16<Bf16_1cta_tma, false, true, true>(part))
-        return rc;
-      const int num_kb = (int)ceil_div64(K, kBlockK);
-      const int used = (int)ceil_div64(num_kb, ceil_div64(num_kb, splits));
-      return launch_splitk_reduce(ws, M, N, used, C, ldc, out_dtype, st);
+        fprintf(stderr, "[gemm_b200] gemm_bf16_at %lldx%lldx%lld -> %d K splits\n", (long long)M, (long long)K, (long long)N, splits);
+      return launch_bf16_splitk(args, b_layout, out_dtype, splits, ws, /*a_mn=*/true);
     }
   }
   const int config = pick_bf16_config(M, N, K, di.sms);
