@@ -600,7 +600,7 @@ static int launch_bf16_splitk(const Bf16Args& a, int b_layout, int out_dtype, in
   // The partial sums leave through TMA stores (32 x 32 boxes, whole 128-byte rows).  All CTAs finish
   // together, so the stores arrive as one burst of k_splits x M x N x 4 bytes; per-thread 16-byte
   // stores to 32 different rows per instruction took 6 us for 16.8 MB (1024 x 8192 x 1024, four K
-  // ranges), the TMA stores about 2.
+  // ranges), the TMA stores 3.2.
   const bool kn = b_layout == GEMM_B200_B_ROW_MAJOR_KN;
   int rc;
   if (bf16_splitk_pairs(a.M)) {
