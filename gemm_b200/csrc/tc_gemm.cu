@@ -234,6 +234,30 @@ static int auto_splits_units(int64_t tiles, int64_t num_kb, int sms) {
   return best;
 }
 
+// K ranges for an MXFP8 problem of more than one row tile, by the estimate bf16_auto_splits uses (the
+// operand bytes per K block are the same: 128 one-byte elements instead of 64 two-byte ones); the
+// partial sums come from single-CTA 128 x 256 tiles.  1 = do not split.
+static int mxfp8_model_splits(int64_t M, int64_t N, int64_t K, int sms) {
+  const int64_t tiles = ceil_div64(M, kBlockM) * ceil_div64(N, kBlockN), slots = sms;
+  const int64_t num_kb = ceil_div64(K, kMxBlockK);
+  if (3 * tiles >= 2 * slots || num_kb < 32) return 1;
+  const int64_t pair_slots = sms / 2 > 0 ? sms / 2 : 1;
+  const int64_t units256 = ceil_div64(M, 2 * kBlockM) * ceil_div64(N, kBlockN), units128 = ceil_div64(M, 2 * kBlockM) * ceil_div64(N, 128);
+  double best_cost = (double)ceil_div64(units256, pair_slots) * (double)num_kb * 0.30;
+  const double c128 = (double)ceil_div64(units128, pair_slots) * (double)num_kb * 0.195;
+  if (c128 < best_cost) best_cost = c128;
+  const double slice_us = (double)M * (double)N * 8.0 / 7.8e6;
+  int best = 1;
+  for (int s = 2; s <= 32; ++s) {
+    const int64_t kb_per = ceil_div64(num_kb, s);
+    if (kb_per < 8) break;
+    if (ceil_div64(num_kb, kb_per) != s) continue;
+    const double cost = (double)ceil_div64(tiles * s, slots) * (double)kb_per * 0.39 + s * slice_us + 6.0;
+    if (cost < best_cost) { best_cost = cost; best = s; }
+  }
+  return best;
+}
+
 static int auto_splits(int64_t M, int64_t N, int64_t K, int sms) {
   // counted in K units of 256: no split below K = 2048, at least 1024 of K per split (1024^3 with
   // 32 tiles: 13.2 us unsplit, 19.4 us cut in two)
@@ -1355,8 +1379,11 @@ extern "C" int gemm_b200_gemm_mxfp8_cfg(const void* Aq, const void* SFA, const v
       if (dyn_ok && config == tc::kDefaultMxConfig && 2 * units256 > (int64_t)di.sms) config = tc::kDynMxConfig;
       // a handful of tiles and a very long K (e.g. 256 x 65536 x 256): only K splits put the GPU to work
       const int64_t tiles_1cta = ceil_div64(M, tc::kBlockM) * ceil_div64(N, tc::kBlockN);
-      if (8 * tiles_1cta <= (int64_t)di.sms && K >= 16384 && N % 4 == 0) {
-        const int splits = tc::auto_splits(M, N, K, di.sms);
+      // ... and so does a long K over a larger output when the estimate of tc::mxfp8_model_splits says so
+      // (1024 x 32768 x 1024: 63.5 us on 256 x 128 pair tiles, 49.9 with four K ranges)
+      const int model_splits = (K >= 16384 && N % 4 == 0) ? tc::mxfp8_model_splits(M, N, K, di.sms) : 1;
+      if ((8 * tiles_1cta <= (int64_t)di.sms && K >= 16384 && N % 4 == 0) || model_splits > 1) {
+        const int splits = model_splits > 1 ? model_splits : tc::auto_splits(M, N, K, di.sms);
         if (splits > 1) {
           if (int rc = tc::cached_scratch(di.dev, (size_t)splits * M * N * sizeof(float), &args.scratch, st)) return rc;
           if (args.scratch) {
