@@ -594,14 +594,20 @@ static int pick_bf16_config(int64_t M, int64_t N, int64_t K, int sms, int64_t ba
   };
   // the 512-wide tile's epilogue is not hidden under a main loop: it pays off from K ~ 4096 up
   // (8192^2 x K, TFLOP/s 256-wide / 512-wide: K=2048 1607 / 1570, 4096 1627 / 1662, 8192 1591 / 1660)
-  const double gain = K >= 3072 ? 1.04 : 0.97;
+  // (interleaved with the 256-wide tile on other shapes: 4096^3 1414 / 1444 for 512- / 256-wide,
+  // 16384 x 4096 x 4096 1704 / 1737, 6144^3 1672 / 1671, 8192 x 8192 x 10240 1592 / 1527)
+  const double gain = K >= 6144 ? 1.04 : 0.97;
   const bool wide = gain * eff(2 * kBlockN) >= eff(kBlockN);
   // More than one round of units: hand them out at run time, so that clusters which fall behind
   // do not end up alone on tiles whose operands the others streamed through the L2 long ago.
   // GEMM_B200_BF16_DYNAMIC=0 keeps the static schedule (A/B comparisons).
   static const bool dyn_ok = env_int("GEMM_B200_BF16_DYNAMIC", 1) != 0;
   const int64_t units = batch * ceil_div64(M, 2 * kBlockM) * ceil_div64(N, wide ? 2 * kBlockN : kBlockN);
-  if (dyn_ok && units > clusters) return wide ? kBf16Cfg512Dyn : kBf16Cfg256Dyn;
+  // The hand-out costs a fixed time per unit and pays through L2 locality over many long units: with
+  // short tiles the static schedule is faster (TFLOP/s static / run-time, timed alternately:
+  // 8192 x 1024 x 8192 1508 / 1357, 16384 x 1024 x 16384 1593 / 1405, 8192 x 2048 x 8192 1667 / 1607,
+  // 16384 x 4096 x 4096 1737 / 1704; 6144^3 1671 / 1683, 8192 x 8192 x 10240 1527 / 1538).
+  if (dyn_ok && units > clusters && K >= 6144) return wide ? kBf16Cfg512Dyn : kBf16Cfg256Dyn;
   return wide ? kBf16Cfg512 : kBf16Cfg256;
 }
 
@@ -1376,7 +1382,8 @@ extern "C" int gemm_b200_gemm_mxfp8_cfg(const void* Aq, const void* SFA, const v
       config = (4 * units256 <= (int64_t)di.sms) ? tc::kN128MxConfig : tc::kDefaultMxConfig;
       // several rounds of units: hand them out at run time (GEMM_B200_MXFP8_DYNAMIC=0: static schedule)
       static const bool dyn_ok = env_int("GEMM_B200_MXFP8_DYNAMIC", 1) != 0;
-      if (dyn_ok && config == tc::kDefaultMxConfig && 2 * units256 > (int64_t)di.sms) config = tc::kDynMxConfig;
+      // (and from K = 8192 up: with shorter tiles the static schedule is ~3 % faster, as in the BF16 kernel)
+      if (dyn_ok && config == tc::kDefaultMxConfig && 2 * units256 > (int64_t)di.sms && K >= 8192) config = tc::kDynMxConfig;
       // a handful of tiles and a very long K (e.g. 256 x 65536 x 256): only K splits put the GPU to work
       const int64_t tiles_1cta = ceil_div64(M, tc::kBlockM) * ceil_div64(N, tc::kBlockN);
       // ... and so does a long K over a larger output when the estimate of tc::mxfp8_model_splits says so
