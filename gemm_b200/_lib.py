@@ -43,6 +43,7 @@ SIGNATURES = {
     "gemm_b200_gemm_mxfp8_cfg": (i32, [vp, vp, vp, vp, vp, i64, i64, i64, i64, i32, i32, vp]),
     "gemm_b200_gemm_mxfp8_quant_out": (i32, [vp, vp, vp, vp, vp, vp, i64, i64, i64, vp]),
     "gemm_b200_gemm_mxfp8_splitk": (i32, [vp, vp, vp, vp, vp, i64, i64, i64, i64, i32, i32, vp, sz, vp]),
+    "gemm_b200_gemm_mxfp8_grouped": (i32, [vp, vp, vp, vp, vp, i64, C.POINTER(C.c_int64), i64, i64, i64, i32, vp]),
     "gemm_b200_gemm_mxfp8_cluster_splitk": (i32, [vp, vp, vp, vp, vp, i64, i64, i64, i64, i32, i32, vp]),
     "gemm_b200_gemm_mxfp8_splitk_scratch_bytes": (sz, [i64, i64, i32]),
     "gemm_b200_gemm_mxfp8_splitk_static": (i32, [vp, vp, vp, vp, vp, i64, i64, i64, i64, i32, i32, vp]),

@@ -70,6 +70,16 @@ struct MxCfg {
   static_assert(SMEM_BYTES <= 232448, "shared memory budget");
 };
 
+// Grouped problems: group g multiplies the 128-row blocks [first_block[g], first_block[g + 1]) of one
+// tall A (and its packed scales) by its own B_g into the same rows of one tall C.  The B matrices
+// and their scale buffers follow one another, so B_g starts N rows (and ceil(N / 128) scale blocks)
+// after B_{g-1}; only the producer warp needs to know the group.  Every group is a whole number of
+// row tiles (256 rows for CTA pairs), so no tile spans two groups.  count == 0: not grouped.
+struct MxGroups {
+  int count;
+  int first_block[kMaxGroups + 1];
+};
+
 // OUT: 0 = bf16, 1 = f32, 2 = MXFP8 (C quantised along its columns: e4m3 data to Cptr, one UE8M0
 // scale per 32 columns to SFC in the packed layout, exactly what quantising the bf16 result gives)
 template <class Cfg, int OUT>
@@ -77,7 +87,7 @@ __global__ void __launch_bounds__(kMxThreads, 1)
 gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                   const __grid_constant__ CUtensorMap tmSFA, const __grid_constant__ CUtensorMap tmSFB,
                   const __grid_constant__ CUtensorMap tmC, void* __restrict__ Cptr, int64_t ldc,
-                  uint8_t* __restrict__ SFC, const GemmShape shape) {
+                  uint8_t* __restrict__ SFC, const GemmShape shape, const __grid_constant__ MxGroups groups) {
   constexpr int CG = Cfg::CG, STAGES = Cfg::STAGES;
   constexpr bool OUT_F32 = (OUT == 1);
   extern __shared__ uint8_t smem_raw[];
@@ -162,7 +172,17 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
       tile_coord(t, shape, tm, tn);
       const int mblk = tm * CG + (int)cta_rank;            // 128-row block of A / C
       const int m0 = mblk * kBlockM;
-      const int n0 = tn * Cfg::BN + (int)cta_rank * Cfg::BN_CTA;
+      int n0 = tn * Cfg::BN + (int)cta_rank * Cfg::BN_CTA;    // row of the (stacked) B matrices
+      int sfb_blk = tn * (Cfg::BN / 128);                      // 128-row block of their scales
+      if (groups.count > 0) {
+        int lo = 0, hi = groups.count - 1;                    // the last group that starts at or before this row block
+        while (lo < hi) {
+          const int mid = (lo + hi + 1) >> 1;
+          if (groups.first_block[mid] <= mblk) lo = mid; else hi = mid - 1;
+        }
+        n0 += lo * shape.N;
+        sfb_blk += lo * ((shape.N + 127) / 128);
+      }
       if constexpr (DYN) {
         if (cta_rank == 0 && issuer) ring.request(n + 1);   // the answer arrives while this unit loads
       }
@@ -180,7 +200,7 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
             tma_load_2d(a_dst, &tmA, kb * kMxBlockK, m0, full_bar(s));
             tma_load_2d(b_dst, &tmB, kb * kMxBlockK, n0, full_bar(s));
             tma_load_2d(sfa_dst, &tmSFA, kb * 128, mblk, full_bar(s));
-            tma_load_2d(sfb_dst, &tmSFB, kb * 128, tn * (Cfg::BN / 128), full_bar(s));
+            tma_load_2d(sfb_dst, &tmSFB, kb * 128, sfb_blk, full_bar(s));
           }
         } else {
           const uint32_t lead_full = map_to_cta(full_bar(s), 0);
@@ -189,7 +209,7 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
             tma_load_2d_pair(a_dst, &tmA, kb * kMxBlockK, m0, lead_full);
             tma_load_2d_pair(b_dst, &tmB, kb * kMxBlockK, n0, lead_full);
             tma_load_2d_pair(sfa_dst, &tmSFA, kb * 128, mblk, lead_full);
-            tma_load_2d_pair(sfb_dst, &tmSFB, kb * 128, tn * (Cfg::BN / 128), lead_full);
+            tma_load_2d_pair(sfb_dst, &tmSFB, kb * 128, sfb_blk, lead_full);
           }
         }
         __syncwarp();

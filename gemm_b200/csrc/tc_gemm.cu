@@ -1074,6 +1074,7 @@ struct MxArgs {
   int k_splits = 1;        // > 1: FP32 partials go to `scratch` ([k_splits][M][N]), then a reduce pass
   float* scratch = nullptr;
   uint8_t* SFC = nullptr;  // packed scales of C for the quantising epilogue
+  MxGroups groups = {};    // count > 0: grouped launch, Bq / SFB hold count matrices one after another
 };
 
 // packed scale buffer of `rows` rows viewed as int32 [row blocks][kchunks * 128]
@@ -1095,11 +1096,13 @@ static int launch_mxfp8(const MxArgs& a) {
   if (int rc = make_map_2d(&tmA, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, a.Aq, a.M, a.K, a.K, kMxBlockK, Cfg::A_ROWS,
                            CU_TENSOR_MAP_SWIZZLE_128B))
     return rc;
-  if (int rc = make_map_2d(&tmB, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, a.Bq, a.N, a.K, a.K, kMxBlockK, Cfg::BN_CTA,
+  // grouped launch: the B matrices (and their scale buffers, ceil(N / 128) blocks each) as one tall matrix
+  const int64_t nb = a.groups.count > 0 ? a.groups.count : 1;
+  if (int rc = make_map_2d(&tmB, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, a.Bq, nb * a.N, a.K, a.K, kMxBlockK, Cfg::BN_CTA,
                            CU_TENSOR_MAP_SWIZZLE_128B))
     return rc;
   if (int rc = make_scale_map(&tmSFA, a.SFA, a.M, a.K, 1)) return rc;
-  if (int rc = make_scale_map(&tmSFB, a.SFB, a.N, a.K, Cfg::BN / 128)) return rc;
+  if (int rc = make_scale_map(&tmSFB, a.SFB, nb > 1 ? nb * ceil_div64(a.N, 128) * 128 : a.N, a.K, Cfg::BN / 128)) return rc;
   CUtensorMap tmC = tmA;   // only read by the TMA-store epilogue
   if (Cfg::EPI == 1) {
     if (OUT == 2) {   // e4m3 bytes: 128 columns x 32 rows per store
@@ -1135,7 +1138,8 @@ static int launch_mxfp8(const MxArgs& a) {
   const int clusters = Cfg::DYN ? (int)num_tiles : (int)(num_tiles < max_clusters ? num_tiles : max_clusters);
   if (Cfg::DYN && shape.k_splits > 1)
     return fail(GEMM_B200_ERR_INVALID_ARG, "gemm_mxfp8: K splits run on the static schedule");
-  return launch_clusters(kern, clusters, CG, kMxThreads, Cfg::SMEM_BYTES, a.stream, tmA, tmB, tmSFA, tmSFB, tmC, a.C, a.ldc, a.SFC, shape);
+  return launch_clusters(kern, clusters, CG, kMxThreads, Cfg::SMEM_BYTES, a.stream, tmA, tmB, tmSFA, tmSFB, tmC, a.C, a.ldc, a.SFC, shape,
+                         a.groups);
 }
 
 // Split-K: FP32 partial sums of every (tile, K split) into scratch, then one reduce pass into C.
@@ -1294,6 +1298,74 @@ extern "C" int gemm_b200_quantize_mxfp8(const void* X, int64_t rows, int64_t K, 
   }
   launch_counter().fetch_add(1, std::memory_order_relaxed);
   GEMM_B200_CUDA_TRY(cudaGetLastError());
+  return GEMM_B200_OK;
+}
+
+extern "C" int gemm_b200_gemm_mxfp8_grouped(const void* Aq, const void* SFA, const void* Bq, const void* SFB, void* C,
+                                            int64_t groups, const int64_t* m_sizes, int64_t N, int64_t K, int64_t ldc,
+                                            int out_dtype, void* stream) {
+  using namespace gemm_b200;
+  if (groups < 0 || N < 0 || K < 0) return fail(GEMM_B200_ERR_INVALID_ARG, "gemm_mxfp8_grouped: negative size");
+  if (out_dtype != GEMM_B200_OUT_BF16 && out_dtype != GEMM_B200_OUT_F32)
+    return fail(GEMM_B200_ERR_INVALID_ARG, "gemm_mxfp8_grouped: out_dtype %d", out_dtype);
+  if (K % 32 != 0) return fail(GEMM_B200_ERR_INVALID_ARG, "gemm_mxfp8_grouped: K must be a multiple of 32");
+  if (groups == 0 || N == 0) return GEMM_B200_OK;
+  if (!m_sizes) return fail(GEMM_B200_ERR_INVALID_ARG, "gemm_mxfp8_grouped: null m_sizes");
+  int64_t rows = 0;
+  for (int64_t g = 0; g < groups; ++g) {
+    if (m_sizes[g] < 0 || m_sizes[g] % 256 != 0)
+      return fail(GEMM_B200_ERR_INVALID_ARG, "gemm_mxfp8_grouped: group %lld has %lld rows, not a multiple of 256 (pad the group)",
+                  (long long)g, (long long)m_sizes[g]);
+    rows += m_sizes[g];
+    if (rows > 0x7fffffff) return fail(GEMM_B200_ERR_TOO_LARGE, "gemm_mxfp8_grouped: more than 2^31-1 rows");
+  }
+  if (rows == 0) return GEMM_B200_OK;
+  if (N > 0x7fffffff || K > 0x7fffffff || groups * N > 0x7fffffff)
+    return fail(GEMM_B200_ERR_TOO_LARGE, "gemm_mxfp8_grouped: a dimension exceeds 2^31-1");
+  if (!C || (K > 0 && (!Aq || !Bq || !SFA || !SFB))) return fail(GEMM_B200_ERR_INVALID_ARG, "gemm_mxfp8_grouped: null pointer");
+  if (ldc < N) return fail(GEMM_B200_ERR_INVALID_ARG, "gemm_mxfp8_grouped: ldc smaller than N");
+  const int c_elem = out_dtype == GEMM_B200_OUT_F32 ? 4 : 2;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (K == 0) {
+    GEMM_B200_CUDA_TRY(cudaMemset2DAsync(C, (size_t)ldc * c_elem, 0, (size_t)N * c_elem, (size_t)rows, st));
+    return GEMM_B200_OK;
+  }
+  if ((reinterpret_cast<uintptr_t>(Aq) | reinterpret_cast<uintptr_t>(Bq) | reinterpret_cast<uintptr_t>(C) |
+       reinterpret_cast<uintptr_t>(SFA) | reinterpret_cast<uintptr_t>(SFB)) % 16 != 0)
+    return fail(GEMM_B200_ERR_ALIGNMENT, "gemm_mxfp8_grouped: all pointers must be 16-byte aligned");
+  if ((ldc * c_elem) % 16 != 0 || N % (16 / c_elem) != 0 || (N * K) % 16 != 0)
+    return fail(GEMM_B200_ERR_ALIGNMENT, "gemm_mxfp8_grouped: ldc*sizeof(C), N*sizeof(C) and N*K must be multiples of 16 bytes");
+  tc::DeviceInfo di;
+  if (int rc = tc::device_info(&di)) return rc;
+  if (di.cc_major != 10)
+    return fail(GEMM_B200_ERR_UNSUPPORTED, "gemm_mxfp8_grouped: device has compute capability %d.x, need 10.x (sm_100a)", di.cc_major);
+  const size_t sf_b = gemm_b200_mxfp8_scale_bytes(N, K);           // scale bytes of one B matrix
+  const size_t sf_row_block = (size_t)ceil_div64(K / 32, 4) * 512; // scale bytes of one 128-row block of A
+  int64_t row0 = 0;
+  for (int64_t g0 = 0; g0 < groups; g0 += tc::kMaxGroups) {
+    const int n = (int)(groups - g0 < tc::kMaxGroups ? groups - g0 : tc::kMaxGroups);
+    tc::MxArgs args{static_cast<const char*>(Aq) + row0 * K, static_cast<const char*>(SFA) + (size_t)(row0 / 128) * sf_row_block,
+                    static_cast<const char*>(Bq) + g0 * N * K, static_cast<const char*>(SFB) + (size_t)g0 * sf_b,
+                    static_cast<char*>(C) + row0 * ldc * c_elem, 0, N, K, ldc, st};
+    args.groups.count = n;
+    int64_t r = 0;
+    for (int g = 0; g < n; ++g) {
+      args.groups.first_block[g] = (int)(r / 128);
+      r += m_sizes[g0 + g];
+    }
+    args.groups.first_block[n] = (int)(r / 128);
+    args.M = r;
+    row0 += r;
+    if (r == 0) continue;
+    // CTA-pair tiles; units handed out at run time for long K and several rounds, as in the plain entry
+    const int64_t units256 = ceil_div64(r, 2 * tc::kBlockM) * ceil_div64(N, tc::kBlockN);
+    static const bool dyn_ok = env_int("GEMM_B200_MXFP8_DYNAMIC", 1) != 0;
+    const int config = (dyn_ok && 2 * units256 > (int64_t)di.sms && K >= 8192) ? tc::kDynMxConfig : tc::kDefaultMxConfig;
+    if (log_enabled())
+      fprintf(stderr, "[gemm_b200] gemm_mxfp8_grouped %d groups, %lld rows x %lldx%lld -> %s\n", n, (long long)r, (long long)K,
+              (long long)N, tc::kMxConfigs[config].name);
+    if (int rc = tc::kMxConfigs[config].launch[out_dtype](args)) return rc;
+  }
   return GEMM_B200_OK;
 }
 

@@ -16,7 +16,7 @@ from ._lib import lib, check
 __all__ = [
     "sgemm_f32", "sgemm_f32_batched", "gemm_bf16", "gemm_bf16_batched", "gemm_bf16_grouped", "gemm_bf16_at", "check_status", "sgemm_f32_host", "gemm_bf16_host",
     "sgemm_f32_configs", "gemm_bf16_configs", "launch_count",
-    "quantize_mxfp8", "gemm_mxfp8", "gemm_mxfp8_configs", "MxFp8Tensor", "gemm_mxfp8_splitk", "gemm_mxfp8_auto_splits", "gemm_mxfp8_quant_out",
+    "quantize_mxfp8", "gemm_mxfp8", "gemm_mxfp8_configs", "MxFp8Tensor", "gemm_mxfp8_splitk", "gemm_mxfp8_auto_splits", "gemm_mxfp8_quant_out", "gemm_mxfp8_grouped", "quantize_mxfp8_stack",
 ]
 
 
@@ -339,6 +339,46 @@ def gemm_mxfp8(A: MxFp8Tensor, B: MxFp8Tensor, out: torch.Tensor | None = None, 
         else:
             check(lib.gemm_b200_gemm_mxfp8_cfg(A.data.data_ptr(), A.scales.data_ptr(), B.data.data_ptr(), B.scales.data_ptr(),
                                                out.data_ptr(), M, N, K, _row_major_ld(out), od, config, _stream(A.data)))
+    return out
+
+
+def quantize_mxfp8_stack(B3: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor]:
+    """Quantises a stack of B matrices ``[groups, K, N]`` (bf16) for ``gemm_mxfp8_grouped``: returns the e4m3
+    bytes ``[groups, N, K]`` and the packed scale buffers ``[groups, scale_bytes(N, K)]``, one matrix after another."""
+    _require(B3.is_cuda and B3.dtype == torch.bfloat16 and B3.dim() == 3, "expected a 3-D CUDA bfloat16 tensor")
+    G, K, N = (int(x) for x in B3.shape)
+    sb = max(int(lib.gemm_b200_mxfp8_scale_bytes(N, K)), 1)
+    data = torch.empty((G, N, K), device=B3.device, dtype=torch.uint8)
+    scales = torch.empty((G, sb), device=B3.device, dtype=torch.uint8)
+    for g in range(G):
+        q = quantize_mxfp8(B3[g], transposed_in=True)
+        data[g].copy_(q.data)
+        scales[g].copy_(q.scales)
+    return data, scales
+
+
+def gemm_mxfp8_grouped(A: MxFp8Tensor, b_data: torch.Tensor, b_scales: torch.Tensor, m_sizes, out: torch.Tensor | None = None, *,
+                       out_dtype: torch.dtype = torch.bfloat16) -> torch.Tensor:
+    """Grouped MXFP8 GEMM: rows of group g of ``A`` (quantised as one tall matrix) times ``B_g`` into the same
+    rows of ``out``.  ``b_data`` ``[groups, N, K]`` / ``b_scales`` ``[groups, scale_bytes]`` as ``quantize_mxfp8_stack``
+    returns them; every entry of ``m_sizes`` a multiple of 256 (pad the groups), their sum ``A.rows``."""
+    _require(b_data.is_cuda and b_data.dtype == torch.uint8 and b_data.dim() == 3 and b_data.is_contiguous(), "b_data must be a contiguous [groups, N, K] uint8 tensor")
+    _require(b_scales.is_cuda and b_scales.dtype == torch.uint8 and b_scales.dim() == 2 and b_scales.is_contiguous(), "b_scales must be a contiguous [groups, bytes] uint8 tensor")
+    _require(out_dtype in (torch.bfloat16, torch.float32), "out_dtype must be bfloat16 or float32")
+    sizes = [int(m) for m in m_sizes]
+    G, N, K = (int(x) for x in b_data.shape)
+    _require(len(sizes) == G, f"{len(sizes)} group sizes for {G} B matrices")
+    _require(K == A.K, f"K mismatch: {A.K} vs {K}")
+    _require(sum(sizes) == A.rows, f"the group sizes sum to {sum(sizes)}, A has {A.rows} rows")
+    _require(b_scales.shape[0] == G and b_scales.shape[1] == max(int(lib.gemm_b200_mxfp8_scale_bytes(N, K)), 1), "b_scales has the wrong shape")
+    if out is None:
+        out = torch.empty((A.rows, N), device=A.data.device, dtype=out_dtype)
+    _require(out.is_cuda and out.dtype == out_dtype and tuple(out.shape) == (A.rows, N), "bad out tensor")
+    arr = (C.c_int64 * max(G, 1))(*sizes)
+    od = _lib.OUT_F32 if out_dtype == torch.float32 else _lib.OUT_BF16
+    with _OnDevice(A.data.device):
+        check(lib.gemm_b200_gemm_mxfp8_grouped(A.data.data_ptr(), A.scales.data_ptr(), b_data.data_ptr(), b_scales.data_ptr(),
+                                               out.data_ptr(), G, arr, N, K, _row_major_ld(out), od, _stream(A.data)))
     return out
 
 

@@ -223,6 +223,21 @@ int gemm_b200_gemm_mxfp8_splitk(const void* Aq, const void* SFA, const void* Bq,
                                 int k_splits, void* scratch, size_t scratch_bytes, void* stream);
 size_t gemm_b200_gemm_mxfp8_splitk_scratch_bytes(int64_t M, int64_t N, int k_splits);
 
+/* Grouped form (tokens sorted by expert in a mixture-of-experts layer, in MXFP8): `groups` problems
+ * that share N and K,
+ *   C[rows of group g, :] = A[rows of group g, :] @ B_g,
+ * with the groups' rows following one another in one tall Aq [sum m_sizes, K] (its packed scales SFA
+ * cover the tall matrix) and one tall C (ldc).  Bq holds the `groups` quantised matrices [N, K] one
+ * after another and SFB their packed scale buffers one after another
+ * (gemm_b200_mxfp8_scale_bytes(N, K) bytes each).  m_sizes is a HOST array; every entry must be a
+ * multiple of 256 (zero allowed): scales are packed per 128 rows and a CTA pair owns 256 rows, so
+ * the caller pads each group.  One launch per 64 groups; each group's rows equal, bit for bit,
+ * gemm_b200_gemm_mxfp8_cfg on that group alone with variant "2cta_256x256x128_s5_maskcommit_tmastore".
+ * The reference multiplies one pair of FP32 matrices per call (naive/naive.cpp:6-22); no counterpart. */
+int gemm_b200_gemm_mxfp8_grouped(const void* Aq, const void* SFA, const void* Bq, const void* SFB, void* C,
+                                 int64_t groups, const int64_t* m_sizes, int64_t N, int64_t K, int64_t ldc,
+                                 int out_dtype, void* stream);
+
 /* Split-K inside a thread-block cluster (see gemm_b200_gemm_bf16_cluster_splitk): k_splits = 2, 4
  * or 8 CTAs per 128 x 128 tile, partial sums combined through distributed shared memory, one
  * launch, no scratch.  Every range must hold at least one block of 128 k.  gemm_b200_gemm_mxfp8()
