@@ -251,6 +251,7 @@ static int mxfp8_model_splits(int64_t M, int64_t N, int64_t K, int sms) {
   for (int s = 2; s <= 32; ++s) {
     const int64_t kb_per = ceil_div64(num_kb, s);
     if (kb_per < 8) break;
+    if ((double)s * (double)M * (double)N * 4.0 > 268435456.0) break;   // scratch of at most 256 MiB
     if (ceil_div64(num_kb, kb_per) != s) continue;
     const double cost = (double)ceil_div64(tiles * s, slots) * (double)kb_per * 0.39 + s * slice_us + 6.0;
     if (cost < best_cost) { best_cost = cost; best = s; }
@@ -742,6 +743,7 @@ static int bf16_auto_splits(int64_t M, int64_t N, int64_t K, int sms) {
   for (int s = 2; s <= 32; ++s) {
     const int64_t kb_per = ceil_div64(num_kb, s);
     if (kb_per < 8) break;                                       // at least 512 of K per range
+    if ((double)s * (double)M * (double)N * 4.0 > 268435456.0) break;   // scratch of at most 256 MiB
     if (ceil_div64(num_kb, kb_per) != s) continue;               // no empty range
     const double cost = (double)ceil_div64(tiles * s, slots) * (double)kb_per * t_kb + s * slice_us + 6.0;
     if (cost < best_cost) { best_cost = cost; best = s; }

@@ -110,7 +110,7 @@ const char* gemm_b200_gemm_bf16_config_name(int config);
  * gemm_b200_gemm_bf16() takes the split path by itself with the count of
  * gemm_b200_gemm_bf16_auto_splits() (1 = it does not split), on scratch the library owns: one
  * buffer per (device, stream), so calls on different streams may overlap and calls on one stream
- * are ordered anyway.  The first split call on a stream, and a later one that needs a larger
+ * are ordered anyway (at most 256 MiB per buffer).  The first split call on a stream, and a later one that needs a larger
  * buffer, allocate (cudaMalloc; growing also frees, which waits for the device); during stream
  * capture such a call runs unsplit instead.  The library keeps buffers for the 32 most recently
  * used streams.  N % 4 == 0.  The reference always walks K inside one thread
@@ -215,9 +215,11 @@ int gemm_b200_gemm_mxfp8_quant_out(const void* Aq, const void* SFA, const void* 
  * ranges of K whose FP32 partial sums go to `scratch` ([k_splits][M][N] floats, device memory,
  * 16-byte aligned, at least gemm_b200_gemm_mxfp8_splitk_scratch_bytes() bytes) and are then
  * summed in ascending split order into C by a second kernel.  gemm_b200_gemm_mxfp8() takes this
- * path by itself for M <= 128 (and for a handful of tiles with K >= 16384) with the split count
- * of gemm_b200_gemm_mxfp8_auto_splits(), on library-owned scratch kept per (device, stream) under
- * the rules given for gemm_b200_gemm_bf16_splitk above.  No counterpart in the reference. */
+ * path by itself for M <= 128 and for a handful of tiles with K >= 16384, with the split count
+ * of gemm_b200_gemm_mxfp8_auto_splits(), and for taller problems with K >= 16384 where its estimate
+ * of the call time favours K ranges, on library-owned scratch kept per (device, stream) under
+ * the rules given for gemm_b200_gemm_bf16_splitk above (at most 256 MiB of it).  No counterpart in
+ * the reference. */
 int gemm_b200_gemm_mxfp8_splitk(const void* Aq, const void* SFA, const void* Bq, const void* SFB,
                                 void* C, int64_t M, int64_t N, int64_t K, int64_t ldc, int out_dtype,
                                 int k_splits, void* scratch, size_t scratch_bytes, void* stream);
