@@ -156,9 +156,11 @@ struct GemmShape {
   // problems share one (batch stride 0).  c_batch_stride: elements between the C matrices.
   int batch, a_z, b_z;
   int64_t c_batch_stride;
-  // BF16 kernel: load A tiles with L2 priority evict-first and B tiles evict-last.  Set for
+  // BF16 kernel, 1: load A tiles with L2 priority evict-first and B tiles evict-last.  Set for
   // problems whose raster band lasts many rounds of units: there the band's B panel is re-read
-  // every round while an A tile is needed only by the clusters of one round.
+  // every round while an A tile is needed only by the clusters of one round.  2: B tiles
+  // evict-first and A tiles evict-last, for problems of one row tile, which stream B once.
+  // MXFP8 kernel, non-zero: B tiles evict-first (single-CTA variants, one row tile).
   int l2_stream_a_keep_b;
 };
 
@@ -294,7 +296,11 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     // elected lane issues the copies.
     const bool issuer = elect_one();
     const bool hinted = shape.l2_stream_a_keep_b != 0;
-    const uint64_t pol_a = hinted ? l2_policy_evict_first() : 0ull, pol_b = hinted ? l2_policy_evict_last() : 0ull;
+    // 1: A tiles evict-first, B tiles evict-last (long raster bands); 2: the other way round (one row
+    // tile: every byte of B is read once, by one CTA, while all CTAs share the few rows of A)
+    const bool stream_b = shape.l2_stream_a_keep_b == 2;
+    const uint64_t pol_a = !hinted ? 0ull : (stream_b ? l2_policy_evict_last() : l2_policy_evict_first());
+    const uint64_t pol_b = !hinted ? 0ull : (stream_b ? l2_policy_evict_first() : l2_policy_evict_last());
     auto load_p = [&](uint32_t dst, const CUtensorMap* map, int x, int y, int z, uint32_t bar, uint64_t pol) {
       if (hinted) {
         if constexpr (CG == 1) tma_load_3d_hint(dst, map, x, y, z, bar, pol);

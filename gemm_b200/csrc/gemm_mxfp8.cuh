@@ -164,6 +164,8 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
     // ------------------------------------------------------------------ TMA producer
     // The whole warp walks the schedule; one elected lane issues the copies.
     const bool issuer = elect_one();
+    const bool stream_b = (CG == 1) && shape.l2_stream_a_keep_b != 0;   // set by the host for single-row-tile problems
+    const uint64_t pol_b = stream_b ? l2_policy_evict_first() : 0ull;
     uint32_t it = 0, n = 0;   // n: how many units this cluster has started
     int u = cluster_id;
     while (u >= 0 && u < num_units && !failed) {
@@ -198,7 +200,11 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
           if (issuer) {
             mbar_arrive_expect_tx(full_bar(s), Cfg::STAGE_BYTES);
             tma_load_2d(a_dst, &tmA, kb * kMxBlockK, m0, full_bar(s));
-            tma_load_2d(b_dst, &tmB, kb * kMxBlockK, n0, full_bar(s));
+            // one row tile: every byte of B is read once, by this CTA.  Evict-first keeps the stream
+            // from pushing other data (the caller's, or dirty lines that would have to be written
+            // back while this kernel reads) out of the L2
+            if (stream_b) tma_load_2d_hint(b_dst, &tmB, kb * kMxBlockK, n0, full_bar(s), pol_b);
+            else tma_load_2d(b_dst, &tmB, kb * kMxBlockK, n0, full_bar(s));
             tma_load_2d(sfa_dst, &tmSFA, kb * 128, mblk, full_bar(s));
             tma_load_2d(sfb_dst, &tmSFB, kb * 128, sfb_blk, full_bar(s));
           }

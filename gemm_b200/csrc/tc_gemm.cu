@@ -421,6 +421,12 @@ static int launch_bf16(const Bf16Args& a) {
   {
     const int64_t band = shape.raster_group < 0 ? (-shape.raster_group < shape.tiles_n ? -shape.raster_group : shape.tiles_n) : 0;
     shape.l2_stream_a_keep_b = (Cfg::DYN && a.batch == 1 && band > 0 && (int64_t)shape.tiles_m * band >= 3 * (int64_t)max_clusters) ? 1 : 0;
+    // one row tile of a single-CTA variant: B is read exactly once; keep the stream from pushing other
+    // data (or dirty lines that would have to be written back meanwhile) out of the L2.  Per call after a
+    // 252 MB write flush, without / with: 16 x 8192 x 28672 90.2 / 78.8 us (cuBLAS 86.8), 128 x 8192 x 28672
+    // 90.9 / 80.7 (95.3), 16 x 8192 x 8192 39.9 / 35.8 (33.7); after a read flush the same either way.
+    static const bool stream_ok = env_int("GEMM_B200_BF16_STREAM_B", 1) != 0;
+    if (stream_ok && CG == 1 && shape.tiles_m == 1 && a.batch == 1) shape.l2_stream_a_keep_b = 2;
   }
   const int64_t num_tiles = (int64_t)shape.tiles_m * shape.tiles_n * a.batch * shape.k_splits;
   if (num_tiles > 0x7fffffff) return fail(GEMM_B200_ERR_TOO_LARGE, "gemm_bf16: too many tiles");
@@ -1131,7 +1137,11 @@ static int launch_mxfp8(const MxArgs& a) {
   shape.batch = 1;
   shape.a_z = shape.b_z = 0;
   shape.c_batch_stride = 0;
-  shape.l2_stream_a_keep_b = 0;
+  // MXFP8 kernel: B tiles evict-first when there is one row tile (B is then read exactly once).
+  // Per call after a 252 MB write flush (an L2 full of dirty lines), without / with: 16 x 8192 x 28672
+  // 57.4 / 53.2 us, 128 x 8192 x 28672 61.7 / 52.0, 16 x 8192 x 8192 27.6 / 23.7; after a read flush the same.
+  static const bool stream_ok = env_int("GEMM_B200_MXFP8_STREAM_B", 1) != 0;
+  shape.l2_stream_a_keep_b = (stream_ok && CG == 1 && shape.tiles_m == 1) ? 1 : 0;
   shape.k_splits = (int)ceil_div64(num_kb, shape.kb_per_split);   // no empty split
   shape.split_stride = a.M * a.N;
   shape.raster_group = raster_group_for((int64_t)Cfg::BN * a.K, Cfg::BN, 0);
