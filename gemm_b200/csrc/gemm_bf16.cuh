@@ -284,8 +284,12 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   tc_fence_after_sync();
   uint32_t tmem_base;
   asm volatile("ld.shared.u32 %0, [%1];" : "=r"(tmem_base) : "r"(tmem_slot) : "memory");
-  // split-K: lets the reduce kernel behind this one be scheduled early; it waits for this grid
-  if (shape.k_splits > 1) pdl_launch_dependents();
+  // Programmatic dependent launch.  This grid may have been scheduled while the kernel before it in
+  // the stream was still running: nothing above touches global memory, everything below may, so
+  // wait here for that kernel to complete.  Then let the kernel behind this one (the split-K
+  // reduction, or the next GEMM) be scheduled early in turn; it waits for this grid the same way.
+  pdl_wait();
+  pdl_launch_dependents();
   if (threadIdx.x == 0) trace_stamp(1);
 
   bool failed = false;

@@ -125,6 +125,9 @@ gemm_bf16_cluster_splitk_kernel(const __grid_constant__ CUtensorMap tmA, const _
   tc_fence_after_sync();
   const uint32_t tmem_base = ld_shared_u32(tmem_slot);
   if (threadIdx.x == 0) trace_stamp(1);
+  // programmatic dependent launch: wait for the kernel before this one, let the one behind it be scheduled
+  pdl_wait();
+  pdl_launch_dependents();
 
   bool failed = false;
 

@@ -155,7 +155,10 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
   uint32_t tmem_base;
   asm volatile("ld.shared.u32 %0, [%1];" : "=r"(tmem_base) : "r"(tmem_slot) : "memory");
   // split-K: lets the reduce kernel behind this one be scheduled early; it waits for this grid
-  if (shape.k_splits > 1) pdl_launch_dependents();
+  // programmatic dependent launch: wait for the kernel before this one, let the one behind it be scheduled
+  // (see gemm_bf16_kernel)
+  pdl_wait();
+  pdl_launch_dependents();
   if (threadIdx.x == 0) trace_stamp(1);
 
   bool failed = false;
@@ -493,6 +496,7 @@ splitk_reduce_kernel(const float* __restrict__ W, int64_t split_stride, int64_t 
   const int64_t n4 = N / 4;
   const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   pdl_wait();   // launched early behind the GEMM that writes W: returns once that grid is complete
+  pdl_launch_dependents();
   if (idx >= (int64_t)M * n4) return;
   const int64_t r = idx / n4, c = (idx % n4) * 4;
   const float* src = W + r * ldw + c;
