@@ -59,6 +59,9 @@ __device__ __forceinline__ uint32_t quantise_block(const uint32_t (&w)[16], uint
 __global__ void __launch_bounds__(256)
 quantize_rows_kernel(const __nv_bfloat16* __restrict__ X, int64_t rows, int64_t K, int64_t ldx,
                      uint8_t* __restrict__ Xq, uint8_t* __restrict__ SF, int64_t kb_pad, int64_t rows_pad) {
+  // the GEMM that consumes this operand is a programmatic dependent launch: let it be scheduled and set
+  // itself up now; it waits for this grid to complete before it reads anything
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   const int64_t kb = idx % kb_pad, r = idx / kb_pad;
   if (r >= rows_pad) return;
@@ -101,6 +104,7 @@ __global__ void __launch_bounds__(COLS * 4)
 quantize_cols_kernel(const __nv_bfloat16* __restrict__ X, int64_t rows, int64_t K, int64_t ldx,
                      uint8_t* __restrict__ Xq, uint8_t* __restrict__ SF, int64_t kb_pad, int vec_ok, int tiles_per_cta) {
   static_assert(COLS * 4 == 32 * (COLS / 8), "one warp per eight columns");
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");   // as in quantize_rows_kernel
   // two tiles: the CTA walks tiles_per_cta consecutive K chunks of its columns and fetches chunk i + 1
   // (cp.async, straight into shared memory) while it quantises chunk i, so loads are in flight
   // all the time
