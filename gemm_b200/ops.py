@@ -20,7 +20,21 @@ __all__ = [
 ]
 
 
+# torch's raw accessors (an integer handle instead of a Stream object, the device index without the
+# lazy-initialisation check) when this build of torch has them: they take a few microseconds off
+# every call, which is what a small GEMM costs on the device
+_raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+_raw_device = getattr(torch._C, "_cuda_getDevice", None)
+
+
+def _current_device() -> int:
+    return _raw_device() if _raw_device is not None else torch.cuda.current_device()
+
+
 def _stream(t: torch.Tensor) -> int:
+    if _raw_stream is not None:
+        idx = t.device.index
+        return _raw_stream(idx if idx is not None else _current_device())
     return torch.cuda.current_stream(t.device).cuda_stream
 
 
@@ -31,11 +45,11 @@ class _OnDevice:
     __slots__ = ("idx", "prev")
 
     def __init__(self, device: torch.device):
-        self.idx = device.index if device.index is not None else torch.cuda.current_device()
+        self.idx = device.index if device.index is not None else _current_device()
         self.prev = -1
 
     def __enter__(self):
-        cur = torch.cuda.current_device()
+        cur = _current_device()
         if cur != self.idx:
             self.prev = cur
             torch.cuda.set_device(self.idx)
@@ -54,8 +68,9 @@ def _require(cond: bool, msg: str) -> None:
 
 def _row_major_ld(t: torch.Tensor) -> int:
     _require(t.dim() == 2, "expected a 2-D tensor")
-    _require(t.size(1) <= 1 or t.stride(1) == 1, "tensor must be row-major (unit column stride)")
-    return t.stride(0) if t.size(0) > 1 else max(t.size(1), 1)
+    (rows, cols), (s0, s1) = t.shape, t.stride()
+    _require(cols <= 1 or s1 == 1, "tensor must be row-major (unit column stride)")
+    return s0 if rows > 1 else max(cols, 1)
 
 
 def sgemm_f32(A: torch.Tensor, B: torch.Tensor, out: torch.Tensor | None = None, config: int = -1) -> torch.Tensor:
