@@ -72,6 +72,11 @@ __global__ void __launch_bounds__(C::THREADS, C::MINB)
 sgemm_kernel(const float* __restrict__ A, const float* __restrict__ B, float* __restrict__ Cm,
              int M, int N, int K, int64_t lda, int64_t ldb, int64_t ldc, int tiles_m, int tiles_n,
              int64_t batch_a, int64_t batch_b, int64_t batch_c) {
+  // Programmatic dependent launch: the grid may have been scheduled while the kernel before it in the
+  // stream still runs (when that kernel is one of this library's); wait for it before touching
+  // memory, then let the kernel behind this one be scheduled early in turn.
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   // blockIdx.y = problem of a strided batch (strides in elements; 0 shares the operand)
   A += (int64_t)blockIdx.y * batch_a;
   B += (int64_t)blockIdx.y * batch_b;
@@ -292,10 +297,20 @@ static int launch_cfg(const float* A, const float* B, float* Cm, int M, int N, i
   // at most 65535 problems per launch (grid.y)
   for (int b0 = 0; b0 < batch; b0 += 65535) {
     const int nb = batch - b0 < 65535 ? batch - b0 : 65535;
-    kern<<<dim3((unsigned)tiles, (unsigned)nb), C::THREADS, C::SMEM_BYTES, stream>>>(
-        A + b0 * batch_a, B + b0 * batch_b, Cm + b0 * batch_c, M, N, K, lda, ldb, ldc, tiles_m, tiles_n, batch_a, batch_b, batch_c);
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)tiles, (unsigned)nb);
+    cfg.blockDim = dim3((unsigned)C::THREADS);
+    cfg.dynamicSmemBytes = (size_t)C::SMEM_BYTES;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    static const bool pdl = env_int("GEMM_B200_PDL", 1) != 0;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl ? 1 : 0;
+    GEMM_B200_CUDA_TRY(cudaLaunchKernelEx(&cfg, kern, A + b0 * batch_a, B + b0 * batch_b, Cm + b0 * batch_c, M, N, K, lda, ldb, ldc, tiles_m,
+                                          tiles_n, batch_a, batch_b, batch_c));
     launch_counter().fetch_add(1, std::memory_order_relaxed);
-    GEMM_B200_CUDA_TRY(cudaGetLastError());
   }
   return GEMM_B200_OK;
 }
